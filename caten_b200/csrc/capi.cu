@@ -1,0 +1,493 @@
+// C ABI of libcaten_b200: context, device memory, weight handles, per-kernel entry points and
+// the whole GPT-2 step.  See include/caten_b200.h for the contract of every function.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+
+namespace cb {
+
+static thread_local std::string g_err = "";
+
+int fail(caten_b200_ctx *ctx, int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (ctx) ctx->err = buf;
+  else g_err = buf;
+  return code;
+}
+
+int cuda_fail(caten_b200_ctx *ctx, cudaError_t e, const char *what) {
+  return fail(ctx, CATEN_B200_ECUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+int scratch_reserve(caten_b200_ctx *ctx, Scratch *s, size_t bytes) {
+  if (s->bytes >= bytes) return 0;
+  if (s->ptr) CB_CUDA(ctx, cudaFree(s->ptr));  // cudaFree waits for work that may still read it
+  s->ptr = nullptr;
+  s->bytes = 0;
+  const size_t want = bytes + bytes / 4;
+  CB_CUDA(ctx, cudaMalloc(&s->ptr, want));
+  s->bytes = want;
+  return 0;
+}
+
+static int check_status(caten_b200_ctx *ctx) {
+  if (ctx->h_status[0] != DEV_OK) {
+    const int code = ctx->h_status[0], where = ctx->h_status[1], detail = ctx->h_status[2];
+    ctx->h_status[0] = 0;
+    cudaMemsetAsync(ctx->d_status, 0, 4 * sizeof(int), ctx->stream);
+    return fail(ctx, CATEN_B200_EDEVICE, "kernel-side check failed: code %d (%s) at site %d, detail %d", code,
+                code == DEV_WAIT_TIMEOUT ? "bounded wait ran out" : "bad index", where, detail);
+  }
+  return 0;
+}
+
+}  // namespace cb
+
+using namespace cb;
+
+#define NEED_CTX(ctx)                                                              \
+  do {                                                                             \
+    if (!(ctx)) return cb::fail(nullptr, CATEN_B200_EINVAL, "%s: ctx is NULL", __func__); \
+    cudaSetDevice((ctx)->device);                                                  \
+  } while (0)
+
+extern "C" {
+
+const char *caten_b200_arch(void) { return "sm_100a"; }
+
+const char *caten_b200_last_error(caten_b200_ctx *ctx) { return ctx ? ctx->err.c_str() : cb::g_err.c_str(); }
+
+int caten_b200_init(int device, caten_b200_ctx **out) {
+  if (!out) return fail(nullptr, CATEN_B200_EINVAL, "caten_b200_init: ctx out pointer is NULL");
+  *out = nullptr;
+  int ndev = 0;
+  cudaError_t e = cudaGetDeviceCount(&ndev);
+  if (e != cudaSuccess) return cuda_fail(nullptr, e, "cudaGetDeviceCount");
+  if (device < 0 || device >= ndev) return fail(nullptr, CATEN_B200_EINVAL, "caten_b200_init: device %d of %d", device, ndev);
+  if ((e = cudaSetDevice(device)) != cudaSuccess) return cuda_fail(nullptr, e, "cudaSetDevice");
+  cudaDeviceProp prop;
+  if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) return cuda_fail(nullptr, e, "cudaGetDeviceProperties");
+  if (prop.major != 10)
+    return fail(nullptr, CATEN_B200_EUNSUPPORTED, "caten_b200_init: device %d is sm_%d%d; this library holds sm_100a code only",
+                device, prop.major, prop.minor);
+  caten_b200_ctx *ctx = new (std::nothrow) caten_b200_ctx();
+  if (!ctx) return fail(nullptr, CATEN_B200_ECUDA, "out of host memory");
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaStreamCreate"); }
+  if ((e = cudaMalloc(&ctx->d_status, 4 * sizeof(int))) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaMalloc"); }
+  cudaMemset(ctx->d_status, 0, 4 * sizeof(int));
+  if ((e = cudaMallocHost(&ctx->h_status, 4 * sizeof(int))) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaMallocHost"); }
+  for (int i = 0; i < 4; ++i) ctx->h_status[i] = 0;
+  cudaDriverEntryPointQueryResult qres;
+  void *fn = nullptr;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+      qres == cudaDriverEntryPointSuccess)
+    ctx->encode_tiled = fn;
+  *out = ctx;
+  return 0;
+}
+
+int caten_b200_destroy(caten_b200_ctx *ctx) {
+  if (!ctx) return 0;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  if (ctx->xbf.ptr) cudaFree(ctx->xbf.ptr);
+  if (ctx->wtmp.ptr) cudaFree(ctx->wtmp.ptr);
+  cudaFree(ctx->d_status);
+  cudaFreeHost(ctx->h_status);
+  cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return 0;
+}
+
+void *caten_b200_stream(caten_b200_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
+
+int caten_b200_malloc(caten_b200_ctx *ctx, size_t bytes, void **d_ptr) {
+  NEED_CTX(ctx);
+  if (!d_ptr) return fail(ctx, CATEN_B200_EINVAL, "malloc: out pointer is NULL");
+  *d_ptr = nullptr;
+  if (bytes == 0) bytes = 16;
+  CB_CUDA(ctx, cudaMalloc(d_ptr, bytes));
+  CB_CUDA(ctx, cudaMemsetAsync(*d_ptr, 0, bytes, ctx->stream));
+  return 0;
+}
+
+int caten_b200_free(caten_b200_ctx *ctx, void *d_ptr) {
+  NEED_CTX(ctx);
+  if (d_ptr) CB_CUDA(ctx, cudaFree(d_ptr));
+  return 0;
+}
+
+int caten_b200_h2d(caten_b200_ctx *ctx, void *d_dst, const void *h_src, size_t bytes) {
+  NEED_CTX(ctx);
+  if (bytes && (!d_dst || !h_src)) return fail(ctx, CATEN_B200_EINVAL, "h2d: NULL pointer");
+  CB_CUDA(ctx, cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  CB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return 0;
+}
+
+int caten_b200_d2h(caten_b200_ctx *ctx, void *h_dst, const void *d_src, size_t bytes) {
+  NEED_CTX(ctx);
+  if (bytes && (!h_dst || !d_src)) return fail(ctx, CATEN_B200_EINVAL, "d2h: NULL pointer");
+  CB_CUDA(ctx, cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  return caten_b200_sync(ctx);
+}
+
+int caten_b200_d2d(caten_b200_ctx *ctx, void *d_dst, const void *d_src, size_t bytes) {
+  NEED_CTX(ctx);
+  if (bytes && (!d_dst || !d_src)) return fail(ctx, CATEN_B200_EINVAL, "d2d: NULL pointer");
+  CB_CUDA(ctx, cudaMemcpyAsync(d_dst, d_src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  return 0;
+}
+
+int caten_b200_memset(caten_b200_ctx *ctx, void *d_dst, int byte, size_t bytes) {
+  NEED_CTX(ctx);
+  CB_CUDA(ctx, cudaMemsetAsync(d_dst, byte, bytes, ctx->stream));
+  return 0;
+}
+
+int caten_b200_sync(caten_b200_ctx *ctx) {
+  NEED_CTX(ctx);
+  CB_CUDA(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, 4 * sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  CB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return check_status(ctx);
+}
+
+// ------------------------------------------------------------------------------------------------
+// weights
+// ------------------------------------------------------------------------------------------------
+int64_t caten_b200_weight_nbytes(int type, int64_t rows, int64_t cols) {
+  const int64_t n = rows * cols;
+  switch (type) {
+    case CATEN_B200_F32: return n * 4;
+    case CATEN_B200_F16: return n * 2;
+    case CATEN_B200_Q4_0: return cols % 32 ? -1 : n / 32 * 18;
+    case CATEN_B200_Q8_0: return cols % 32 ? -1 : n / 32 * 34;
+  }
+  return -1;
+}
+
+int caten_b200_weight_upload_device(caten_b200_ctx *ctx, int type, const void *d_blocks, int64_t rows, int64_t cols,
+                                    caten_b200_weight **out) {
+  NEED_CTX(ctx);
+  if (!out) return fail(ctx, CATEN_B200_EINVAL, "weight_upload: out pointer is NULL");
+  *out = nullptr;
+  if (!d_blocks || rows <= 0 || cols <= 0) return fail(ctx, CATEN_B200_EINVAL, "weight_upload: NULL data or empty shape %lldx%lld", (long long)rows, (long long)cols);
+  const int64_t nbytes = caten_b200_weight_nbytes(type, rows, cols);
+  if (nbytes < 0)
+    return fail(ctx, CATEN_B200_EUNSUPPORTED, "weight_upload: ggml type %d with cols=%lld (types: F32=0 F16=1 Q4_0=2 Q8_0=8; quantised cols %% 32 == 0)", type, (long long)cols);
+  caten_b200_weight *w = new (std::nothrow) caten_b200_weight();
+  if (!w) return fail(ctx, CATEN_B200_ECUDA, "out of host memory");
+  w->type = type; w->rows = rows; w->cols = cols; w->ctx = ctx;
+  cudaError_t e;
+  if (type == CATEN_B200_F32 || type == CATEN_B200_F16) {
+    if ((e = cudaMalloc(&w->qs, (size_t)nbytes)) != cudaSuccess) { delete w; return cuda_fail(ctx, e, "cudaMalloc(weight)"); }
+    if ((e = cudaMemcpyAsync(w->qs, d_blocks, (size_t)nbytes, cudaMemcpyDeviceToDevice, ctx->stream)) != cudaSuccess) {
+      cudaFree(w->qs); delete w; return cuda_fail(ctx, e, "cudaMemcpyAsync(weight)");
+    }
+  } else {
+    w->nkb = cols / 32;
+    const int64_t nblocks = rows * w->nkb;
+    const size_t qbytes = (size_t)nblocks * (type == CATEN_B200_Q4_0 ? 16 : 32);
+    if ((e = cudaMalloc(&w->qs, qbytes)) != cudaSuccess) { delete w; return cuda_fail(ctx, e, "cudaMalloc(weight codes)"); }
+    if ((e = cudaMalloc((void **)&w->d, (size_t)nblocks * 2)) != cudaSuccess) { cudaFree(w->qs); delete w; return cuda_fail(ctx, e, "cudaMalloc(weight scales)"); }
+    if (int rc = launch_repack(ctx, type, (const uint8_t *)d_blocks, nblocks, w->qs, w->d)) { cudaFree(w->qs); cudaFree(w->d); delete w; return rc; }
+  }
+  *out = w;
+  return 0;
+}
+
+int caten_b200_weight_upload(caten_b200_ctx *ctx, int type, const void *h_blocks, int64_t rows, int64_t cols,
+                             caten_b200_weight **out) {
+  NEED_CTX(ctx);
+  if (!out) return fail(ctx, CATEN_B200_EINVAL, "weight_upload: out pointer is NULL");
+  *out = nullptr;
+  if (!h_blocks || rows <= 0 || cols <= 0) return fail(ctx, CATEN_B200_EINVAL, "weight_upload: NULL data or empty shape %lldx%lld", (long long)rows, (long long)cols);
+  const int64_t nbytes = caten_b200_weight_nbytes(type, rows, cols);
+  if (nbytes < 0)
+    return fail(ctx, CATEN_B200_EUNSUPPORTED, "weight_upload: ggml type %d with cols=%lld (types: F32=0 F16=1 Q4_0=2 Q8_0=8; quantised cols %% 32 == 0)", type, (long long)cols);
+  void *staging = nullptr;
+  CB_CUDA(ctx, cudaMalloc(&staging, (size_t)nbytes));
+  cudaError_t e = cudaMemcpyAsync(staging, h_blocks, (size_t)nbytes, cudaMemcpyHostToDevice, ctx->stream);
+  if (e != cudaSuccess) { cudaFree(staging); return cuda_fail(ctx, e, "cudaMemcpyAsync(weight H2D)"); }
+  const int rc = caten_b200_weight_upload_device(ctx, type, staging, rows, cols, out);
+  cudaStreamSynchronize(ctx->stream);
+  cudaFree(staging);
+  return rc;
+}
+
+int caten_b200_weight_free(caten_b200_ctx *ctx, caten_b200_weight *w) {
+  NEED_CTX(ctx);
+  if (!w) return 0;
+  if (w->qs) cudaFree(w->qs);
+  if (w->d) cudaFree(w->d);
+  delete w;
+  return 0;
+}
+
+int caten_b200_weight_dequant(caten_b200_ctx *ctx, const caten_b200_weight *w, float *d_out) {
+  NEED_CTX(ctx);
+  if (!w || !d_out) return fail(ctx, CATEN_B200_EINVAL, "weight_dequant: NULL argument");
+  return launch_dequant(ctx, w, d_out);
+}
+
+// ------------------------------------------------------------------------------------------------
+// kernels
+// ------------------------------------------------------------------------------------------------
+static bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+int caten_b200_linear(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *d_x, const float *d_bias,
+                      const float *d_residual, int act, float *d_y, int64_t M, int precision) {
+  NEED_CTX(ctx);
+  if (!w || !d_x || !d_y) return fail(ctx, CATEN_B200_EINVAL, "linear: NULL argument");
+  if (M < 0) return fail(ctx, CATEN_B200_EINVAL, "linear: M < 0");
+  if (M == 0) return 0;
+  if (act < 0 || act > 2) return fail(ctx, CATEN_B200_EINVAL, "linear: unknown activation %d", act);
+  if (!aligned16(d_x) || !aligned16(d_y)) return fail(ctx, CATEN_B200_EINVAL, "linear: x and y must be 16-byte aligned");
+  if (M <= 4) {
+    for (int64_t m = 0; m < M; ++m)
+      if (int rc = launch_gemv(ctx, w, d_x + m * w->cols, d_bias, d_residual ? d_residual + m * w->rows : nullptr, act,
+                               d_y + m * w->rows))
+        return rc;
+    return 0;
+  }
+  switch (precision) {
+    case CATEN_B200_PREC_FP32: return launch_gemm_simt(ctx, w, d_x, d_bias, d_residual, act, d_y, M);
+    case CATEN_B200_PREC_BF16: return launch_gemm_tc(ctx, w, d_x, d_bias, d_residual, act, d_y, M, 1);
+    case CATEN_B200_PREC_BF16X3: return launch_gemm_tc(ctx, w, d_x, d_bias, d_residual, act, d_y, M, 3);
+  }
+  return fail(ctx, CATEN_B200_EINVAL, "linear: unknown precision %d", precision);
+}
+
+int caten_b200_relu_matmul(caten_b200_ctx *ctx, const float *d_a, const float *d_b, float *d_c, int64_t M, int64_t K,
+                           int64_t N, int precision) {
+  NEED_CTX(ctx);
+  if (!d_a || !d_b || !d_c) return fail(ctx, CATEN_B200_EINVAL, "relu_matmul: NULL argument");
+  if (M < 0 || K <= 0 || N < 0) return fail(ctx, CATEN_B200_EINVAL, "relu_matmul: bad shape");
+  switch (precision) {
+    case CATEN_B200_PREC_FP32: return launch_relu_matmul_simt(ctx, d_a, d_b, d_c, M, K, N);
+    case CATEN_B200_PREC_BF16: return launch_relu_matmul_tc(ctx, d_a, d_b, d_c, M, K, N, 1);
+    case CATEN_B200_PREC_BF16X3: return launch_relu_matmul_tc(ctx, d_a, d_b, d_c, M, K, N, 3);
+  }
+  return fail(ctx, CATEN_B200_EINVAL, "relu_matmul: unknown precision %d", precision);
+}
+
+int caten_b200_layernorm(caten_b200_ctx *ctx, const float *d_x, const float *d_gamma, const float *d_beta, float *d_y,
+                         int64_t rows, int64_t d, float eps) {
+  NEED_CTX(ctx);
+  if (!d_x || !d_gamma || !d_beta || !d_y) return fail(ctx, CATEN_B200_EINVAL, "layernorm: NULL argument");
+  if (rows < 0 || d <= 0) return fail(ctx, CATEN_B200_EINVAL, "layernorm: bad shape");
+  return launch_layernorm(ctx, d_x, d_gamma, d_beta, d_y, rows, d, eps);
+}
+
+int caten_b200_embed(caten_b200_ctx *ctx, const float *d_ids_f32, const int64_t *d_ids_i64, const float *d_wte,
+                     const float *d_wpe, float *d_out, int64_t B, int64_t s, int64_t n, int64_t d, int64_t V, int64_t T) {
+  NEED_CTX(ctx);
+  if (!d_wte || !d_wpe || !d_out) return fail(ctx, CATEN_B200_EINVAL, "embed: NULL argument");
+  if (B < 0 || s < 0 || d <= 0) return fail(ctx, CATEN_B200_EINVAL, "embed: bad shape");
+  return launch_embed(ctx, d_ids_f32, d_ids_i64, d_wte, d_wpe, d_out, B, s, n, d, V, T);
+}
+
+int caten_b200_attention(caten_b200_ctx *ctx, const float *d_qkv, float *d_kcache, float *d_vcache, float *d_out,
+                         int64_t B, int64_t s, int64_t n, int64_t H, int64_t T) {
+  NEED_CTX(ctx);
+  if (!d_qkv || !d_kcache || !d_vcache || !d_out) return fail(ctx, CATEN_B200_EINVAL, "attention: NULL argument");
+  if (B < 0 || s < 0 || H <= 0 || T <= 0) return fail(ctx, CATEN_B200_EINVAL, "attention: bad shape");
+  return launch_attention(ctx, d_qkv, d_kcache, d_vcache, d_out, B, s, n, H, T);
+}
+
+int caten_b200_argmax(caten_b200_ctx *ctx, const float *d_x, int64_t rows, int64_t V, int64_t *d_out) {
+  NEED_CTX(ctx);
+  if (!d_x || !d_out) return fail(ctx, CATEN_B200_EINVAL, "argmax: NULL argument");
+  return launch_argmax(ctx, d_x, rows, V, d_out);
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// whole model
+// ------------------------------------------------------------------------------------------------
+struct caten_b200_gpt2 {
+  caten_b200_ctx *ctx = nullptr;
+  caten_b200_gpt2_desc desc;
+  std::vector<const float *> ln1_g, ln1_b, attn_b, proj_b, ln2_g, ln2_b, fc_b, mproj_b;
+  std::vector<const caten_b200_weight *> attn_w, proj_w, fc_w, mproj_w;
+  std::vector<float *> kc, vc;
+  int64_t max_rows = 0;
+  float *h = nullptr, *h2 = nullptr, *xn = nullptr, *qkv = nullptr, *att = nullptr, *ff = nullptr;
+  float *last = nullptr, *logits = nullptr;
+  float *ids_f32 = nullptr;  // staging for host ids [B * T]
+  int64_t *out_ids = nullptr;
+  float *h_ids_pinned = nullptr;
+  int64_t *h_out_pinned = nullptr;
+  int64_t launches0 = 0;
+};
+
+static int linear_any(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
+                      const float *res, int act, float *y, int64_t M, int prec) {
+  return caten_b200_linear(ctx, w, x, bias, res, act, y, M, prec);
+}
+
+extern "C" {
+
+int caten_b200_gpt2_create(caten_b200_ctx *ctx, const caten_b200_gpt2_desc *dsc, caten_b200_gpt2 **out) {
+  NEED_CTX(ctx);
+  if (!dsc || !out) return fail(ctx, CATEN_B200_EINVAL, "gpt2_create: NULL argument");
+  *out = nullptr;
+  const int64_t L = dsc->n_layers, d = dsc->d_model, H = dsc->n_heads, V = dsc->vocab, T = dsc->max_seq_len, B = dsc->batch;
+  if (L <= 0 || d <= 0 || H <= 0 || V <= 0 || T <= 0 || B <= 0) return fail(ctx, CATEN_B200_EINVAL, "gpt2_create: non-positive size");
+  if (d != H * 64) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gpt2_create: head dim %lld/%lld; the attention kernels cover head dim 64 (all GPT-2 sizes)", (long long)d, (long long)H);
+  if (!dsc->wte || !dsc->wpe || !dsc->lnf_g || !dsc->lnf_b || !dsc->lm_head) return fail(ctx, CATEN_B200_EINVAL, "gpt2_create: NULL top-level weight");
+  if (dsc->lm_head->rows != V || dsc->lm_head->cols != d) return fail(ctx, CATEN_B200_EINVAL, "gpt2_create: lm_head is %lldx%lld, expected %lldx%lld", (long long)dsc->lm_head->rows, (long long)dsc->lm_head->cols, (long long)V, (long long)d);
+  caten_b200_gpt2 *m = new (std::nothrow) caten_b200_gpt2();
+  if (!m) return fail(ctx, CATEN_B200_ECUDA, "out of host memory");
+  m->ctx = ctx;
+  m->desc = *dsc;
+  for (int64_t l = 0; l < L; ++l) {
+    const caten_b200_weight *ws[4] = {dsc->attn_w[l], dsc->proj_w[l], dsc->fc_w[l], dsc->mproj_w[l]};
+    const int64_t er[4] = {3 * d, d, 4 * d, d}, ec[4] = {d, d, d, 4 * d};
+    for (int i = 0; i < 4; ++i)
+      if (!ws[i] || ws[i]->rows != er[i] || ws[i]->cols != ec[i]) {
+        delete m;
+        return fail(ctx, CATEN_B200_EINVAL, "gpt2_create: layer %lld weight %d has the wrong shape", (long long)l, i);
+      }
+    m->ln1_g.push_back(dsc->ln1_g[l]); m->ln1_b.push_back(dsc->ln1_b[l]);
+    m->attn_b.push_back(dsc->attn_b[l]); m->proj_b.push_back(dsc->proj_b[l]);
+    m->ln2_g.push_back(dsc->ln2_g[l]); m->ln2_b.push_back(dsc->ln2_b[l]);
+    m->fc_b.push_back(dsc->fc_b[l]); m->mproj_b.push_back(dsc->mproj_b[l]);
+    m->attn_w.push_back(ws[0]); m->proj_w.push_back(ws[1]); m->fc_w.push_back(ws[2]); m->mproj_w.push_back(ws[3]);
+  }
+  int64_t max_rows = dsc->max_rows > 0 ? dsc->max_rows : 8192;
+  if (max_rows < B) max_rows = B;  // a decode step processes the whole batch at once
+  m->max_rows = max_rows;
+  auto alloc = [&](float **p, int64_t n) { return caten_b200_malloc(ctx, (size_t)n * sizeof(float), (void **)p); };
+  int rc = 0;
+  const int64_t kv = B * H * T * 64;
+  for (int64_t l = 0; l < L && !rc; ++l) {
+    float *k = nullptr, *v = nullptr;
+    rc = alloc(&k, kv);
+    if (!rc) rc = alloc(&v, kv);
+    m->kc.push_back(k); m->vc.push_back(v);
+  }
+  if (!rc) rc = alloc(&m->h, max_rows * d);
+  if (!rc) rc = alloc(&m->h2, max_rows * d);
+  if (!rc) rc = alloc(&m->xn, max_rows * d);
+  if (!rc) rc = alloc(&m->qkv, max_rows * 3 * d);
+  if (!rc) rc = alloc(&m->att, max_rows * d);
+  if (!rc) rc = alloc(&m->ff, max_rows * 4 * d);
+  if (!rc) rc = alloc(&m->last, B * d);
+  if (!rc) rc = alloc(&m->logits, B * V);
+  if (!rc) rc = alloc(&m->ids_f32, B * T);
+  if (!rc) rc = caten_b200_malloc(ctx, (size_t)B * sizeof(int64_t), (void **)&m->out_ids);
+  if (!rc && cudaMallocHost(&m->h_ids_pinned, (size_t)B * T * sizeof(float)) != cudaSuccess) rc = fail(ctx, CATEN_B200_ECUDA, "cudaMallocHost(ids)");
+  if (!rc && cudaMallocHost(&m->h_out_pinned, (size_t)B * sizeof(int64_t)) != cudaSuccess) rc = fail(ctx, CATEN_B200_ECUDA, "cudaMallocHost(out ids)");
+  if (rc) { caten_b200_gpt2_destroy(m); return rc; }
+  m->launches0 = ctx->launches;
+  *out = m;
+  return 0;
+}
+
+int caten_b200_gpt2_destroy(caten_b200_gpt2 *m) {
+  if (!m) return 0;
+  caten_b200_ctx *ctx = m->ctx;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  for (float *p : m->kc) if (p) cudaFree(p);
+  for (float *p : m->vc) if (p) cudaFree(p);
+  float *bufs[] = {m->h, m->h2, m->xn, m->qkv, m->att, m->ff, m->last, m->logits, m->ids_f32};
+  for (float *p : bufs) if (p) cudaFree(p);
+  if (m->out_ids) cudaFree(m->out_ids);
+  if (m->h_ids_pinned) cudaFreeHost(m->h_ids_pinned);
+  if (m->h_out_pinned) cudaFreeHost(m->h_out_pinned);
+  delete m;
+  return 0;
+}
+
+// Runs the Transformer (external/llm/layers.lisp:81-90) on `nb` sequences [b0, b0+nb) of s tokens.
+static int run_chunk(caten_b200_gpt2 *m, const float *ids_f32, const int64_t *ids_i64, int64_t b0, int64_t nb, int64_t s,
+                     int64_t n) {
+  caten_b200_ctx *ctx = m->ctx;
+  const caten_b200_gpt2_desc &c = m->desc;
+  const int64_t d = c.d_model, H = c.n_heads, V = c.vocab, T = c.max_seq_len, L = c.n_layers, R = nb * s;
+  const int prec = c.precision;
+  const float eps = c.eps;
+  const int64_t kv_off = b0 * H * T * 64;
+  if (int rc = launch_embed(ctx, ids_f32 ? ids_f32 + b0 * s : nullptr, ids_i64 ? ids_i64 + b0 * s : nullptr, c.wte, c.wpe,
+                            m->h, nb, s, n, d, V, T))
+    return rc;
+  for (int64_t l = 0; l < L; ++l) {
+    int rc = launch_layernorm(ctx, m->h, m->ln1_g[l], m->ln1_b[l], m->xn, R, d, eps);
+    if (!rc) rc = linear_any(ctx, m->attn_w[l], m->xn, m->attn_b[l], nullptr, CATEN_B200_ACT_NONE, m->qkv, R, prec);
+    if (!rc) rc = launch_attention(ctx, m->qkv, m->kc[l] + kv_off, m->vc[l] + kv_off, m->att, nb, s, n, H, T);
+    if (!rc) rc = linear_any(ctx, m->proj_w[l], m->att, m->proj_b[l], m->h, CATEN_B200_ACT_NONE, m->h2, R, prec);
+    if (!rc) rc = launch_layernorm(ctx, m->h2, m->ln2_g[l], m->ln2_b[l], m->xn, R, d, eps);
+    if (!rc) rc = linear_any(ctx, m->fc_w[l], m->xn, m->fc_b[l], nullptr, CATEN_B200_ACT_GELU, m->ff, R, prec);
+    if (!rc) rc = linear_any(ctx, m->mproj_w[l], m->ff, m->mproj_b[l], m->h2, CATEN_B200_ACT_NONE, m->h, R, prec);
+    if (rc) return rc;
+  }
+  // ln_f on the last position of every sequence only (the reference views the last row of the
+  // logits, layers.lisp:90), gathered into rows [b0, b0+nb) of `last`
+  return launch_layernorm_strided(ctx, m->h, c.lnf_g, c.lnf_b, m->last + b0 * d, nb, d, eps, s);
+}
+
+int caten_b200_gpt2_step_device(caten_b200_gpt2 *m, const float *d_ids_f32, const int64_t *d_ids_i64, int64_t s, int64_t n,
+                                int64_t *d_out_ids) {
+  if (!m) return fail(nullptr, CATEN_B200_EINVAL, "gpt2_step: model is NULL");
+  caten_b200_ctx *ctx = m->ctx;
+  cudaSetDevice(ctx->device);
+  const caten_b200_gpt2_desc &c = m->desc;
+  if ((d_ids_f32 == nullptr) == (d_ids_i64 == nullptr)) return fail(ctx, CATEN_B200_EINVAL, "gpt2_step: pass exactly one id array");
+  if (!d_out_ids) return fail(ctx, CATEN_B200_EINVAL, "gpt2_step: out ids is NULL");
+  if (s < 1 || n < 0 || n + s > c.max_seq_len)
+    return fail(ctx, CATEN_B200_EINVAL, "gpt2_step: s=%lld n=%lld outside the cache (max_seq_len=%d)", (long long)s, (long long)n, c.max_seq_len);
+  const int64_t B = c.batch;
+  int64_t per = m->max_rows / s;
+  if (per < 1) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gpt2_step: s=%lld exceeds max_rows=%lld", (long long)s, (long long)m->max_rows);
+  if (per > B) per = B;
+  for (int64_t b0 = 0; b0 < B; b0 += per) {
+    const int64_t nb = B - b0 < per ? B - b0 : per;
+    if (int rc = run_chunk(m, d_ids_f32, d_ids_i64, b0, nb, s, n)) return rc;
+  }
+  // lm_head (no bias, layers.lisp:79) + argmax over the vocabulary
+  if (int rc = linear_any(ctx, c.lm_head, m->last, nullptr, nullptr, CATEN_B200_ACT_NONE, m->logits, B, c.precision)) return rc;
+  return launch_argmax(ctx, m->logits, B, c.vocab, d_out_ids);
+}
+
+int caten_b200_gpt2_step(caten_b200_gpt2 *m, const float *h_ids_f32, int64_t s, int64_t n, int64_t *h_out_ids) {
+  if (!m) return fail(nullptr, CATEN_B200_EINVAL, "gpt2_step: model is NULL");
+  caten_b200_ctx *ctx = m->ctx;
+  cudaSetDevice(ctx->device);
+  const int64_t B = m->desc.batch;
+  if (!h_ids_f32 || !h_out_ids) return fail(ctx, CATEN_B200_EINVAL, "gpt2_step: NULL host buffer");
+  if (s < 1 || s > m->desc.max_seq_len) return fail(ctx, CATEN_B200_EINVAL, "gpt2_step: s=%lld", (long long)s);
+  memcpy(m->h_ids_pinned, h_ids_f32, (size_t)(B * s) * sizeof(float));
+  CB_CUDA(ctx, cudaMemcpyAsync(m->ids_f32, m->h_ids_pinned, (size_t)(B * s) * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+  if (int rc = caten_b200_gpt2_step_device(m, m->ids_f32, nullptr, s, n, m->out_ids)) return rc;
+  CB_CUDA(ctx, cudaMemcpyAsync(m->h_out_pinned, m->out_ids, (size_t)B * sizeof(int64_t), cudaMemcpyDeviceToHost, ctx->stream));
+  if (int rc = caten_b200_sync(ctx)) return rc;
+  memcpy(h_out_ids, m->h_out_pinned, (size_t)B * sizeof(int64_t));
+  return 0;
+}
+
+const float *caten_b200_gpt2_logits(caten_b200_gpt2 *m) { return m ? m->logits : nullptr; }
+
+int caten_b200_gpt2_kv(caten_b200_gpt2 *m, int layer, float **d_k, float **d_v) {
+  if (!m) return fail(nullptr, CATEN_B200_EINVAL, "gpt2_kv: model is NULL");
+  if (layer < 0 || layer >= m->desc.n_layers || !d_k || !d_v) return fail(m->ctx, CATEN_B200_EINVAL, "gpt2_kv: bad layer or NULL out pointer");
+  *d_k = m->kc[layer];
+  *d_v = m->vc[layer];
+  return 0;
+}
+
+int64_t caten_b200_gpt2_launch_count(caten_b200_gpt2 *m) { return m ? m->ctx->launches - m->launches0 : 0; }
+
+}  // extern "C"

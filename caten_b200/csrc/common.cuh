@@ -1,0 +1,125 @@
+// Shared declarations of libcaten_b200: context, weight storage, launch prototypes.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/caten_b200.h"
+
+namespace cb {
+
+// Device-side status word layout (ctx->d_status, 4 ints): [0] error code, [1..3] detail.
+enum DevErr : int { DEV_OK = 0, DEV_WAIT_TIMEOUT = 1, DEV_BAD_INDEX = 2 };
+
+struct Scratch {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+};
+
+}  // namespace cb
+
+struct caten_b200_ctx {
+  int device = 0;
+  int sm_count = 148;
+  cudaStream_t stream = nullptr;
+  std::string err;
+  int *d_status = nullptr;   // device status word written by kernels whose bounded waits run out
+  int *h_status = nullptr;   // pinned mirror
+  cb::Scratch xbf;           // bf16 copy (hi, lo) of the activation operand of the tensor-core GEMM
+  cb::Scratch wtmp;          // transposed/converted operand of relu_matmul
+  void *encode_tiled = nullptr;  // cuTensorMapEncodeTiled, resolved at init
+  int64_t launches = 0;
+};
+
+struct caten_b200_weight {
+  int type = 0;
+  int64_t rows = 0, cols = 0;
+  int64_t nkb = 0;          // blocks of 32 per row (quantised types)
+  void *qs = nullptr;       // F32: float[rows*cols]; F16: half[rows*cols]; Q8_0: int8[rows*nkb*32]; Q4_0: u8[rows*nkb*16]
+  __half *d = nullptr;      // per-block scales [rows*nkb] (quantised types)
+  caten_b200_ctx *ctx = nullptr;
+};
+
+namespace cb {
+
+int fail(caten_b200_ctx *ctx, int code, const char *fmt, ...);
+int cuda_fail(caten_b200_ctx *ctx, cudaError_t e, const char *what);
+int scratch_reserve(caten_b200_ctx *ctx, Scratch *s, size_t bytes);
+
+#define CB_CUDA(ctx, call)                                          \
+  do {                                                              \
+    cudaError_t e__ = (call);                                       \
+    if (e__ != cudaSuccess) return cb::cuda_fail((ctx), e__, #call); \
+  } while (0)
+#define CB_LAUNCH_CHECK(ctx, what)                                   \
+  do {                                                               \
+    cudaError_t e__ = cudaGetLastError();                            \
+    if (e__ != cudaSuccess) return cb::cuda_fail((ctx), e__, what);  \
+    (ctx)->launches++;                                               \
+  } while (0)
+
+// ---- launchers (each returns a status code; all asynchronous on ctx->stream) ----
+int launch_repack(caten_b200_ctx *ctx, int type, const uint8_t *d_blocks, int64_t nblocks, void *qs, __half *d);
+int launch_dequant(caten_b200_ctx *ctx, const caten_b200_weight *w, float *out);
+int launch_layernorm(caten_b200_ctx *ctx, const float *x, const float *g, const float *b, float *y,
+                     int64_t rows, int64_t d, float eps);
+// src_rows: optional gather — row r of the output reads row (r+1)*src_stride-1 of x when src_stride > 1
+int launch_layernorm_strided(caten_b200_ctx *ctx, const float *x, const float *g, const float *b, float *y,
+                             int64_t rows, int64_t d, float eps, int64_t src_stride);
+int launch_embed(caten_b200_ctx *ctx, const float *ids_f32, const int64_t *ids_i64, const float *wte,
+                 const float *wpe, float *out, int64_t B, int64_t s, int64_t n, int64_t d, int64_t V, int64_t T);
+int launch_argmax(caten_b200_ctx *ctx, const float *x, int64_t rows, int64_t V, int64_t *out);
+int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc, float *out, int64_t B,
+                     int64_t s, int64_t n, int64_t H, int64_t T);
+int launch_gemv(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
+                const float *res, int act, float *y);
+int launch_gemm_simt(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
+                     const float *res, int act, float *y, int64_t M);
+int launch_gemm_tc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
+                   const float *res, int act, float *y, int64_t M, int nsplit);
+// relu(a.b) with b given [K, N] row-major fp32
+int launch_relu_matmul_simt(caten_b200_ctx *ctx, const float *a, const float *b, float *c, int64_t M, int64_t K, int64_t N);
+int launch_relu_matmul_tc(caten_b200_ctx *ctx, const float *a, const float *b, float *c, int64_t M, int64_t K,
+                          int64_t N, int nsplit);
+
+// ---- device helpers ----
+
+// GeLU exactly as the reference composes it (source/nn/activations.lisp:202-204 with
+// tanh(z) = 2*sigmoid(2z) - 1 and sigmoid(y) = 1/(1 + exp2(y * -1/ln2))), every step in fp32.
+__device__ __forceinline__ float gelu_ref(float x) {
+  const float kC = 0.7978845608028654f, k044 = 0.044715f, kNegInvLn2 = -1.0f / 0.6931472f;
+  float x3 = x * x;
+  x3 = x3 * x;
+  float in = k044 * x3;
+  in = x + in;
+  const float z = kC * in;
+  float a = 2.0f * z;
+  a = a * kNegInvLn2;
+  float e = exp2f(a);
+  e = 1.0f + e;
+  const float sg = 1.0f / e;
+  float th = 2.0f * sg;
+  th = th + (-1.0f);
+  const float l = 0.5f * x;
+  const float r = 1.0f + th;
+  return l * r;
+}
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == CATEN_B200_ACT_GELU) return gelu_ref(v);
+  if (act == CATEN_B200_ACT_RELU) return v > 0.0f ? v : 0.0f;
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+}  // namespace cb

@@ -1,0 +1,273 @@
+// Dequant-GEMV for decode with one sequence: y[o] = act(sum_k x[k] * W[o,k] + bias[o]) + res[o]
+// (source/nn/linear.lisp:12-17 with M = 1).  HBM-bound: the packed weights are streamed once
+// with 128-bit loads and unpacked in registers; x lives in registers (quantised types) or
+// shared memory (fp32/fp16 weights).  fp32 accumulation throughout.
+#include "common.cuh"
+
+namespace cb {
+
+struct GemvArgs {
+  const void *qs;
+  const __half *d;
+  const float *x, *bias, *res;
+  float *y;
+  int act, N, nkb, G;
+};
+
+constexpr int GEMV_MAX_THREADS = 640;
+
+__device__ __forceinline__ uint4 ld_stream(const uint4 *p) { return __ldcs(p); }
+
+// ---- per-format block arithmetic -------------------------------------------------------------
+// A thread owns one 32-wide column block kb of x and walks down the rows of W.
+//
+// Q4_0.  A nibble masked in place inside its 32-bit word, `w & (0xF << p)`, reinterpreted as a
+// float, is the (sub)normal number nibble * 2^(p-149): the binary32 encoding is linear in its
+// integer bit pattern below 2^24.  So with x pre-multiplied by 2^(64-p) (a power of two: exact),
+// one AND plus one FMA accumulates x*nibble*2^-85 exactly as an fp32 FMA of x and nibble would,
+// with no shift, integer-to-float conversion or subtraction per weight.  The "-8" offset of
+// Q4_0 is folded into the accumulator's start value -8*sum(x)*2^-85, and 2^85 into the block
+// scale.  Nibbles of the top byte (bits 24..31 overlap the exponent field) are taken from
+// w >> 8.  Valid for |x| < 2^62; FMA with subnormal operands runs at full rate.
+struct BlkQ4 {
+  static constexpr int WORDS = 4;
+  float xs[32];
+  float c0;
+  __device__ __forceinline__ void prep(const float *xv) {
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) sum += xv[j];
+    c0 = sum * -0x1p-82f;  // -8 * 2^-85
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      xs[8 * i + 0] = xv[4 * i + 0] * 0x1p64f;        // byte 0 low  nibble, p = 0
+      xs[8 * i + 1] = xv[16 + 4 * i + 0] * 0x1p60f;   // byte 0 high nibble, p = 4
+      xs[8 * i + 2] = xv[4 * i + 1] * 0x1p56f;        // byte 1 low,  p = 8
+      xs[8 * i + 3] = xv[16 + 4 * i + 1] * 0x1p52f;   // byte 1 high, p = 12
+      xs[8 * i + 4] = xv[4 * i + 2] * 0x1p48f;        // byte 2 low,  p = 16
+      xs[8 * i + 5] = xv[16 + 4 * i + 2] * 0x1p44f;   // byte 2 high, p = 20
+      xs[8 * i + 6] = xv[4 * i + 3] * 0x1p48f;        // byte 3 low  (of w >> 8), p = 16
+      xs[8 * i + 7] = xv[16 + 4 * i + 3] * 0x1p44f;   // byte 3 high (of w >> 8), p = 20
+    }
+  }
+  __device__ __forceinline__ float dot(const uint32_t *w, float scale) const {
+    float a0 = c0, a1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t q = w[i], q8 = q >> 8;
+      a0 = fmaf(xs[8 * i + 0], __uint_as_float(q & 0x0000000Fu), a0);
+      a1 = fmaf(xs[8 * i + 1], __uint_as_float(q & 0x000000F0u), a1);
+      a0 = fmaf(xs[8 * i + 2], __uint_as_float(q & 0x00000F00u), a0);
+      a1 = fmaf(xs[8 * i + 3], __uint_as_float(q & 0x0000F000u), a1);
+      a0 = fmaf(xs[8 * i + 4], __uint_as_float(q & 0x000F0000u), a0);
+      a1 = fmaf(xs[8 * i + 5], __uint_as_float(q & 0x00F00000u), a1);
+      a0 = fmaf(xs[8 * i + 6], __uint_as_float(q8 & 0x000F0000u), a0);
+      a1 = fmaf(xs[8 * i + 7], __uint_as_float(q8 & 0x00F00000u), a1);
+    }
+    return (a0 + a1) * (scale * 0x1p85f);
+  }
+};
+
+// Q8_0: sign-extended byte -> float -> FMA; (float)q * scale is exact in fp32 (8 + 11 bits), so
+// scaling the 32-term sum once per block only changes where the roundings of the sum fall.
+struct BlkQ8 {
+  static constexpr int WORDS = 8;
+  float xs[32];
+  __device__ __forceinline__ void prep(const float *xv) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) xs[j] = xv[j];
+  }
+  __device__ __forceinline__ float dot(const uint32_t *w, float scale) const {
+    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t q = w[i];
+      a0 = fmaf(xs[4 * i + 0], (float)(int8_t)(q), a0);
+      a1 = fmaf(xs[4 * i + 1], (float)(int8_t)(q >> 8), a1);
+      a0 = fmaf(xs[4 * i + 2], (float)(int8_t)(q >> 16), a0);
+      a1 = fmaf(xs[4 * i + 3], (float)(int8_t)(q >> 24), a1);
+    }
+    return (a0 + a1) * scale;
+  }
+};
+
+// Thread t < G*nkb owns column block kb = t % nkb and row offset ro = t / nkb; a CTA iteration
+// covers G*RI consecutive rows (RI independent 16/32-byte loads in flight per thread).  The
+// per-(row, block) partial sums go through shared memory and are added in a fixed order (lane
+// strided, then a butterfly), so results do not depend on scheduling.
+template <class BLK, int RI>
+__global__ void __launch_bounds__(GEMV_MAX_THREADS) gemv_blocked_kernel(GemvArgs a) {
+  extern __shared__ float red[];
+  constexpr int W = BLK::WORDS;
+  const int tid = threadIdx.x, nkb = a.nkb, G = a.G;
+  const bool active = tid < G * nkb;
+  const int kb = active ? tid % nkb : 0, ro = active ? tid / nkb : 0;
+  BLK blk;
+  {
+    float xv[32];
+    const float4 *xp = reinterpret_cast<const float4 *>(a.x + (int64_t)kb * 32);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 v = xp[i];
+      xv[4 * i] = v.x; xv[4 * i + 1] = v.y; xv[4 * i + 2] = v.z; xv[4 * i + 3] = v.w;
+    }
+    blk.prep(xv);
+  }
+  const uint4 *qs = reinterpret_cast<const uint4 *>(a.qs);
+  const int rows_per_iter = G * RI;
+  const int warp = tid >> 5, lane = tid & 31, nwarps = (blockDim.x + 31) >> 5;
+  for (int64_t base = (int64_t)blockIdx.x * rows_per_iter; base < a.N; base += (int64_t)gridDim.x * rows_per_iter) {
+    uint32_t q[RI][W];
+    float sc[RI];
+#pragma unroll
+    for (int i = 0; i < RI; ++i) {
+      const int64_t row = base + i * G + ro;
+      const bool ok = active && row < a.N;
+      const int64_t bidx = row * nkb + kb;
+#pragma unroll
+      for (int j = 0; j < W / 4; ++j) {
+        const uint4 v = ok ? ld_stream(qs + bidx * (W / 4) + j) : make_uint4(0, 0, 0, 0);
+        q[i][4 * j] = v.x; q[i][4 * j + 1] = v.y; q[i][4 * j + 2] = v.z; q[i][4 * j + 3] = v.w;
+      }
+      sc[i] = ok ? __half2float(a.d[bidx]) : 0.0f;
+    }
+    if (active) {
+#pragma unroll
+      for (int i = 0; i < RI; ++i) red[(i * G + ro) * nkb + kb] = blk.dot(q[i], sc[i]);
+    }
+    __syncthreads();
+    for (int r = warp; r < rows_per_iter; r += nwarps) {
+      const int64_t row = base + r;
+      if (row >= a.N) break;
+      float s = 0.0f;
+      for (int k = lane; k < nkb; k += 32) s += red[r * nkb + k];
+      s = warp_sum(s);
+      if (lane == 0) {
+        if (a.bias) s = s + a.bias[row];
+        s = apply_act(s, a.act);
+        if (a.res) s = a.res[row] + s;
+        a.y[row] = s;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// fp32 / fp16 weights: one warp per row, RI rows in flight, x in shared memory.
+template <typename T> struct DenseLoad;
+template <> struct DenseLoad<float> {
+  static constexpr int VEC = 4;
+  __device__ static __forceinline__ void load(const float *p, float *o) {
+    const float4 v = __ldcs(reinterpret_cast<const float4 *>(p));
+    o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+  }
+};
+template <> struct DenseLoad<__half> {
+  static constexpr int VEC = 8;
+  __device__ static __forceinline__ void load(const __half *p, float *o) {
+    const uint4 v = __ldcs(reinterpret_cast<const uint4 *>(p));
+    const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      o[2 * i] = f.x; o[2 * i + 1] = f.y;
+    }
+  }
+};
+
+template <typename T, int RI>
+__global__ void __launch_bounds__(256) gemv_dense_kernel(const T *__restrict__ W, const float *__restrict__ x,
+                                                         const float *__restrict__ bias, const float *__restrict__ res,
+                                                         float *__restrict__ y, int act, int N, int K) {
+  extern __shared__ float xs[];
+  constexpr int VEC = DenseLoad<T>::VEC;
+  for (int i = threadIdx.x; i < K; i += blockDim.x) xs[i] = x[i];
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = K / VEC;
+  for (int64_t base = ((int64_t)blockIdx.x * 8 + warp) * RI; base < N; base += (int64_t)gridDim.x * 8 * RI) {
+    float acc[RI];
+#pragma unroll
+    for (int i = 0; i < RI; ++i) acc[i] = 0.0f;
+    for (int c = lane; c < nvec; c += 32) {
+      float wv[RI][VEC];
+#pragma unroll
+      for (int i = 0; i < RI; ++i) {
+        if (base + i < N) DenseLoad<T>::load(W + (base + i) * K + (int64_t)c * VEC, wv[i]);
+        else {
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) wv[i][j] = 0.0f;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float xv = xs[c * VEC + j];
+#pragma unroll
+        for (int i = 0; i < RI; ++i) acc[i] = fmaf(xv, wv[i][j], acc[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < RI; ++i) {
+      float s = warp_sum(acc[i]);
+      const int64_t row = base + i;
+      if (lane == 0 && row < N) {
+        if (bias) s = s + bias[row];
+        s = apply_act(s, act);
+        if (res) s = res[row] + s;
+        y[row] = s;
+      }
+    }
+  }
+}
+
+template <class BLK, int RI>
+static int launch_blocked(caten_b200_ctx *ctx, const GemvArgs &a) {
+  const int threads = ((a.G * a.nkb + 31) / 32) * 32;
+  const size_t smem = (size_t)a.G * RI * a.nkb * sizeof(float);
+  int occ = 1;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_blocked_kernel<BLK, RI>, threads, smem);
+  if (occ < 1) occ = 1;
+  const int64_t slabs = ((int64_t)a.N + a.G * RI - 1) / (a.G * RI);
+  int64_t grid = (int64_t)ctx->sm_count * occ;
+  if (grid > slabs) grid = slabs;
+  gemv_blocked_kernel<BLK, RI><<<(unsigned)grid, threads, smem, ctx->stream>>>(a);
+  CB_LAUNCH_CHECK(ctx, "gemv_blocked_kernel");
+  return 0;
+}
+
+int launch_gemv(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
+                const float *res, int act, float *y) {
+  if (w->rows > 0x7fffffff || w->cols > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv: dimension too large");
+  const int N = (int)w->rows, K = (int)w->cols;
+  if (w->type == CATEN_B200_Q4_0 || w->type == CATEN_B200_Q8_0) {
+    GemvArgs a;
+    a.qs = w->qs; a.d = w->d; a.x = x; a.bias = bias; a.res = res; a.y = y; a.act = act; a.N = N;
+    a.nkb = (int)w->nkb;
+    if (a.nkb > GEMV_MAX_THREADS) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv: cols=%d too wide (max %d)", K, GEMV_MAX_THREADS * 32);
+    a.G = GEMV_MAX_THREADS / a.nkb;
+    // few rows: keep every SM busy with single-row-group iterations; many rows: 4 loads in flight
+    const bool deep = (int64_t)N >= (int64_t)a.G * 4 * ctx->sm_count;
+    if (w->type == CATEN_B200_Q4_0) return deep ? launch_blocked<BlkQ4, 4>(ctx, a) : launch_blocked<BlkQ4, 1>(ctx, a);
+    return deep ? launch_blocked<BlkQ8, 4>(ctx, a) : launch_blocked<BlkQ8, 1>(ctx, a);
+  }
+  const size_t smem = (size_t)K * sizeof(float);
+  if (smem > 160 * 1024) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv: cols=%d too wide", K);
+  const int64_t groups = ((int64_t)N + 8 * 2 - 1) / (8 * 2);
+  int64_t grid = (int64_t)ctx->sm_count * 4;
+  if (grid > groups) grid = groups;
+  if (w->type == CATEN_B200_F32) {
+    if (K % 4) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv f32: cols %% 4 != 0");
+    if (smem > 48 * 1024) cudaFuncSetAttribute(gemv_dense_kernel<float, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gemv_dense_kernel<float, 2><<<(unsigned)grid, 256, smem, ctx->stream>>>((const float *)w->qs, x, bias, res, y, act, N, K);
+  } else if (w->type == CATEN_B200_F16) {
+    if (K % 8) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv f16: cols %% 8 != 0");
+    if (smem > 48 * 1024) cudaFuncSetAttribute(gemv_dense_kernel<__half, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gemv_dense_kernel<__half, 2><<<(unsigned)grid, 256, smem, ctx->stream>>>((const __half *)w->qs, x, bias, res, y, act, N, K);
+  } else {
+    return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv: weight type %d", w->type);
+  }
+  CB_LAUNCH_CHECK(ctx, "gemv_dense_kernel");
+  return 0;
+}
+
+}  // namespace cb

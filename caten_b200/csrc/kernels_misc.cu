@@ -1,0 +1,228 @@
+// Small HBM-bound kernels of the GPT-2 graph: weight re-layout and dequantisation, LayerNorm,
+// token+position embedding gather, arg-max.
+#include "common.cuh"
+
+namespace cb {
+
+// ---------------------------------------------------------------------------------------------
+// GGUF blocks -> (codes, scales) arrays.  Q8_0 block = fp16 scale + 32 int8 (34 B); Q4_0 block =
+// fp16 scale + 16 bytes of nibbles (18 B) (external/gguf/dequantize.lisp:40-53 reads the same
+// fields in the same order).  The bytes are copied unchanged; only their placement differs.
+// ---------------------------------------------------------------------------------------------
+template <int QBYTES>
+__global__ void repack_kernel(const uint8_t *__restrict__ src, int64_t nblocks, uint8_t *__restrict__ qs,
+                              __half *__restrict__ d) {
+  const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nblocks) return;
+  const uint8_t *p = src + b * (QBYTES + 2);
+  const uint16_t hs = (uint16_t)p[0] | ((uint16_t)p[1] << 8);
+  d[b] = __ushort_as_half(hs);
+  uint32_t w[QBYTES / 4];
+#pragma unroll
+  for (int i = 0; i < QBYTES / 4; ++i)
+    w[i] = (uint32_t)p[2 + 4 * i] | ((uint32_t)p[3 + 4 * i] << 8) | ((uint32_t)p[4 + 4 * i] << 16) |
+           ((uint32_t)p[5 + 4 * i] << 24);
+  uint4 *o = reinterpret_cast<uint4 *>(qs + b * QBYTES);
+#pragma unroll
+  for (int i = 0; i < QBYTES / 16; ++i) o[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+}
+
+int launch_repack(caten_b200_ctx *ctx, int type, const uint8_t *d_blocks, int64_t nblocks, void *qs, __half *d) {
+  const int threads = 256;
+  const int64_t grid = (nblocks + threads - 1) / threads;
+  if (grid > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "repack: too many blocks");
+  if (type == CATEN_B200_Q4_0)
+    repack_kernel<16><<<(unsigned)grid, threads, 0, ctx->stream>>>(d_blocks, nblocks, (uint8_t *)qs, d);
+  else
+    repack_kernel<32><<<(unsigned)grid, threads, 0, ctx->stream>>>(d_blocks, nblocks, (uint8_t *)qs, d);
+  CB_LAUNCH_CHECK(ctx, "repack_kernel");
+  return 0;
+}
+
+// w = (float)code * (float)scale, one rounded fp32 multiply (external/gguf/dequantize.lisp:51).
+__global__ void dequant_kernel(int type, const void *__restrict__ qs, const __half *__restrict__ d,
+                               int64_t n, float *__restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t blk = i >> 5;
+  const int j = (int)(i & 31);
+  if (type == CATEN_B200_F32) {
+    out[i] = ((const float *)qs)[i];
+  } else if (type == CATEN_B200_F16) {
+    out[i] = __half2float(((const __half *)qs)[i]);
+  } else if (type == CATEN_B200_Q8_0) {
+    const int q = ((const int8_t *)qs)[blk * 32 + j];
+    out[i] = (float)q * __half2float(d[blk]);
+  } else {
+    const uint8_t byte = ((const uint8_t *)qs)[blk * 16 + (j & 15)];
+    const int q = (j < 16 ? (byte & 0x0F) : (byte >> 4)) - 8;
+    out[i] = (float)q * __half2float(d[blk]);
+  }
+}
+
+int launch_dequant(caten_b200_ctx *ctx, const caten_b200_weight *w, float *out) {
+  const int64_t n = w->rows * w->cols;
+  const int threads = 256;
+  const int64_t grid = (n + threads - 1) / threads;
+  if (grid > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "dequant: tensor too large");
+  dequant_kernel<<<(unsigned)grid, threads, 0, ctx->stream>>>(w->type, w->qs, w->d, n, out);
+  CB_LAUNCH_CHECK(ctx, "dequant_kernel");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// LayerNorm (source/nn/normalization.lisp:48-58): u = sum(x)*(1/d); dl = x - u;
+// var = sum(dl*dl)*(1/d); y = dl * (1/sqrt(var+eps)) * gamma + beta.  One warp per row, the
+// row held in registers so x is read from HBM once.  d % 4 == 0, d <= 2048.
+// ---------------------------------------------------------------------------------------------
+constexpr int LN_MAXV = 16;  // float4 per lane
+
+__global__ void __launch_bounds__(128) layernorm_kernel(const float *__restrict__ x, const float *__restrict__ g,
+                                                        const float *__restrict__ b, float *__restrict__ y,
+                                                        int64_t rows, int d4, float invd, float eps,
+                                                        int64_t src_stride) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int64_t src_row = src_stride > 1 ? (row + 1) * src_stride - 1 : row;
+  const float4 *xr = reinterpret_cast<const float4 *>(x) + src_row * d4;
+  float4 v[LN_MAXV];
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < LN_MAXV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < d4) {
+      v[i] = xr[c];
+      sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+  }
+  sum = warp_sum(sum);
+  const float u = sum * invd;
+  float sq = 0.0f;
+#pragma unroll
+  for (int i = 0; i < LN_MAXV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < d4) {
+      v[i].x -= u; v[i].y -= u; v[i].z -= u; v[i].w -= u;
+      sq += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+    }
+  }
+  sq = warp_sum(sq);
+  const float var = sq * invd;
+  const float rs = 1.0f / sqrtf(var + eps);
+  const float4 *g4 = reinterpret_cast<const float4 *>(g), *b4 = reinterpret_cast<const float4 *>(b);
+  float4 *yr = reinterpret_cast<float4 *>(y) + row * d4;
+#pragma unroll
+  for (int i = 0; i < LN_MAXV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < d4) {
+      const float4 gg = g4[c], bb = b4[c];
+      float4 o;
+      o.x = (v[i].x * rs) * gg.x + bb.x;
+      o.y = (v[i].y * rs) * gg.y + bb.y;
+      o.z = (v[i].z * rs) * gg.z + bb.z;
+      o.w = (v[i].w * rs) * gg.w + bb.w;
+      yr[c] = o;
+    }
+  }
+}
+
+int launch_layernorm_strided(caten_b200_ctx *ctx, const float *x, const float *g, const float *b, float *y,
+                             int64_t rows, int64_t d, float eps, int64_t src_stride) {
+  if (rows <= 0) return 0;
+  if (d % 4 || d > 128 * LN_MAXV) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: d=%lld (need d%%4==0, d<=2048)", (long long)d);
+  const int64_t grid = (rows + 3) / 4;
+  layernorm_kernel<<<(unsigned)grid, 128, 0, ctx->stream>>>(x, g, b, y, rows, (int)(d / 4), 1.0f / (float)d, eps, src_stride);
+  CB_LAUNCH_CHECK(ctx, "layernorm_kernel");
+  return 0;
+}
+
+int launch_layernorm(caten_b200_ctx *ctx, const float *x, const float *g, const float *b, float *y, int64_t rows,
+                     int64_t d, float eps) {
+  return launch_layernorm_strided(ctx, x, g, b, y, rows, d, eps, 1);
+}
+
+// ---------------------------------------------------------------------------------------------
+// h[b,i,:] = wte[tok[b,i]] + wpe[n+i] (external/llm/layers.lisp:83-85).  The reference builds the
+// token embedding as sum_v where(v == tok, W[v,:], 0) (source/nn/embedding.lisp:17-25): an id that
+// matches no v contributes a zero row, which is kept here.
+// ---------------------------------------------------------------------------------------------
+__global__ void embed_kernel(const float *__restrict__ ids_f32, const int64_t *__restrict__ ids_i64,
+                             const float *__restrict__ wte, const float *__restrict__ wpe, float *__restrict__ out,
+                             int64_t s, int64_t n, int d4, int64_t V, int64_t T) {
+  const int64_t r = blockIdx.x;
+  int64_t tok = -1;
+  if (ids_i64) {
+    tok = ids_i64[r];
+  } else {
+    const float t = ids_f32[r];
+    if (t >= 0.0f && t < (float)V && truncf(t) == t) tok = (int64_t)t;
+  }
+  const bool has_tok = tok >= 0 && tok < V;
+  const int64_t pos = n + (r % s);
+  const bool has_pos = pos >= 0 && pos < T;
+  const float4 *te = reinterpret_cast<const float4 *>(wte) + (has_tok ? tok : 0) * d4;
+  const float4 *pe = reinterpret_cast<const float4 *>(wpe) + (has_pos ? pos : 0) * d4;
+  float4 *o = reinterpret_cast<float4 *>(out) + r * d4;
+  for (int c = threadIdx.x; c < d4; c += blockDim.x) {
+    float4 a = has_tok ? te[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 p = has_pos ? pe[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    a.x += p.x; a.y += p.y; a.z += p.z; a.w += p.w;
+    o[c] = a;
+  }
+}
+
+int launch_embed(caten_b200_ctx *ctx, const float *ids_f32, const int64_t *ids_i64, const float *wte,
+                 const float *wpe, float *out, int64_t B, int64_t s, int64_t n, int64_t d, int64_t V, int64_t T) {
+  if (B * s <= 0) return 0;
+  if (d % 4) return fail(ctx, CATEN_B200_EUNSUPPORTED, "embed: d %% 4 != 0");
+  if ((ids_f32 == nullptr) == (ids_i64 == nullptr)) return fail(ctx, CATEN_B200_EINVAL, "embed: pass exactly one id array");
+  embed_kernel<<<(unsigned)(B * s), 128, 0, ctx->stream>>>(ids_f32, ids_i64, wte, wpe, out, s, n, (int)(d / 4), V, T);
+  CB_LAUNCH_CHECK(ctx, "embed_kernel");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// arg-max with the reference's tie rule: the lowest index among the maxima
+// (source/api/high-level-ops.lisp:321-325).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ x, int64_t V, int64_t *__restrict__ out) {
+  const float *xr = x + (int64_t)blockIdx.x * V;
+  float best = -INFINITY;
+  int64_t bi = V;  // V = "nothing seen"
+  for (int64_t v = threadIdx.x; v < V; v += blockDim.x) {
+    const float f = xr[v];
+    if (f > best || bi == V) {
+      if (f > best || bi == V) { best = f; bi = v; }
+    }
+  }
+  __shared__ float sv[256];
+  __shared__ int64_t si[256];
+  sv[threadIdx.x] = best;
+  si[threadIdx.x] = bi;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) {
+      const float ov = sv[threadIdx.x + o];
+      const int64_t oi = si[threadIdx.x + o];
+      const float mv = sv[threadIdx.x];
+      const int64_t mi = si[threadIdx.x];
+      if (oi < V && (mi == V || ov > mv || (ov == mv && oi < mi))) {
+        sv[threadIdx.x] = ov;
+        si[threadIdx.x] = oi;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) out[blockIdx.x] = si[0] == V ? 0 : si[0];
+}
+
+int launch_argmax(caten_b200_ctx *ctx, const float *x, int64_t rows, int64_t V, int64_t *out) {
+  if (rows <= 0) return 0;
+  if (V <= 0) return fail(ctx, CATEN_B200_EINVAL, "argmax: V <= 0");
+  argmax_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(x, V, out);
+  CB_LAUNCH_CHECK(ctx, "argmax_kernel");
+  return 0;
+}
+
+}  // namespace cb

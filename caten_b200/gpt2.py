@@ -1,0 +1,170 @@
+"""GPT-2 on the B200 backend: the host-side counterpart of apps/gpt2/gpt2.lisp.
+
+``make_gpt2`` plays the role of `make-gpt2` (gpt2.lisp:82-93: build the Transformer, load the
+state dict, compile), ``GPT2.forward`` of ``(forward model (x . tokens) (s . len) (n . start-pos))``
+(gpt2.lisp:104) and ``gpt2_generate`` of `gpt2-generate` (gpt2.lisp:97-113) without the tokenizer:
+prompts are token ids.  Unlike the reference, whose compiled graph is fixed to batch 1
+(gpt2.lisp:93), ``batch`` independent sequences advance together.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import numpy as np
+
+from . import _lib as L
+from .runtime import B200Buffer, B200Runtime, B200Weight
+from .synthetic import GPT2_SIZES, GPT2Params, Packed
+
+_LINEAR_KEYS = ("attn.c_attn", "attn.c_proj", "mlp.c_fc", "mlp.c_proj")
+
+
+class GPT2:
+    def __init__(self, runtime: B200Runtime, params: GPT2Params, state_dict: dict, max_seq_len: int = 1024,
+                 batch: int = 1, precision: str = "fp32", max_rows: int = 0, device_blobs: Optional[dict] = None):
+        """``state_dict``: reference keys -> fp32 arrays, or :class:`Packed` for Linear weights.
+
+        ``device_blobs``: optional ``{key: device pointer}`` of raw GGUF blocks already resident on
+        this GPU (e.g. received through an NCCL broadcast); those entries of ``state_dict`` then
+        only need ``ggml_type/rows/cols`` and are not read from the host."""
+        self.rt, self.params, self.batch, self.max_seq_len = runtime, params, batch, max_seq_len
+        self.precision = L.PRECISIONS[precision] if isinstance(precision, str) else int(precision)
+        self._bufs, self._weights, self._keep = [], [], []
+        p, rt = params, runtime
+        Lr = p.n_layers
+
+        def f32(key) -> int:
+            b = rt.transfer_from_array(state_dict[key], np.float32)
+            self._bufs.append(b)
+            return b.ptr
+
+        def weight(key) -> int:
+            w = state_dict[key]
+            if device_blobs is not None and key in device_blobs:
+                h = rt.upload_weight_device(w.ggml_type, device_blobs[key], w.rows, w.cols)
+            else:
+                h = rt.upload_weight(w)
+            self._weights.append(h)
+            return h.handle
+
+        def parr(vals):
+            arr = (C.c_void_p * Lr)(*vals)
+            self._keep.append(arr)
+            return C.cast(arr, C.POINTER(C.c_void_p))
+
+        self.packed_bytes = 0
+        d = L.GPT2Desc()
+        d.n_layers, d.d_model, d.n_heads, d.vocab = p.n_layers, p.dim, p.n_heads, p.vocab_size
+        d.max_seq_len, d.batch, d.eps, d.precision, d.max_rows = max_seq_len, batch, p.norm_eps, self.precision, max_rows
+        d.wte, d.wpe = f32("wte.weight"), f32("wpe.weight")
+        d.lnf_g, d.lnf_b = f32("ln_f.affine"), f32("ln_f.bias")
+        d.lm_head = weight("lm_head.weight")
+        d.ln1_g = parr([f32(f"h.{l}.ln_1.affine") for l in range(Lr)])
+        d.ln1_b = parr([f32(f"h.{l}.ln_1.bias") for l in range(Lr)])
+        d.ln2_g = parr([f32(f"h.{l}.ln_2.affine") for l in range(Lr)])
+        d.ln2_b = parr([f32(f"h.{l}.ln_2.bias") for l in range(Lr)])
+        d.attn_b = parr([f32(f"h.{l}.attn.c_attn.bias") for l in range(Lr)])
+        d.proj_b = parr([f32(f"h.{l}.attn.c_proj.bias") for l in range(Lr)])
+        d.fc_b = parr([f32(f"h.{l}.mlp.c_fc.bias") for l in range(Lr)])
+        d.mproj_b = parr([f32(f"h.{l}.mlp.c_proj.bias") for l in range(Lr)])
+        d.attn_w = parr([weight(f"h.{l}.attn.c_attn.weight") for l in range(Lr)])
+        d.proj_w = parr([weight(f"h.{l}.attn.c_proj.weight") for l in range(Lr)])
+        d.fc_w = parr([weight(f"h.{l}.mlp.c_fc.weight") for l in range(Lr)])
+        d.mproj_w = parr([weight(f"h.{l}.mlp.c_proj.weight") for l in range(Lr)])
+        self.linear_weight_bytes = sum(w.packed_nbytes for w in self._weights)
+        self._desc = d
+        h = C.c_void_p()
+        L.check(rt.ctx, rt.lib.caten_b200_gpt2_create(rt.ctx, C.byref(d), C.byref(h)))
+        self._h = h
+        self._dev_ids = rt.open_buffer((2, batch), np.int64)  # ping-pong ids for device-resident decode
+
+    # -- one step from host ids: the call the reference's token loop makes --
+    def forward(self, x, s: Optional[int] = None, n: int = 0) -> np.ndarray:
+        """x: [batch, s] token ids (any numeric dtype; sent as float32 like gpt2.lisp:95).
+        Returns int64 [batch]: argmax of the logits at the last position."""
+        tok = np.ascontiguousarray(x, dtype=np.float32).reshape(self.batch, -1)
+        s = tok.shape[1] if s is None else int(s)
+        if s != tok.shape[1]:
+            raise ValueError("forward: s does not match x")
+        out = np.empty(self.batch, np.int64)
+        L.check(self.rt.ctx, self.rt.lib.caten_b200_gpt2_step(self._h, tok.ctypes.data, s, int(n), out.ctypes.data))
+        return out
+
+    # -- device-resident variants (ids never leave HBM) --
+    def forward_device(self, ids: B200Buffer, s: int, n: int, out: B200Buffer) -> None:
+        f32 = ids.ptr if ids.dtype == np.float32 else None
+        i64 = ids.ptr if ids.dtype == np.int64 else None
+        L.check(self.rt.ctx, self.rt.lib.caten_b200_gpt2_step_device(self._h, f32, i64, int(s), int(n), out.ptr))
+
+    def decode_device(self, first_ids: np.ndarray, start_pos: int, steps: int) -> np.ndarray:
+        """Greedy decode ``steps`` tokens with ids staying on the GPU; returns [batch, steps]."""
+        a = self._dev_ids.view(0, (self.batch, 1))
+        b = self._dev_ids.view(self.batch, (self.batch, 1))
+        ids0 = np.ascontiguousarray(first_ids, dtype=np.int64).reshape(self.batch)
+        L.check(self.rt.ctx, self.rt.lib.caten_b200_h2d(self.rt.ctx, a.ptr, ids0.ctypes.data, ids0.nbytes))
+        hist = self.rt.open_buffer((steps, self.batch), np.int64)
+        cur, nxt = a, b
+        for i in range(steps):
+            self.forward_device(cur, 1, start_pos + i, nxt)
+            L.check(self.rt.ctx, self.rt.lib.caten_b200_d2d(self.rt.ctx, hist.ptr + i * self.batch * 8, nxt.ptr, self.batch * 8))
+            cur, nxt = nxt, cur
+        out = hist.numpy().T.copy()
+        hist.close()
+        return out
+
+    def logits(self) -> np.ndarray:
+        """[batch, vocab] fp32 logits of the last step."""
+        ptr = self.rt.lib.caten_b200_gpt2_logits(self._h)
+        return B200Buffer(self.rt, ptr, (self.batch, self.params.vocab_size), np.float32, owned=False).numpy()
+
+    def kv_cache(self, layer: int):
+        """(k, v) of one layer as numpy arrays [batch, heads, max_seq_len, 64]."""
+        k, v = C.c_void_p(), C.c_void_p()
+        L.check(self.rt.ctx, self.rt.lib.caten_b200_gpt2_kv(self._h, layer, C.byref(k), C.byref(v)))
+        shp = (self.batch, self.params.n_heads, self.max_seq_len, 64)
+        return (B200Buffer(self.rt, k.value, shp, np.float32, owned=False).numpy(),
+                B200Buffer(self.rt, v.value, shp, np.float32, owned=False).numpy())
+
+    @property
+    def launch_count(self) -> int:
+        return int(self.rt.lib.caten_b200_gpt2_launch_count(self._h))
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self.rt.lib.caten_b200_gpt2_destroy(self._h)
+            self._h = None
+            for w in self._weights:
+                w.close()
+            for b in self._bufs:
+                b.close()
+            self._dev_ids.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def make_gpt2(model_type, state_dict: dict, runtime: Optional[B200Runtime] = None, max_seq_len: int = 1024,
+              batch: int = 1, precision: str = "fp32", **kw) -> GPT2:
+    """`make-gpt2` (apps/gpt2/gpt2.lisp:82-93). ``model_type``: "gpt2", "gpt2-medium", "gpt2-large",
+    "gpt2-xl" or a :class:`GPT2Params`."""
+    params = model_type if isinstance(model_type, GPT2Params) else GPT2_SIZES[str(model_type).lstrip(":")]
+    rt = runtime or B200Runtime(0)
+    return GPT2(rt, params, state_dict, max_seq_len=max_seq_len, batch=batch, precision=precision, **kw)
+
+
+def gpt2_generate(gpt2: GPT2, prompt_ids, max_length: int = 100) -> np.ndarray:
+    """`gpt2-generate` (apps/gpt2/gpt2.lisp:97-113) on token ids: the first call feeds the whole
+    prompt at start position 0, each later call one token; every call's argmax is appended.
+    Returns [batch, prompt_len + max_length] int64."""
+    tokens = np.ascontiguousarray(prompt_ids, dtype=np.int64).reshape(gpt2.batch, -1)
+    start_pos = 0
+    for _ in range(max_length):
+        in_tokens = tokens[:, start_pos:]
+        out = gpt2.forward(in_tokens, in_tokens.shape[1], start_pos)
+        start_pos = tokens.shape[1]
+        tokens = np.concatenate([tokens, out.reshape(-1, 1)], axis=1)
+    return tokens

@@ -71,42 +71,44 @@ def pack_q4_0(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
     return out.reshape(-1)
 
 
-def _rand_packed(rng: np.random.Generator, rows: int, cols: int, wtype: str) -> Packed:
+def _rand_packed(rng: np.random.Generator, rows: int, cols: int, wtype: str, std: float = 0.02) -> Packed:
     assert cols % 32 == 0
     nb = rows * (cols // 32)
     if wtype == "q8_0":
         # 32 int8 uniform in [-127, 127]; scale = |N(0, 0.02)| / 127
         codes = rng.integers(-127, 128, size=(nb, 32), dtype=np.int8)
-        scales = (np.abs(rng.standard_normal(nb, dtype=np.float32)) * np.float32(0.02 / 127)).astype(np.float16)
+        scales = (np.abs(rng.standard_normal(nb, dtype=np.float32)) * np.float32(std / 127)).astype(np.float16)
         return Packed(GGML_Q8_0, rows, cols, pack_q8_0(codes, scales))
     if wtype == "q4_0":
         # 32 4-bit codes uniform in [0, 15] (offset 8); scale = |N(0, 0.02)| / 8.  A uniform byte
         # is two independent uniform nibbles, so the quant bytes are drawn directly.
         out = np.empty((nb, 18), np.uint8)
         out[:, 2:] = rng.integers(0, 256, size=(nb, 16), dtype=np.uint8)
-        scales = (np.abs(rng.standard_normal(nb, dtype=np.float32)) * np.float32(0.02 / 8)).astype("<f2")
+        scales = (np.abs(rng.standard_normal(nb, dtype=np.float32)) * np.float32(std / 8)).astype("<f2")
         out[:, 0:2] = scales.reshape(nb, 1).view(np.uint8)
         return Packed(GGML_Q4_0, rows, cols, out.reshape(-1))
     raise ValueError(wtype)
 
 
 def synth_state_dict(p: GPT2Params, wtype: str = "f32", seed: int = 0, max_seq_len: int = 1024,
-                     trivial_affine: bool = True) -> dict:
+                     trivial_affine: bool = True, weight_std: float = 0.02) -> dict:
     """Draw order (fixed): wte, wpe, then per layer c_attn, attn.c_proj, mlp.c_fc, mlp.c_proj
     (weight, then bias/affine extras when ``trivial_affine`` is False), then lm_head.
 
     wtype "f32": every matrix ~ N(0, 0.02).  "q8_0"/"q4_0": the five kinds of Linear weight are
     packed blocks; embeddings, LayerNorm parameters and biases stay fp32.
     ``trivial_affine``: biases 0, LayerNorm gamma 1 / beta 0 (the benchmark configurations);
-    False draws them at random so tests exercise those terms."""
+    False draws them at random so tests exercise those terms.  ``weight_std`` scales the fp32
+    matrices and the quantisation scales (0.02 in the benchmark configurations; tests use a
+    larger value so that sequences and logits differ visibly)."""
     rng = np.random.Generator(np.random.PCG64(seed))
     d, L, V = p.dim, p.n_layers, p.vocab_size
 
     def normal(*shape):
-        return (rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02))
+        return (rng.standard_normal(shape, dtype=np.float32) * np.float32(weight_std))
 
     def lin(rows, cols):
-        return normal(rows, cols) if wtype == "f32" else _rand_packed(rng, rows, cols, wtype)
+        return normal(rows, cols) if wtype == "f32" else _rand_packed(rng, rows, cols, wtype, weight_std)
 
     def vec(n, base):
         if trivial_affine:

@@ -1,0 +1,184 @@
+/* libcaten_b200.so — C ABI of the B200 (sm_100a) backend for Caten's GPT-2 forward path.
+ *
+ * Callers: Common Lisp through CFFI (`cffi:foreign-funcall`, the way source/byoc/clang.lisp:197-205
+ * calls its gcc-built kernels) and the Python ctypes host in caten_b200/.  Plain pointers and
+ * sizes only; every function returns an int status (0 = ok) unless stated, and the message of
+ * the last failure is read with caten_b200_last_error().
+ *
+ * Conventions.  All activations are fp32, row-major.  A Linear weight is W[out, in] row-major
+ * and y = x.W^T + b (source/nn/linear.lisp:12-17).  Pointers named d_* are device pointers
+ * obtained from caten_b200_malloc (or any CUDA allocation of the context's device); pointers
+ * named h_* are host pointers.  Kernels are launched asynchronously on the context's stream;
+ * only the functions documented as synchronising wait for the GPU.  A context is driven by one
+ * host thread at a time (Caten's VM is single-threaded, source/runtime/runtime.lisp:106-145).
+ *
+ * Paths below are relative to the hikettei/Caten source tree.
+ */
+#ifndef CATEN_B200_H
+#define CATEN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct caten_b200_ctx caten_b200_ctx;
+typedef struct caten_b200_weight caten_b200_weight;
+typedef struct caten_b200_gpt2 caten_b200_gpt2;
+
+/* status codes */
+enum {
+  CATEN_B200_OK = 0,
+  CATEN_B200_EINVAL = 1,      /* bad argument (null handle, wrong size, misaligned pointer) */
+  CATEN_B200_ECUDA = 2,       /* a CUDA runtime/driver call failed */
+  CATEN_B200_EUNSUPPORTED = 3,/* shape or type outside what the kernels cover */
+  CATEN_B200_EDEVICE = 4      /* a kernel reported a failed internal check (e.g. a bounded wait ran out) */
+};
+
+/* ggml tensor type ids as stored in GGUF (external/gguf/tensor-info.lisp:3-34). */
+enum { CATEN_B200_F32 = 0, CATEN_B200_F16 = 1, CATEN_B200_Q4_0 = 2, CATEN_B200_Q8_0 = 8 };
+
+/* epilogue applied by the Linear kernels after the bias: the scheduler fuses the activation
+ * into the matmul kernel (source/test-suite/test-schedule.lisp:72-74). */
+enum { CATEN_B200_ACT_NONE = 0, CATEN_B200_ACT_GELU = 1, CATEN_B200_ACT_RELU = 2 };
+
+/* arithmetic of the Linear kernels when more than a few rows are multiplied at once:
+ *   FP32    fp32 operands and accumulation on the CUDA cores (max-abs 1e-3 logit class)
+ *   BF16    operands rounded to bf16, fp32 accumulation on tcgen05 tensor cores (rel 2e-2 class)
+ *   BF16X3  each operand split into two bf16 terms, three tensor-core products (about 2^-16 rel.)
+ * Single-row products (decode with one sequence) always run the fp32 dequant-GEMV. */
+enum { CATEN_B200_PREC_FP32 = 0, CATEN_B200_PREC_BF16 = 1, CATEN_B200_PREC_BF16X3 = 2 };
+
+/* ---- context, memory, transfers -------------------------------------------------------------
+ * Replaces, for BACKEND=B200, what a Caten backend supplies through define-backend
+ * (source/codegen/backend.lisp:22-34): the buffer generics open-buffer / close-buffer /
+ * transfer-from-array / transfer-into-array / copy-buffer-value (source/runtime/buffer.lisp:78-89). */
+
+/* Creates a context on CUDA device `device` with its own stream. */
+int caten_b200_init(int device, caten_b200_ctx **ctx);
+int caten_b200_destroy(caten_b200_ctx *ctx);
+/* Message of the last failed call on this context (or of the last failed call without a
+ * context when ctx is NULL). Never NULL. The pointer stays valid until the next failing call. */
+const char *caten_b200_last_error(caten_b200_ctx *ctx);
+/* open-buffer: zero-filled device allocation (source/runtime/buffer.lisp:79). */
+int caten_b200_malloc(caten_b200_ctx *ctx, size_t bytes, void **d_ptr);
+/* close-buffer. */
+int caten_b200_free(caten_b200_ctx *ctx, void *d_ptr);
+/* transfer-from-array: host -> device, ordered on the context's stream; returns after the host
+ * buffer may be reused. */
+int caten_b200_h2d(caten_b200_ctx *ctx, void *d_dst, const void *h_src, size_t bytes);
+/* transfer-into-array / bref: device -> host; synchronises. */
+int caten_b200_d2h(caten_b200_ctx *ctx, void *h_dst, const void *d_src, size_t bytes);
+/* copy-buffer-value: device -> device. */
+int caten_b200_d2d(caten_b200_ctx *ctx, void *d_dst, const void *d_src, size_t bytes);
+int caten_b200_memset(caten_b200_ctx *ctx, void *d_dst, int byte, size_t bytes);
+/* Waits for all work queued on the context and reports kernel-side check failures. */
+int caten_b200_sync(caten_b200_ctx *ctx);
+/* The context's cudaStream_t, for callers that time or order work themselves. */
+void *caten_b200_stream(caten_b200_ctx *ctx);
+
+/* ---- weights ----------------------------------------------------------------------------------
+ * Replaces external/gguf/tensor-info.lisp:71-77,104-120 + external/gguf/dequantize.lisp:14-53,
+ * which dequantise every tensor to a fp32 Lisp array at load: here the raw GGUF blocks are
+ * uploaded as they are in the file and stay packed in HBM (Q8_0: 34-byte blocks, Q4_0: 18-byte
+ * blocks; on the device codes and fp16 scales are kept in two arrays so code loads are 16-byte
+ * aligned — same bytes, same values). `cols` (the `in` dimension) must be a multiple of 32 for
+ * the quantised types. */
+int caten_b200_weight_upload(caten_b200_ctx *ctx, int ggml_type, const void *h_blocks, int64_t rows,
+                             int64_t cols, caten_b200_weight **w);
+/* Same, from raw blocks already in device memory (e.g. after an NCCL broadcast of the file's
+ * tensor data). The blocks are re-laid out into storage owned by the handle; d_blocks may be
+ * freed after the call returns and the stream is synchronised. */
+int caten_b200_weight_upload_device(caten_b200_ctx *ctx, int ggml_type, const void *d_blocks,
+                                    int64_t rows, int64_t cols, caten_b200_weight **w);
+int caten_b200_weight_free(caten_b200_ctx *ctx, caten_b200_weight *w);
+/* Number of bytes of a rows x cols tensor in GGUF block form; -1 for an unknown type. */
+int64_t caten_b200_weight_nbytes(int ggml_type, int64_t rows, int64_t cols);
+/* dequantize (external/gguf/dequantize.lisp:8): writes rows*cols fp32 values, bit-identical to
+ * (float)code * (float)scale, to d_out. */
+int caten_b200_weight_dequant(caten_b200_ctx *ctx, const caten_b200_weight *w, float *d_out);
+
+/* ---- kernels of the GPT-2 graph -----------------------------------------------------------------
+ * One entry per fused kernel the scheduler produces for external/llm/layers.lisp
+ * ([Embedding_Embedding_ADD] [LayerNorm] [Matmul+GELU] [Attention], source/codegen/jit.lisp:8);
+ * these are what the :b200 renderer's compiled lambdas call in place of the C functions
+ * CLANG emits (source/byoc/clang.lisp:163-205). */
+
+/* Linear (source/nn/linear.lisp:12-17; api/high-level-ops.lisp:76-99):
+ *   y[m, o] = act(sum_k x[m,k] * W[o,k] + bias[o]) + residual[m, o]
+ * x [M, cols], y [M, rows]; d_bias [rows] or NULL; d_residual [M, rows] or NULL (may alias y).
+ * M == 1..4 runs the dequant-GEMV; larger M runs the GEMM selected by `precision`. */
+int caten_b200_linear(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *d_x,
+                      const float *d_bias, const float *d_residual, int act, float *d_y, int64_t M,
+                      int precision);
+/* `(!relu (!matmul a b))` with a [M,K] and b [K,N], both row-major fp32 (Readme.md:55-60):
+ * c = max(a.b, 0).  precision as above (FP32 or BF16X3 keep the reference's 1e-5 tolerance). */
+int caten_b200_relu_matmul(caten_b200_ctx *ctx, const float *d_a, const float *d_b, float *d_c,
+                           int64_t M, int64_t K, int64_t N, int precision);
+/* LayerNorm over the last axis (source/nn/normalization.lisp:48-58). x, y [rows, d]. */
+int caten_b200_layernorm(caten_b200_ctx *ctx, const float *d_x, const float *d_gamma,
+                         const float *d_beta, float *d_y, int64_t rows, int64_t d, float eps);
+/* h = wte(tokens) + wpe(n + arange(s)) (external/llm/layers.lisp:83-85, nn/embedding.lisp:13-25).
+ * Exactly one of d_ids_f32 (what apps/gpt2/gpt2.lisp:95 feeds) and d_ids_i64 (what argmax
+ * writes) is non-NULL; both are [B, s]. An id that is not an integer in [0, V) selects no row
+ * (the one-hot compare of the reference matches nothing): its token embedding is zero. */
+int caten_b200_embed(caten_b200_ctx *ctx, const float *d_ids_f32, const int64_t *d_ids_i64,
+                     const float *d_wte, const float *d_wpe, float *d_out, int64_t B, int64_t s,
+                     int64_t n, int64_t d, int64_t V, int64_t T);
+/* Attention core of external/llm/layers.lisp:19-51 for head dim 64: appends this step's K and V
+ * rows (columns [d,2d) and [2d,3d) of qkv) at positions [n, n+s) of the caches, then
+ * out = softmax(q.K^T * 0.125 + causal mask) . V over positions [0, n+s).
+ * qkv [B*s, 3d]; out [B*s, d]; caches are [B, H, T, 64] fp32 (head-major so one head's history
+ * is contiguous; the reference's [B, T, H, 64] holds the same values). */
+int caten_b200_attention(caten_b200_ctx *ctx, const float *d_qkv, float *d_kcache, float *d_vcache,
+                         float *d_out, int64_t B, int64_t s, int64_t n, int64_t H, int64_t T);
+/* argmax over the last axis, lowest index on ties (api/high-level-ops.lisp:314-343). */
+int caten_b200_argmax(caten_b200_ctx *ctx, const float *d_x, int64_t rows, int64_t V, int64_t *d_out);
+
+/* ---- whole GPT-2 step ---------------------------------------------------------------------------
+ * Replaces one `(forward runtime (x . tokens) (s . len) (n . start-pos))` of
+ * apps/gpt2/gpt2.lisp:104 on the GraphRuntime built by make-gpt2 (gpt2.lisp:82-93): the whole
+ * kernel sequence of source/runtime/runtime.lisp:106-145 in one call. */
+typedef struct {
+  int32_t n_layers, d_model, n_heads, vocab, max_seq_len, batch;
+  float eps;
+  int32_t precision;      /* CATEN_B200_PREC_* for steps with more than 4 rows */
+  int32_t max_rows;       /* rows (sequences x tokens) processed at once in prefill; 0 = default */
+  /* fp32 device arrays (not owned): */
+  const float *wte, *wpe, *lnf_g, *lnf_b;
+  const caten_b200_weight *lm_head;
+  /* per layer, arrays of n_layers entries (host arrays of device pointers / handles): */
+  const float *const *ln1_g, *const *ln1_b, *const *attn_b, *const *proj_b;
+  const float *const *ln2_g, *const *ln2_b, *const *fc_b, *const *mproj_b;
+  const caten_b200_weight *const *attn_w, *const *proj_w, *const *fc_w, *const *mproj_w;
+} caten_b200_gpt2_desc;
+
+/* Allocates the KV caches ([B, H, T, 64] per layer, zero-filled as layers.lisp:25-26 does) and
+ * the activation workspace. Weights stay owned by the caller and must outlive the model. */
+int caten_b200_gpt2_create(caten_b200_ctx *ctx, const caten_b200_gpt2_desc *desc, caten_b200_gpt2 **m);
+int caten_b200_gpt2_destroy(caten_b200_gpt2 *m);
+/* One step from host buffers: h_ids_f32 [B, s] token ids as float32, start position n;
+ * h_out_ids [B] int64 = argmax of the last position's logits. Copies in, runs, copies out,
+ * synchronises. */
+int caten_b200_gpt2_step(caten_b200_gpt2 *m, const float *h_ids_f32, int64_t s, int64_t n,
+                         int64_t *h_out_ids);
+/* Same with device-resident ids: exactly one of d_ids_f32 / d_ids_i64 is non-NULL; d_out_ids
+ * [B] int64 (may be the next step's d_ids_i64). Asynchronous. */
+int caten_b200_gpt2_step_device(caten_b200_gpt2 *m, const float *d_ids_f32, const int64_t *d_ids_i64,
+                                int64_t s, int64_t n, int64_t *d_out_ids);
+/* Device pointer to the [B, V] fp32 logits of the last step (valid until the next step). */
+const float *caten_b200_gpt2_logits(caten_b200_gpt2 *m);
+/* Device pointers to layer l's caches, [B, H, T, 64] fp32. */
+int caten_b200_gpt2_kv(caten_b200_gpt2 *m, int layer, float **d_k, float **d_v);
+/* Number of kernel launches issued by this model's steps since creation. */
+int64_t caten_b200_gpt2_launch_count(caten_b200_gpt2 *m);
+
+/* Library build id (sm architecture it was compiled for), e.g. "sm_100a". */
+const char *caten_b200_arch(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,168 @@
+"""GPU parity tests of the whole GPT-2 step (prefill + KV-cached greedy decode) through the
+C ABI, against the CPU oracle, on the same seeded synthetic weights."""
+import numpy as np
+import pytest
+
+from caten_b200 import synthetic as S
+from caten_b200._lib import B200Error
+from caten_b200.gpt2 import GPT2, gpt2_generate, make_gpt2
+
+pytestmark = pytest.mark.gpu
+
+
+def dequantised(oracle, sd):
+    out = {}
+    for k, v in sd.items():
+        out[k] = oracle.dequant(v.ggml_type, v.data, v.rows * v.cols).reshape(v.rows, v.cols) if isinstance(v, S.Packed) else v
+    return out
+
+
+def comparable_rows(l32, lmix, l64, margin=8.0):
+    """Rows whose greedy id is decided by more than rounding: all three oracle variants agree and
+    the float64 top-2 gap exceeds `margin` x the largest disagreement between the variants."""
+    spread = max(np.abs(l32 - l64).max(), np.abs(lmix - l64).max(), 1e-7)
+    top2 = np.sort(l64, axis=1)[:, -2:]
+    gap = top2[:, 1] - top2[:, 0]
+    agree = (l32.argmax(1) == l64.argmax(1)) & (lmix.argmax(1) == l64.argmax(1))
+    return agree & (gap > margin * spread)
+
+
+def run_parity(rt, oracle, p, wtype, precision, B, prompt_len, steps, T, logit_tol, seed=3, rel=False):
+    sd = S.synth_state_dict(p, wtype, seed=seed, max_seq_len=T, trivial_affine=False, weight_std=0.08)
+    fsd = dequantised(oracle, sd)
+    prompt = S.synth_prompts(B, prompt_len, p.vocab_size, seed=seed + 1)
+    orcs = [oracle.GPT2(p.n_layers, p.dim, p.n_heads, p.vocab_size, T, B, fsd, eps=p.norm_eps, mode=m) for m in (0, 1, 2)]
+    g = GPT2(rt, p, sd, max_seq_len=T, batch=B, precision=precision)
+    tokens, pos, checked, total = prompt, 0, 0, 0
+    for step in range(steps):
+        s = tokens.shape[1] - pos
+        res = [o.step(tokens[:, pos:], pos) for o in orcs]
+        ids = g.forward(tokens[:, pos:], s, pos)
+        logits = g.logits()
+        l32, lmix, l64 = (r[1] for r in res)
+        err = np.abs(logits - l32).max()
+        bound = logit_tol * (np.abs(l32).max() if rel else 1.0)
+        assert err <= bound, f"step {step}: logits differ by {err} (bound {bound})"
+        ok = comparable_rows(l32, lmix, l64)
+        np.testing.assert_array_equal(ids[ok], res[0][0][ok])
+        np.testing.assert_array_equal(ids, logits.argmax(1))  # the kernel's argmax agrees with its own logits
+        checked += int(ok.sum()); total += B
+        pos = tokens.shape[1]
+        tokens = np.concatenate([tokens, res[0][0].reshape(-1, 1)], axis=1)  # teacher forcing on the oracle's ids
+    assert checked >= total // 2, "too few rows had a decisive top-2 gap; enlarge weight_std"
+    # the KV cache holds what the oracle's holds (device layout [B,H,T,64], oracle [B,T,H,64])
+    k_dev, v_dev = g.kv_cache(p.n_layers - 1)
+    g.close()
+    for o in orcs:
+        o.close()
+    return k_dev, v_dev
+
+
+TINY = S.GPT2Params(n_layers=2, n_heads=2, dim=128, vocab_size=1003)
+
+
+@pytest.mark.parametrize("wtype", ["f32", "q8_0", "q4_0"])
+def test_tiny_fp32_parity(rt, oracle, wtype):
+    # logits: max-abs 1e-3 (fp32 accumulate); greedy ids identical wherever rounding cannot decide
+    run_parity(rt, oracle, TINY, wtype, "fp32", B=3, prompt_len=9, steps=7, T=48, logit_tol=1e-3)
+
+
+@pytest.mark.parametrize("wtype", ["f32", "q4_0"])
+def test_tiny_single_sequence_uses_gemv(rt, oracle, wtype):
+    run_parity(rt, oracle, TINY, wtype, "fp32", B=1, prompt_len=3, steps=8, T=32, logit_tol=1e-3)
+
+
+@pytest.mark.parametrize("wtype", ["q8_0", "q4_0"])
+def test_tiny_bf16x3_parity(rt, oracle, wtype):
+    run_parity(rt, oracle, TINY, wtype, "bf16x3", B=6, prompt_len=9, steps=5, T=48, logit_tol=1e-3)
+
+
+@pytest.mark.parametrize("wtype", ["f32", "q4_0"])
+def test_tiny_bf16_parity(rt, oracle, wtype):
+    # bf16 tensor-core class: relative 2e-2
+    run_parity(rt, oracle, TINY, wtype, "bf16", B=6, prompt_len=9, steps=4, T=48, logit_tol=2e-2, rel=True)
+
+
+def test_gpt2_small_width_one_layer(rt, oracle):
+    """Real GPT-2 small widths (d=768, 12 heads, d_ff=3072), one layer, reduced vocabulary."""
+    p = S.GPT2Params(n_layers=1, n_heads=12, dim=768, vocab_size=4099)
+    run_parity(rt, oracle, p, "q8_0", "fp32", B=2, prompt_len=16, steps=4, T=64, logit_tol=1e-3)
+
+
+def test_gpt2_xl_width_one_layer(rt, oracle):
+    """GPT-2 XL widths (d=1600, 25 heads: rows of 900 / 1700 packed bytes), one layer."""
+    p = S.GPT2Params(n_layers=1, n_heads=25, dim=1600, vocab_size=2053)
+    run_parity(rt, oracle, p, "q4_0", "fp32", B=1, prompt_len=5, steps=3, T=32, logit_tol=1e-3)
+
+
+def test_golden_fixture_float64_torch(rt, golden):
+    """Against the committed float64 PyTorch run (tests/golden/gpt2_tiny_f64.npz)."""
+    g = golden["gpt2_tiny_f64"]
+    sd = S.synth_state_dict(TINY, "f32", seed=int(g["seed"]), max_seq_len=int(g["max_seq_len"]), trivial_affine=False,
+                            weight_std=float(g["weight_std"]))
+    m = GPT2(rt, TINY, sd, max_seq_len=int(g["max_seq_len"]), batch=g["prompt"].shape[0], precision="fp32")
+    toks = gpt2_generate(m, g["prompt"], max_length=g["new_ids"].shape[1])
+    np.testing.assert_array_equal(toks[:, g["prompt"].shape[1]:], g["new_ids"])
+    np.testing.assert_allclose(m.logits(), g["logits"][-1], atol=1e-3, rtol=0)
+    m.close()
+
+
+def test_device_resident_decode_matches_host_loop(rt):
+    sd = S.synth_state_dict(TINY, "q4_0", seed=5, max_seq_len=40, trivial_affine=False, weight_std=0.08)
+    prompt = S.synth_prompts(2, 6, TINY.vocab_size, seed=2)
+    a = GPT2(rt, TINY, sd, max_seq_len=40, batch=2)
+    toks = gpt2_generate(a, prompt, max_length=10)
+    b = GPT2(rt, TINY, sd, max_seq_len=40, batch=2)
+    first = b.forward(prompt, 6, 0)
+    rest = b.decode_device(first, 6, 9)
+    np.testing.assert_array_equal(np.concatenate([first.reshape(-1, 1), rest], 1), toks[:, 6:])
+    assert b.launch_count > 0
+    a.close(); b.close()
+
+
+def test_prefill_in_chunks_equals_one_pass(rt):
+    """max_rows forces the prefill to run sequence group by sequence group."""
+    sd = S.synth_state_dict(TINY, "q8_0", seed=6, max_seq_len=32, trivial_affine=False, weight_std=0.08)
+    prompt = S.synth_prompts(5, 8, TINY.vocab_size, seed=3)
+    a = GPT2(rt, TINY, sd, max_seq_len=32, batch=5)
+    b = GPT2(rt, TINY, sd, max_seq_len=32, batch=5, max_rows=16)  # two sequences at a time
+    ia, ib = a.forward(prompt, 8, 0), b.forward(prompt, 8, 0)
+    np.testing.assert_array_equal(ia, ib)
+    np.testing.assert_array_equal(a.logits(), b.logits())
+    a.close(); b.close()
+
+
+def test_chunked_prompt_equals_whole_prompt(rt):
+    """Feeding the prompt in two calls (n = 0 then n = 5) fills the cache like one call does."""
+    sd = S.synth_state_dict(TINY, "f32", seed=7, max_seq_len=32, trivial_affine=False, weight_std=0.08)
+    prompt = S.synth_prompts(2, 11, TINY.vocab_size, seed=4)
+    a = GPT2(rt, TINY, sd, max_seq_len=32, batch=2)
+    b = GPT2(rt, TINY, sd, max_seq_len=32, batch=2)
+    a.forward(prompt, 11, 0)
+    b.forward(prompt[:, :5], 5, 0)
+    b.forward(prompt[:, 5:], 6, 5)
+    np.testing.assert_allclose(a.logits(), b.logits(), atol=1e-5, rtol=0)
+    ka, _ = a.kv_cache(1)
+    kb, _ = b.kv_cache(1)
+    np.testing.assert_allclose(ka[:, :, :11], kb[:, :, :11], atol=1e-5, rtol=0)
+    assert not ka[:, :, 11:].any()  # untouched positions stay zero (layers.lisp:25-26)
+    a.close(); b.close()
+
+
+def test_step_errors(rt):
+    sd = S.synth_state_dict(TINY, "f32", seed=8, max_seq_len=16)
+    m = GPT2(rt, TINY, sd, max_seq_len=16, batch=1)
+    with pytest.raises(B200Error):
+        m.forward(np.zeros((1, 17)), 17, 0)       # longer than the cache
+    with pytest.raises(B200Error):
+        m.forward(np.zeros((1, 4)), 4, 14)        # runs past the end
+    m.forward(np.zeros((1, 4)), 4, 0)             # still usable afterwards
+    m.close()
+    bad = S.GPT2Params(n_layers=1, n_heads=4, dim=128, vocab_size=50)  # head dim 32
+    with pytest.raises(B200Error):
+        GPT2(rt, bad, S.synth_state_dict(bad, "f32", seed=0, max_seq_len=8), max_seq_len=8)
+
+
+def test_make_gpt2_by_name(rt):
+    with pytest.raises(KeyError):
+        make_gpt2("gpt3", {}, runtime=rt)

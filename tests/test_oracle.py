@@ -1,0 +1,164 @@
+"""CPU tests of the oracle: pinned against the golden fixtures (made by tests/golden/make_golden.py
+from the Python `gguf` package and PyTorch, the reference test-suite's own oracles) with the
+tolerances the reference's tests use."""
+import numpy as np
+import pytest
+
+from caten_b200 import synthetic as S
+
+
+def test_dequant_arange_fixture(oracle, golden):
+    # source/test-suite/external/test-gguf.lisp:53-75 (atol 1e-5); here the match is exact
+    g = golden["gguf_dequant"]
+    for name, t in (("f32", 0), ("f16", 1), ("q8_0", 8)):
+        got = oracle.dequant(t, g[f"arange_{name}_raw"], 64)
+        np.testing.assert_array_equal(got, g[f"arange_{name}"])
+
+
+@pytest.mark.parametrize("name,t", [("q4_0", 2), ("q8_0", 8)])
+def test_dequant_random_blocks_bit_exact(oracle, golden, name, t):
+    g = golden["gguf_dequant"]
+    want = g[f"rand_{name}"]
+    got = oracle.dequant(t, g[f"rand_{name}_raw"], want.size).reshape(want.shape)
+    np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_dequant_q4_0_scale_edge_cases(oracle, golden):
+    g = golden["gguf_dequant"]
+    got = oracle.dequant(2, g["edge_q4_0_raw"], g["edge_q4_0"].size).reshape(g["edge_q4_0"].shape)
+    np.testing.assert_array_equal(got.view(np.uint32), g["edge_q4_0"].view(np.uint32))
+
+
+def test_half_to_float_all_bit_patterns(oracle):
+    h = np.arange(65536, dtype=np.uint16)
+    want = h.view(np.float16).astype(np.float32)
+    got = np.array([oracle.half_to_float(int(x)) for x in h], dtype=np.float32)
+    ok = ~np.isnan(want)
+    np.testing.assert_array_equal(got.view(np.uint32)[ok], want.view(np.uint32)[ok])
+    assert np.isnan(got[~ok]).all()
+
+
+def test_dequant_rejects_unknown(oracle):
+    with pytest.raises(ValueError):
+        oracle.dequant(12, np.zeros(64, np.uint8), 32)
+    with pytest.raises(ValueError):
+        oracle.dequant(2, np.zeros(18, np.uint8), 17)  # Q4_0 needs whole blocks
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_matmul_vs_torch(oracle, golden, mode):
+    # test-gemm.lisp:3-22: atol 1e-5 / rtol 1e-5 against torch.matmul
+    g = golden["torch_ops"]
+    c = oracle.linear(g["mm_a"], np.ascontiguousarray(g["mm_b"].T), mode=mode)
+    np.testing.assert_allclose(c, g["mm_c"], atol=1e-5, rtol=1e-5)
+    r = oracle.relu_matmul(g["mm_a"], g["mm_b"], mode=mode)
+    np.testing.assert_allclose(r, g["relu_mm_c"], atol=1e-5, rtol=1e-5)
+    assert (r >= 0).all()
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_layernorm_vs_torch(oracle, golden, mode):
+    # test-normalization.lisp:48-55: atol 1e-5 / rtol 1e-2
+    g = golden["torch_ops"]
+    y = oracle.layernorm(g["ln_x"], g["ln_g"], g["ln_b"], mode=mode)
+    np.testing.assert_allclose(y, g["ln_y"], atol=1e-5, rtol=1e-2)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_gelu_vs_torch(oracle, golden, mode):
+    # test-activations.lisp:176-184 compares with the tanh formula at 1e-6 for inputs in [-1, 1);
+    # the fixture spans |x| up to ~15, where values reach ~15, hence the relative part
+    g = golden["torch_ops"]
+    np.testing.assert_allclose(oracle.gelu(g["gelu_x"], mode=mode), g["gelu_y"], atol=2e-6, rtol=2e-6)
+
+
+def _sdpa_via_oracle(oracle, q, k, v, causal, mode):
+    # q,k,v [B,H,T,64] -> the oracle's fused qkv rows / [B,T,H,hd] cache protocol, prefill of T tokens
+    B, H, T, hd = q.shape
+    d = H * hd
+    qkv = np.concatenate([x.transpose(0, 2, 1, 3).reshape(B * T, d) for x in (q, k, v)], axis=1)
+    kc = np.zeros((B, T, H, hd), np.float32)
+    vc = np.zeros_like(kc)
+    if causal:
+        o = oracle.attention(qkv, kc, vc, B, T, 0, H, mode=mode)
+    else:  # one query at a time against the full cache: decode protocol, no future to mask
+        oracle.attention(qkv, kc, vc, B, T, 0, H, mode=mode)
+        o = np.empty((B * T, d), np.float32)
+        for i in range(T):
+            kc2, vc2 = kc.copy(), vc.copy()
+            # move row i to the end so that the query at position T-1 sees every key
+            perm = [j for j in range(T) if j != i] + [i]
+            kc2, vc2 = np.ascontiguousarray(kc2[:, perm]), np.ascontiguousarray(vc2[:, perm])
+            row = qkv.reshape(B, T, 3 * d)[:, i]
+            o.reshape(B, T, d)[:, i] = oracle.attention(row, kc2, vc2, B, 1, T - 1, H, mode=mode)
+    return o.reshape(B, T, H, hd).transpose(0, 2, 1, 3)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_sdpa_vs_torch(oracle, golden, mode):
+    # test-llm.lisp:28-62: atol 1e-5 / rtol 1e-5
+    g = golden["torch_ops"]
+    o = _sdpa_via_oracle(oracle, g["sdpa_q"], g["sdpa_k"], g["sdpa_v"], True, mode)
+    np.testing.assert_allclose(o, g["sdpa_causal_o"], atol=1e-5, rtol=1e-5)
+    o = _sdpa_via_oracle(oracle, g["sdpa_q"], g["sdpa_k"], g["sdpa_v"], False, mode)
+    np.testing.assert_allclose(o, g["sdpa_o"], atol=1e-5, rtol=1e-5)
+
+
+def test_argmax_first_index_on_ties(oracle):
+    x = np.zeros((3, 10), np.float32)
+    x[0, [4, 7]] = 2.0
+    x[1, :] = -1.0
+    x[2, 9] = 5.0
+    np.testing.assert_array_equal(oracle.argmax(x), [4, 0, 9])
+
+
+def test_embedding_ignores_ids_outside_vocab(oracle):
+    # the one-hot compare of nn/embedding.lisp:17-25 matches nothing: zero token row + position row
+    wte = np.arange(12, dtype=np.float32).reshape(4, 3) + 1
+    wpe = np.full((5, 3), 100.0, np.float32)
+    out = oracle.embedding(np.array([[2, 7, -1, 1.5]], np.float32), 1, wte, wpe)
+    np.testing.assert_array_equal(out[0, 0], wte[2] + 100)
+    for i in (1, 2, 3):
+        np.testing.assert_array_equal(out[0, i], [100, 100, 100])
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_gpt2_tiny_vs_torch_f64(oracle, golden, mode):
+    """Whole model, prefill then cached decode, against an uncached float64 PyTorch forward."""
+    g = golden["gpt2_tiny_f64"]
+    p = S.GPT2Params(n_layers=2, n_heads=2, dim=128, vocab_size=1003)
+    sd = S.synth_state_dict(p, "f32", seed=int(g["seed"]), max_seq_len=int(g["max_seq_len"]), trivial_affine=False,
+                            weight_std=float(g["weight_std"]))
+    prompt = g["prompt"]
+    m = oracle.GPT2(p.n_layers, p.dim, p.n_heads, p.vocab_size, int(g["max_seq_len"]), prompt.shape[0], sd, mode=mode)
+    ids, logits = m.step(prompt, 0)
+    pos = prompt.shape[1]
+    for i in range(g["new_ids"].shape[1]):
+        np.testing.assert_allclose(logits, g["logits"][i], atol=1e-3 if mode < 2 else 1e-6, rtol=0)
+        np.testing.assert_array_equal(ids, g["new_ids"][:, i])
+        ids, logits = m.step(ids.reshape(-1, 1), pos)
+        pos += 1
+    m.close()
+
+
+def test_gpt2_rejects_positions_outside_cache(oracle):
+    p = S.GPT2Params(n_layers=1, n_heads=1, dim=64, vocab_size=50)
+    sd = S.synth_state_dict(p, "f32", seed=0, max_seq_len=8)
+    m = oracle.GPT2(1, 64, 1, 50, 8, 1, sd)
+    with pytest.raises(ValueError):
+        m.step(np.zeros((1, 9)), 0)
+    m.close()
+
+
+def test_variants_agree_to_rounding(oracle):
+    """The three numeric variants differ by rounding only (the spread that decides whether a
+    greedy id is comparable at all)."""
+    p = S.GPT2Params(n_layers=2, n_heads=2, dim=128, vocab_size=257)
+    sd = S.synth_state_dict(p, "f32", seed=9, max_seq_len=32, trivial_affine=False, weight_std=0.08)
+    toks = S.synth_prompts(2, 12, 257, seed=1)
+    lg = []
+    for mode in (0, 1, 2):
+        m = oracle.GPT2(2, 128, 2, 257, 32, 2, sd, mode=mode)
+        lg.append(m.step(toks, 0)[1])
+        m.close()
+    assert np.abs(lg[0] - lg[2]).max() < 1e-4 and np.abs(lg[1] - lg[2]).max() < 1e-4
