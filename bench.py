@@ -1,0 +1,377 @@
+"""Benchmark of the GPT-2 decode path on B200 (one process per GPU).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--workload xl-q4_0-b256|medium-q4_0-b64|small-q8_0-b1|small-f32-b1] [--precision bf16x3|bf16|fp32]
+
+A "step" is one KV-cached greedy decode step of the whole batch (one new token per sequence).
+Default workload: GPT-2 XL, Q4_0 weights, 256 sequences, 512-token prompts, fp32 KV cache, batch
+sharded over the N GPUs with replicated weights (strong scaling).  Prints ONE JSON line on rank 0.
+
+* ``value``  decode tokens/s with token ids resident in HBM (CUDA events on the library's stream,
+             barrier + synchronize on both sides, max over ranks).
+* ``e2e``    the same steps through ``GPT2.forward`` (the call of apps/gpt2/gpt2.lisp:104): host
+             ids in (pinned H2D) and host ids out (D2H) inside every timed step.
+* ``roofline``  attention-decode kernel (the dominant one: the KV cache is re-read every step),
+             algorithmic bytes = 2 * t * d_model * 4 B per sequence per layer, timed live with
+             CUDA events around its launches inside the timed region.
+* ``cpu_baseline``  the CPU oracle (restatement of BACKEND=CLANG's arithmetic, one thread as the
+             reference runs) on a bounded sample; ``--impl reference`` times the same code with
+             every host thread.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (model, weight type, total batch, prompt length, decode length)
+    "xl-q4_0-b256": ("gpt2-xl", "q4_0", 256, 512, 256),
+    "medium-q4_0-b64": ("gpt2-medium", "q4_0", 64, 128, 128),
+    "small-q8_0-b1": ("gpt2", "q8_0", 1, 128, 256),
+    "small-f32-b1": ("gpt2", "f32", 1, 16, 100),
+}
+METRIC = "gpt2_decode_tokens_per_s"
+BPW = {"f32": 4.0, "q8_0": 34 / 32, "q4_0": 18 / 32}
+
+
+def load_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    except Exception:
+        return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.path = tempfile.mktemp(suffix=".csv")
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(device), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        # the first samples may precede the load; the median of the upper half reflects the timed region
+        top = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(top) if top else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_decode_sample(params, sd, context: int, steps: int, threads: int, budget_s: float):
+    """Times the CPU oracle on `steps` decode steps of ONE sequence at a context of `context`
+    tokens (KV cache pre-filled with a value pattern: its contents do not change the work)."""
+    import oracle as O
+    from caten_b200 import synthetic as S
+    O.build()
+    fsd = {k: (O.dequant(v.ggml_type, v.data, v.rows * v.cols).reshape(v.rows, v.cols) if isinstance(v, S.Packed) else v)
+           for k, v in sd.items()}
+    T = context + steps + 2
+    fsd["wpe.weight"] = fsd["wpe.weight"][:T] if fsd["wpe.weight"].shape[0] >= T else fsd["wpe.weight"]
+    steps = max(1, min(steps, fsd["wpe.weight"].shape[0] - context - 1))
+    O.set_threads(threads)
+    m = O.GPT2(params.n_layers, params.dim, params.n_heads, params.vocab_size, fsd["wpe.weight"].shape[0], 1, fsd)
+    m.fill_cache(0.01)
+    ids = np.zeros((1, 1), np.float32)
+    m.step(ids, context - 1, want_logits=False)  # warm the caches / page in the weights
+    done, t0 = 0, time.perf_counter()
+    for i in range(steps):
+        out, _ = m.step(ids, context + i, want_logits=False)
+        ids = out.reshape(1, 1).astype(np.float32)
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    m.close()
+    O.set_threads(1)
+    return done / dt, done, dt
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="xl-q4_0-b256", choices=sorted(WORKLOADS))
+    ap.add_argument("--precision", default="bf16x3", choices=["fp32", "bf16", "bf16x3"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the prefill/GEMV/kernel-breakdown side measurements")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    model_name, wtype, batch, prompt_len, decode_len = WORKLOADS[args.workload]
+    W = max(0, args.warmup)
+    K = args.steps if args.steps is not None else max(1, min(64, decode_len - W - 1))
+    if W + K > decode_len:
+        K = max(1, decode_len - W)
+    T = prompt_len + decode_len
+
+    from caten_b200 import synthetic as S
+    params = S.GPT2_SIZES[model_name]
+    config = {"workload": f"{model_name} {wtype} batch {batch} prompt {prompt_len} decode", "model_dims": f"L{params.n_layers} d{params.dim} H{params.n_heads} V{params.vocab_size}",
+              "kv_cache": f"fp32 [B,H,{T},64] per layer", "weights_seed": 0, "prompt_seed": 0}
+
+    # ------------------------------------------------------------------ reference arm (CPU)
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        sd = S.synth_state_dict(params, wtype, seed=0, max_seq_len=T)
+        import oracle as O
+        threads = O.max_threads()
+        ctx_len = prompt_len + decode_len // 2
+        tps, done, dt = cpu_decode_sample(params, sd, ctx_len, K, threads, budget_s=150.0)
+        line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": done, "warmup": 1,
+                "ms_per_step": 1000.0 * dt / done, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                 "sample": f"{done} decode steps of 1 sequence at context {ctx_len}, KV cache pre-filled, OpenMP over output rows"},
+                "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    # ------------------------------------------------------------------ B200 arm
+    import torch
+    import torch.distributed as dist
+    from caten_b200 import dist as D
+    from caten_b200.gpt2 import GPT2
+    from caten_b200.runtime import B200Runtime
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    b0, nb = D.shard_batch(batch, world, rank)
+    if nb < 1:
+        raise SystemExit("more ranks than sequences")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    rt = B200Runtime(local_rank)
+    sd = S.synth_state_dict(params, wtype, seed=0, max_seq_len=T) if rank == 0 else None
+    if world > 1:
+        arena, index = D.broadcast_state_dict(sd, dev)   # NCCL broadcast of the packed weights at load
+        stubs, ptrs = D.device_views(arena, index)
+        torch.cuda.synchronize()
+        model = GPT2(rt, params, stubs, max_seq_len=T, batch=nb, precision=args.precision, device_blobs=ptrs)
+        rt.sync()
+        del arena
+    else:
+        model = GPT2(rt, params, sd, max_seq_len=T, batch=nb, precision=args.precision)
+    prompts = S.synth_prompts(batch, prompt_len, params.vocab_size, seed=0)[b0:b0 + nb]
+    ext = torch.cuda.ExternalStream(rt.stream, device=dev)
+
+    def ev():
+        e = torch.cuda.Event(enable_timing=True)
+        e.record(ext)
+        return e
+
+    # ---- prefill (fills the cache; timed on the side)
+    ids_dev = rt.transfer_from_array(prompts.astype(np.float32))
+    a = model._dev_ids.view(0, (nb, 1))
+    b = model._dev_ids.view(nb, (nb, 1))
+    first = rt.open_buffer((nb,), np.int64)
+    rt.sync(); barrier()
+    e0 = ev()
+    model.forward_device(ids_dev, prompt_len, 0, first)
+    e1 = ev()
+    rt.sync()
+    prefill_ms = max_over_ranks(e0.elapsed_time(e1))
+    first_ids = first.numpy()
+
+    def run_device_steps(n_start, count, cur, nxt, hist=None, h0=0):
+        for i in range(count):
+            model.forward_device(cur, 1, n_start + i, nxt)
+            if hist is not None:
+                rt.lib.caten_b200_d2d(rt.ctx, hist.ptr + (h0 + i) * nb * 8, nxt.ptr, nb * 8)
+            cur, nxt = nxt, cur
+        return cur, nxt
+
+    # ---- timed region 1: device-resident decode
+    hist = rt.open_buffer((W + K, nb), np.int64)
+    rt.lib.caten_b200_h2d(rt.ctx, a.ptr, first_ids.ctypes.data, first_ids.nbytes)
+    cur, nxt = run_device_steps(prompt_len, W, a, b, hist, 0)
+    rt.sync(); barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = model.launch_count
+    rt.profile_begin(["attn_decode"])
+    torch.cuda.synchronize(); barrier()
+    e0 = ev()
+    cur, nxt = run_device_steps(prompt_len + W, K, cur, nxt, hist, W)
+    e1 = ev()
+    rt.sync(); torch.cuda.synchronize(); barrier()
+    dec_ms = max_over_ranks(e0.elapsed_time(e1))
+    prof = rt.profile_end()
+    clocks = sampler.stop() if sampler else None
+    launches = model.launch_count - launches0
+    ids_device_path = hist.numpy()
+    value = batch * K / (dec_ms / 1e3)
+
+    # roofline of the attention-decode kernel: average context over the timed steps
+    attn_ms, attn_calls = prof.get("attn_decode", (0.0, 0))
+    t_mean = prompt_len + W + (K - 1) / 2.0 + 1            # keys read per step incl. the new one
+    attn_bytes = nb * 2 * t_mean * params.dim * 4.0        # per launch (one layer), K and V rows once
+    peak, peak_src = load_peaks()
+    attn_avg_s = (attn_ms / attn_calls / 1e3) if attn_calls else float("nan")
+    achieved = attn_bytes / attn_avg_s / 1e9 if attn_calls else None
+    roofline = {"bound": "hbm", "kernel": "attn_decode_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": (achieved / peak) if achieved else None, "traffic": None, "peak_source": peak_src,
+                "bytes_per_launch": attn_bytes, "avg_launch_us": attn_avg_s * 1e6, "launches_timed": attn_calls,
+                "share_of_step": (attn_ms / (dec_ms)) if dec_ms else None}
+    # whole-step algorithmic bytes (weights once + KV read + small terms), for context
+    d, Ln, V = params.dim, params.n_layers, params.vocab_size
+    p_lin = 12 * d * d * Ln + V * d
+    step_bytes = p_lin * BPW[wtype] + 4 * (13 * d * Ln + 2 * d) + nb * (2 * d * 4 + Ln * 2 * t_mean * d * 4 + Ln * 2 * d * 4 + 8)
+    step_frac = step_bytes / (dec_ms / K / 1e3) / 1e9 / peak
+
+    # ---- timed region 2: the public host API, host ids in / out every step
+    tok = first_ids.reshape(nb, 1)
+    for i in range(W):
+        tok = model.forward(tok, 1, prompt_len + i).reshape(nb, 1)
+    rt.sync(); barrier()
+    t0 = time.perf_counter()
+    e2e_ids = []
+    for i in range(K):
+        tok = model.forward(tok, 1, prompt_len + W + i).reshape(nb, 1)
+        e2e_ids.append(tok[:, 0].copy())
+    rt.sync(); barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    e2e = {"value": batch * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": nb * 4 * world, "d2h_bytes_per_step": nb * 8 * world,
+           "ms_per_step": 1000.0 * e2e_s / K, "timer": "host wall clock between barrier+synchronize pairs, max over ranks"}
+    same_ids = bool((np.stack(e2e_ids) == ids_device_path[W:]).all())
+
+    # gather the generated ids on all ranks (the only collective after load)
+    if world > 1:
+        gathered = D.gather_ids(torch.from_numpy(ids_device_path).to(dev), batch, world)
+        assert gathered.shape == (W + K, batch)
+
+    extras = {}
+    if not args.no_extras:
+        # per-class breakdown of a few decode steps (all classes timed; not part of `value`)
+        rt.lib.caten_b200_h2d(rt.ctx, a.ptr, first_ids.ctypes.data, first_ids.nbytes)
+        rt.profile_begin(None)
+        run_device_steps(prompt_len + W, min(K, 8), a, b)
+        br = rt.profile_end()
+        tot = sum(v[0] for v in br.values()) or 1.0
+        extras["kernel_ms_share"] = {k: round(v[0] / tot, 4) for k, v in br.items()}
+        extras["prefill"] = {"tokens_per_s": sum_over_ranks(nb * prompt_len) / (prefill_ms / 1e3), "ms": prefill_ms,
+                             "tokens": batch * prompt_len}
+        if rank == 0 and wtype != "f32":
+            # dequant-GEMV on the model's own matrices, cycling over all layers so the weights
+            # (hundreds of MB in total) do not stay in the 126 MB L2
+            x1 = rt.open_buffer((1, 4 * d))
+            res = {}
+            for kind, rows, cols in (("attn.c_attn", 3 * d, d), ("attn.c_proj", d, d), ("mlp.c_fc", 4 * d, d), ("mlp.c_proj", d, 4 * d)):
+                ws = [model.weights[f"h.{l}.{kind}.weight"] for l in range(Ln)]
+                y = rt.open_buffer((1, rows))
+                xin = x1.view(0, (1, cols))
+                for w in ws:
+                    rt.linear(w, xin, out=y)
+                rt.sync()
+                s0 = ev()
+                for _ in range(3):
+                    for w in ws:
+                        rt.linear(w, xin, out=y)
+                s1 = ev()
+                rt.sync()
+                per = s0.elapsed_time(s1) / (3 * len(ws)) / 1e3
+                nbytes = ws[0].packed_nbytes
+                res[f"{rows}x{cols}"] = {"GB/s": nbytes / per / 1e9, "frac_of_peak": nbytes / per / 1e9 / peak, "us": per * 1e6}
+            w = model.weights["lm_head.weight"]
+            y = rt.open_buffer((1, V)); xin = x1.view(0, (1, d))
+            rt.linear(w, xin, out=y); rt.sync()
+            s0 = ev()
+            for _ in range(10):
+                rt.linear(w, xin, out=y)
+            s1 = ev(); rt.sync()
+            per = s0.elapsed_time(s1) / 10 / 1e3
+            res[f"{V}x{d}"] = {"GB/s": w.packed_nbytes / per / 1e9, "frac_of_peak": w.packed_nbytes / per / 1e9 / peak, "us": per * 1e6,
+                               "note": "45 MB matrix re-read from L2-resident state is possible; see DESIGN.md"}
+            extras["dequant_gemv"] = res
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        ctx_len = prompt_len + decode_len // 2
+        tps, done, dt = cpu_decode_sample(params, sd, ctx_len, 6, 1, budget_s=30.0)
+        cpu = {"value": tps, "unit": "tokens/s", "cores": 1, "kind": "port",
+               "sample": f"{done} decode steps of 1 sequence at context {ctx_len} (KV cache pre-filled), {dt:.1f} s; "
+                         "BACKEND=CLANG executes its kernels on one thread"}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": dec_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f32 (attention, LayerNorm, accumulation); linears " + {"fp32": "f32", "bf16": "bf16 operands", "bf16x3": "split-bf16 operands (3 products)"}[args.precision] + " on tcgen05",
+                "data": "synthetic",
+                "config": {**config, "parallelism": f"batch-sharded x{world}, weights replicated", "local_batch": nb, "precision": args.precision,
+                           "context_tokens": [prompt_len + W + 1, prompt_len + W + K],
+                           "l2": "inputs larger than L2: every step re-reads the whole KV cache and all weights (>= hundreds of MB)"},
+                "roofline": roofline, "whole_step": {"algorithmic_bytes": step_bytes, "frac_of_hbm_peak": step_frac},
+                "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+                "ids_host_path_equal_device_path": same_ids, **extras}
+        print(json.dumps(line))
+    model.close()
+    rt.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -16,6 +16,8 @@ OK, EINVAL, ECUDA, EUNSUPPORTED, EDEVICE = 0, 1, 2, 3, 4
 F32, F16, Q4_0, Q8_0 = 0, 1, 2, 8
 ACT_NONE, ACT_GELU, ACT_RELU = 0, 1, 2
 PREC_FP32, PREC_BF16, PREC_BF16X3 = 0, 1, 2
+K_EMBED, K_LAYERNORM, K_GEMV, K_GEMM, K_ATTN_DECODE, K_ATTN_PREFILL, K_ARGMAX, K_COUNT = 0, 1, 2, 3, 4, 5, 6, 8
+KERNEL_CLASSES = ["embed", "layernorm", "gemv", "gemm", "attn_decode", "attn_prefill", "argmax", "other"]
 PRECISIONS = {"fp32": PREC_FP32, "bf16": PREC_BF16, "bf16x3": PREC_BF16X3}
 
 
@@ -74,6 +76,8 @@ SIGNATURES = {
     "caten_b200_gpt2_logits": (_vp, [_vp]),
     "caten_b200_gpt2_kv": (C.c_int, [_vp, C.c_int, _PFP, _PFP]),
     "caten_b200_gpt2_launch_count": (_i64, [_vp]),
+    "caten_b200_profile_begin": (C.c_int, [_vp, C.c_uint]),
+    "caten_b200_profile_end": (C.c_int, [_vp, _vp, _vp]),
     "caten_b200_arch": (C.c_char_p, []),
 }
 

@@ -49,6 +49,29 @@ static int check_status(caten_b200_ctx *ctx) {
   return 0;
 }
 
+// Brackets one kernel-class call with events when that class is being profiled.
+struct ProfScope {
+  caten_b200_ctx *ctx;
+  cudaEvent_t b = nullptr;
+  ProfScope(caten_b200_ctx *c, int klass) : ctx(c) {
+    if (!(ctx->prof_mask & (1u << klass))) return;
+    cudaEvent_t a;
+    auto get = [&]() {
+      cudaEvent_t e;
+      if (!ctx->prof_pool.empty()) { e = ctx->prof_pool.back(); ctx->prof_pool.pop_back(); }
+      else cudaEventCreate(&e);
+      return e;
+    };
+    a = get();
+    b = get();
+    cudaEventRecord(a, ctx->stream);
+    ctx->prof.push_back({klass, a, b});
+  }
+  ~ProfScope() {
+    if (b) cudaEventRecord(b, ctx->stream);
+  }
+};
+
 }  // namespace cb
 
 using namespace cb;
@@ -100,6 +123,8 @@ int caten_b200_destroy(caten_b200_ctx *ctx) {
   if (!ctx) return 0;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  for (auto &r : ctx->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+  for (auto e : ctx->prof_pool) cudaEventDestroy(e);
   if (ctx->xbf.ptr) cudaFree(ctx->xbf.ptr);
   if (ctx->wtmp.ptr) cudaFree(ctx->wtmp.ptr);
   cudaFree(ctx->d_status);
@@ -160,6 +185,30 @@ int caten_b200_sync(caten_b200_ctx *ctx) {
   CB_CUDA(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, 4 * sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
   CB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return check_status(ctx);
+}
+
+int caten_b200_profile_begin(caten_b200_ctx *ctx, unsigned class_mask) {
+  NEED_CTX(ctx);
+  for (auto &r : ctx->prof) { ctx->prof_pool.push_back(r.a); ctx->prof_pool.push_back(r.b); }
+  ctx->prof.clear();
+  ctx->prof_mask = class_mask;
+  return 0;
+}
+
+int caten_b200_profile_end(caten_b200_ctx *ctx, double *ms, int64_t *calls) {
+  NEED_CTX(ctx);
+  ctx->prof_mask = 0;
+  if (!ms || !calls) return fail(ctx, CATEN_B200_EINVAL, "profile_end: NULL output");
+  for (int i = 0; i < CATEN_B200_K_COUNT; ++i) { ms[i] = 0.0; calls[i] = 0; }
+  CB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  for (auto &r : ctx->prof) {
+    float t = 0.0f;
+    if (cudaEventElapsedTime(&t, r.a, r.b) == cudaSuccess) { ms[r.klass] += t; calls[r.klass]++; }
+    ctx->prof_pool.push_back(r.a);
+    ctx->prof_pool.push_back(r.b);
+  }
+  ctx->prof.clear();
+  return 0;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -253,6 +302,7 @@ int caten_b200_linear(caten_b200_ctx *ctx, const caten_b200_weight *w, const flo
   if (M == 0) return 0;
   if (act < 0 || act > 2) return fail(ctx, CATEN_B200_EINVAL, "linear: unknown activation %d", act);
   if (!aligned16(d_x) || !aligned16(d_y)) return fail(ctx, CATEN_B200_EINVAL, "linear: x and y must be 16-byte aligned");
+  ProfScope prof(ctx, M <= 4 ? CATEN_B200_K_GEMV : CATEN_B200_K_GEMM);
   if (M <= 4) {
     for (int64_t m = 0; m < M; ++m)
       if (int rc = launch_gemv(ctx, w, d_x + m * w->cols, d_bias, d_residual ? d_residual + m * w->rows : nullptr, act,
@@ -273,6 +323,7 @@ int caten_b200_relu_matmul(caten_b200_ctx *ctx, const float *d_a, const float *d
   NEED_CTX(ctx);
   if (!d_a || !d_b || !d_c) return fail(ctx, CATEN_B200_EINVAL, "relu_matmul: NULL argument");
   if (M < 0 || K <= 0 || N < 0) return fail(ctx, CATEN_B200_EINVAL, "relu_matmul: bad shape");
+  ProfScope prof(ctx, CATEN_B200_K_GEMM);
   switch (precision) {
     case CATEN_B200_PREC_FP32: return launch_relu_matmul_simt(ctx, d_a, d_b, d_c, M, K, N);
     case CATEN_B200_PREC_BF16: return launch_relu_matmul_tc(ctx, d_a, d_b, d_c, M, K, N, 1);
@@ -302,6 +353,7 @@ int caten_b200_attention(caten_b200_ctx *ctx, const float *d_qkv, float *d_kcach
   NEED_CTX(ctx);
   if (!d_qkv || !d_kcache || !d_vcache || !d_out) return fail(ctx, CATEN_B200_EINVAL, "attention: NULL argument");
   if (B < 0 || s < 0 || H <= 0 || T <= 0) return fail(ctx, CATEN_B200_EINVAL, "attention: bad shape");
+  ProfScope prof(ctx, s == 1 ? CATEN_B200_K_ATTN_DECODE : CATEN_B200_K_ATTN_PREFILL);
   return launch_attention(ctx, d_qkv, d_kcache, d_vcache, d_out, B, s, n, H, T);
 }
 
@@ -421,21 +473,26 @@ static int run_chunk(caten_b200_gpt2 *m, const float *ids_f32, const int64_t *id
   const int prec = c.precision;
   const float eps = c.eps;
   const int64_t kv_off = b0 * H * T * 64;
-  if (int rc = launch_embed(ctx, ids_f32 ? ids_f32 + b0 * s : nullptr, ids_i64 ? ids_i64 + b0 * s : nullptr, c.wte, c.wpe,
-                            m->h, nb, s, n, d, V, T))
-    return rc;
+  {
+    ProfScope prof(ctx, CATEN_B200_K_EMBED);
+    if (int rc = launch_embed(ctx, ids_f32 ? ids_f32 + b0 * s : nullptr, ids_i64 ? ids_i64 + b0 * s : nullptr, c.wte, c.wpe,
+                              m->h, nb, s, n, d, V, T))
+      return rc;
+  }
   for (int64_t l = 0; l < L; ++l) {
-    int rc = launch_layernorm(ctx, m->h, m->ln1_g[l], m->ln1_b[l], m->xn, R, d, eps);
+    int rc;
+    { ProfScope prof(ctx, CATEN_B200_K_LAYERNORM); rc = launch_layernorm(ctx, m->h, m->ln1_g[l], m->ln1_b[l], m->xn, R, d, eps); }
     if (!rc) rc = linear_any(ctx, m->attn_w[l], m->xn, m->attn_b[l], nullptr, CATEN_B200_ACT_NONE, m->qkv, R, prec);
-    if (!rc) rc = launch_attention(ctx, m->qkv, m->kc[l] + kv_off, m->vc[l] + kv_off, m->att, nb, s, n, H, T);
+    if (!rc) { ProfScope prof(ctx, s == 1 ? CATEN_B200_K_ATTN_DECODE : CATEN_B200_K_ATTN_PREFILL); rc = launch_attention(ctx, m->qkv, m->kc[l] + kv_off, m->vc[l] + kv_off, m->att, nb, s, n, H, T); }
     if (!rc) rc = linear_any(ctx, m->proj_w[l], m->att, m->proj_b[l], m->h, CATEN_B200_ACT_NONE, m->h2, R, prec);
-    if (!rc) rc = launch_layernorm(ctx, m->h2, m->ln2_g[l], m->ln2_b[l], m->xn, R, d, eps);
+    if (!rc) { ProfScope prof(ctx, CATEN_B200_K_LAYERNORM); rc = launch_layernorm(ctx, m->h2, m->ln2_g[l], m->ln2_b[l], m->xn, R, d, eps); }
     if (!rc) rc = linear_any(ctx, m->fc_w[l], m->xn, m->fc_b[l], nullptr, CATEN_B200_ACT_GELU, m->ff, R, prec);
     if (!rc) rc = linear_any(ctx, m->mproj_w[l], m->ff, m->mproj_b[l], m->h2, CATEN_B200_ACT_NONE, m->h, R, prec);
     if (rc) return rc;
   }
   // ln_f on the last position of every sequence only (the reference views the last row of the
   // logits, layers.lisp:90), gathered into rows [b0, b0+nb) of `last`
+  ProfScope prof(ctx, CATEN_B200_K_LAYERNORM);
   return launch_layernorm_strided(ctx, m->h, c.lnf_g, c.lnf_b, m->last + b0 * d, nb, d, eps, s);
 }
 
@@ -459,6 +516,7 @@ int caten_b200_gpt2_step_device(caten_b200_gpt2 *m, const float *d_ids_f32, cons
   }
   // lm_head (no bias, layers.lisp:79) + argmax over the vocabulary
   if (int rc = linear_any(ctx, c.lm_head, m->last, nullptr, nullptr, CATEN_B200_ACT_NONE, m->logits, B, c.precision)) return rc;
+  ProfScope prof(ctx, CATEN_B200_K_ARGMAX);
   return launch_argmax(ctx, m->logits, B, c.vocab, d_out_ids);
 }
 

@@ -8,6 +8,7 @@
 #include <stdint.h>
 
 #include <string>
+#include <vector>
 
 #include "../../include/caten_b200.h"
 
@@ -34,6 +35,11 @@ struct caten_b200_ctx {
   cb::Scratch wtmp;          // transposed/converted operand of relu_matmul
   void *encode_tiled = nullptr;  // cuTensorMapEncodeTiled, resolved at init
   int64_t launches = 0;
+  // per-kernel-class event timing (caten_b200_profile_begin / _end)
+  unsigned prof_mask = 0;
+  struct ProfRec { int klass; cudaEvent_t a, b; };
+  std::vector<ProfRec> prof;
+  std::vector<cudaEvent_t> prof_pool;
 };
 
 struct caten_b200_weight {

@@ -31,11 +31,17 @@ class GPT2:
         self.rt, self.params, self.batch, self.max_seq_len = runtime, params, batch, max_seq_len
         self.precision = L.PRECISIONS[precision] if isinstance(precision, str) else int(precision)
         self._bufs, self._weights, self._keep = [], [], []
+        self.weights = {}  # state-dict key -> B200Weight
         p, rt = params, runtime
         Lr = p.n_layers
 
         def f32(key) -> int:
-            b = rt.transfer_from_array(state_dict[key], np.float32)
+            a = state_dict[key]
+            if device_blobs is not None and key in device_blobs:
+                b = rt.open_buffer(a.shape, np.float32)
+                L.check(rt.ctx, rt.lib.caten_b200_d2d(rt.ctx, b.ptr, device_blobs[key], b.nbytes))
+            else:
+                b = rt.transfer_from_array(a, np.float32)
             self._bufs.append(b)
             return b.ptr
 
@@ -46,6 +52,7 @@ class GPT2:
             else:
                 h = rt.upload_weight(w)
             self._weights.append(h)
+            self.weights[key] = h
             return h.handle
 
         def parr(vals):
@@ -53,7 +60,6 @@ class GPT2:
             self._keep.append(arr)
             return C.cast(arr, C.POINTER(C.c_void_p))
 
-        self.packed_bytes = 0
         d = L.GPT2Desc()
         d.n_layers, d.d_model, d.n_heads, d.vocab = p.n_layers, p.dim, p.n_heads, p.vocab_size
         d.max_seq_len, d.batch, d.eps, d.precision, d.max_rows = max_seq_len, batch, p.norm_eps, self.precision, max_rows

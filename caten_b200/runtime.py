@@ -121,6 +121,22 @@ class B200Runtime:
     def sync(self):
         L.check(self.ctx, self.lib.caten_b200_sync(self.ctx))
 
+    def profile_begin(self, classes=None):
+        """Starts CUDA-event timing of the given kernel classes (names of ``_lib.KERNEL_CLASSES``;
+        all when None): the counterpart of PROFILE=1 (source/runtime/profile.lisp:15-39)."""
+        names = L.KERNEL_CLASSES if classes is None else classes
+        mask = 0
+        for nme in names:
+            mask |= 1 << L.KERNEL_CLASSES.index(nme)
+        L.check(self.ctx, self.lib.caten_b200_profile_begin(self.ctx, mask))
+
+    def profile_end(self) -> dict:
+        """Stops timing; returns {class: (milliseconds, calls)} for classes that ran."""
+        ms = (C.c_double * L.K_COUNT)()
+        calls = (C.c_int64 * L.K_COUNT)()
+        L.check(self.ctx, self.lib.caten_b200_profile_end(self.ctx, ms, calls))
+        return {L.KERNEL_CLASSES[i]: (ms[i], calls[i]) for i in range(L.K_COUNT) if calls[i]}
+
     @property
     def stream(self) -> int:
         return int(self.lib.caten_b200_stream(self.ctx) or 0)

@@ -175,6 +175,20 @@ int caten_b200_gpt2_kv(caten_b200_gpt2 *m, int layer, float **d_k, float **d_v);
 /* Number of kernel launches issued by this model's steps since creation. */
 int64_t caten_b200_gpt2_launch_count(caten_b200_gpt2 *m);
 
+/* ---- per-kernel timing ----------------------------------------------------------------------------
+ * Counterpart of PROFILE=1 (source/runtime/profile.lisp:15-39, source/codegen/runner.lisp:28-31),
+ * which wall-clocks every node of the VM: here launches of the selected kernel classes are
+ * bracketed with CUDA events on the context's stream, so asynchronous execution is kept. */
+enum {
+  CATEN_B200_K_EMBED = 0, CATEN_B200_K_LAYERNORM = 1, CATEN_B200_K_GEMV = 2, CATEN_B200_K_GEMM = 3,
+  CATEN_B200_K_ATTN_DECODE = 4, CATEN_B200_K_ATTN_PREFILL = 5, CATEN_B200_K_ARGMAX = 6, CATEN_B200_K_COUNT = 8
+};
+/* Starts timing the classes whose bit (1 << class) is set in class_mask. */
+int caten_b200_profile_begin(caten_b200_ctx *ctx, unsigned class_mask);
+/* Stops timing, synchronises, and writes per class the summed device milliseconds and the number
+ * of timed calls into ms[CATEN_B200_K_COUNT] and calls[CATEN_B200_K_COUNT]. */
+int caten_b200_profile_end(caten_b200_ctx *ctx, double *ms, int64_t *calls);
+
 /* Library build id (sm architecture it was compiled for), e.g. "sm_100a". */
 const char *caten_b200_arch(void);
 
