@@ -108,6 +108,7 @@ int caten_b200_init(int device, caten_b200_ctx **out) {
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaStreamCreate"); }
   if ((e = cudaMalloc(&ctx->d_status, 4 * sizeof(int))) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaMalloc"); }
   cudaMemset(ctx->d_status, 0, 4 * sizeof(int));
+
   if ((e = cudaMallocHost(&ctx->h_status, 4 * sizeof(int))) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaMallocHost"); }
   for (int i = 0; i < 4; ++i) ctx->h_status[i] = 0;
   cudaDriverEntryPointQueryResult qres;

@@ -32,7 +32,7 @@ struct caten_b200_ctx {
   int *d_status = nullptr;   // device status word written by kernels whose bounded waits run out
   int *h_status = nullptr;   // pinned mirror
   cb::Scratch xbf;           // bf16 copy (hi, lo) of the activation operand of the tensor-core GEMM
-  cb::Scratch wtmp;          // transposed/converted operand of relu_matmul
+  cb::Scratch wtmp;          // split-K partial tiles of the tensor-core GEMM
   void *encode_tiled = nullptr;  // cuTensorMapEncodeTiled, resolved at init
   int64_t launches = 0;
   // per-kernel-class event timing (caten_b200_profile_begin / _end)

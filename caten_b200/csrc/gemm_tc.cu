@@ -8,14 +8,14 @@
 // the epilogue one thread owns one output feature, so bias is a scalar and stores of a fixed
 // activation row are coalesced across the warp.
 //
-// Pipeline per CTA (320 threads), K in chunks of 64:
-//   warps 0-7  load the packed weight chunk (128 rows x 64 k) with vector loads, dequantise in
+// Pipeline per CTA (576 threads), K in chunks of 64:
+//   warps 0-15 load the packed weight chunk (128 rows x 64 k) with vector loads, dequantise in
 //              registers to bf16 and write it to shared memory in the 128-byte-swizzled K-major
 //              layout tcgen05.mma reads; after the K loop they run the epilogue
 //              (tcgen05.ld -> bias/activation/residual -> global)
-//   warp 8     one lane issues the TMA loads of the activation chunk (bf16 copy of x made by a
+//   warp 16    one lane issues the TMA loads of the activation chunk (bf16 copy of x made by a
 //              small pre-pass; tiled cp.async.bulk.tensor, no multicast)
-//   warp 9     allocates TMEM; one lane issues tcgen05.mma and commits to the stage's mbarrier
+//   warp 17    allocates TMEM; one lane issues tcgen05.mma and commits to the stage's mbarrier
 // NSPLIT = 1: plain bf16 operands.  NSPLIT = 3: x = x_hi + x_lo and w = w_hi + w_lo in bf16 and
 // three products (hi*hi + lo*hi + hi*lo) accumulate in the same fp32 TMEM tile.
 //
@@ -30,7 +30,8 @@ constexpr int WT_F32_T = 100;  // fp32 operand given as [K, N] row-major (relu_m
 constexpr int TC_BM = 128;      // weight rows per CTA (MMA M)
 constexpr int TC_BK = 64;       // k per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int TC_WBYTES = TC_BM * TC_BK * 2;
-constexpr int TC_THREADS = 320;
+constexpr int TC_PRODUCERS = 512;  // 16 warps dequantise; warp 16 issues TMA, warp 17 issues MMA
+constexpr int TC_THREADS = TC_PRODUCERS + 64;
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
 
 struct TcArgs {
@@ -41,6 +42,10 @@ struct TcArgs {
   int *status;
   int act, M, N, K, nkb, bnx, stages;
   uint32_t idesc, tmem_cols;
+  // split-K: grid.z CTAs share one output tile, each covering `cps` K-chunks; partial tiles go
+  // to `part` and splitk_reduce_kernel adds them in split order and applies the epilogue
+  int splits, cps;
+  float *part;
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -142,81 +147,159 @@ __device__ __forceinline__ void store8(uint8_t *whi, uint8_t *wlo, int r, int c,
   }
 }
 
-// Weight chunk (128 rows x 64 k) -> shared memory, by the 256 producer threads.
-template <int WT, int NSPLIT>
-__device__ __forceinline__ void produce_w(const TcArgs &a, int n0, int kc, uint8_t *whi, uint8_t *wlo, int tid) {
-  if (WT == CATEN_B200_Q4_0 || WT == CATEN_B200_Q8_0) {
-    // thread = (row, block of 32): two adjacent threads read 32 (Q4_0) / 64 (Q8_0) contiguous bytes
-    const int r = tid >> 1, blk = tid & 1;
-    const int64_t row = (int64_t)n0 + r;
-    const bool ok = row < a.N;
-    const int64_t bi = row * a.nkb + (int64_t)kc * 2 + blk;
-    const float sc = ok ? __half2float(a.d[bi]) : 0.0f;
-    if (WT == CATEN_B200_Q4_0) {
-      const uint4 q = ok ? __ldcs(reinterpret_cast<const uint4 *>(a.qs) + bi) : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-      const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
-      // chunk 0: low nibbles of bytes 0-7, 1: low of bytes 8-15, 2: high of 0-7, 3: high of 8-15
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float w[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const uint32_t word = wd[(c & 1) * 2 + (e >> 2)];
-          const int nib = (int)((word >> (8 * (e & 3) + (c >> 1) * 4)) & 0xF);
-          w[e] = (float)(nib - 8) * sc;
-        }
-        store8<NSPLIT>(whi, wlo, r, blk * 4 + c, w);
-      }
+// One thread's share of a weight chunk (128 rows x 64 k), split into a global-load step and a
+// convert-and-store step so that the loads of later chunks are in flight while the current one
+// is dequantised (DEPTH chunks of look-ahead hide the HBM latency of the packed stream).
+//
+// 512 producer threads.  For the row-major formats warp w owns rows 8w..8w+7 and lane l is
+// (row 8w + (l & 7), part l >> 3): one warp-wide load reads 8 rows x one contiguous run per row
+// (whole 32-byte sectors), and the 8 lanes that store together write 8 different rows, which the
+// 128-byte swizzle spreads over all banks.
+template <int WT> struct WChunk;
+
+// exact (float)(nibble - 8): 0x4B000000 | nibble is the float 2^23 + nibble
+__device__ __forceinline__ float nib_to_float(uint32_t word, int shift) {
+  return __uint_as_float(((word >> shift) & 0xFu) | 0x4B000000u) - 8388616.0f;
+}
+
+template <> struct WChunk<CATEN_B200_Q4_0> {
+  static constexpr int DEPTH = 4;
+  uint2 q;   // 8 of the block's 16 code bytes: low nibbles = 8 elements, high nibbles = 8 more
+  float sc;
+  __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int tid) {
+    const int l = tid & 31, part = l >> 3;
+    const int64_t row = (int64_t)n0 + 8 * (tid >> 5) + (l & 7);
+    const int64_t bi = row * a.nkb + (int64_t)kc * 2 + (part >> 1);
+    if (row < a.N) {
+      q = __ldcs(reinterpret_cast<const uint2 *>(a.qs) + bi * 2 + (part & 1));
+      sc = __half2float(a.d[bi]);
     } else {
-      const uint4 *p = reinterpret_cast<const uint4 *>(a.qs) + bi * 2;
-      const uint4 q0 = ok ? __ldcs(p) : make_uint4(0, 0, 0, 0), q1 = ok ? __ldcs(p + 1) : make_uint4(0, 0, 0, 0);
-      const uint32_t wd[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float w[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) w[e] = (float)(int8_t)(wd[2 * c + (e >> 2)] >> (8 * (e & 3))) * sc;
-        store8<NSPLIT>(whi, wlo, r, blk * 4 + c, w);
-      }
+      q = make_uint2(0x88888888u, 0x88888888u);
+      sc = 0.0f;
     }
-  } else if (WT == CATEN_B200_F32) {
-    // warp w covers rows 16w..16w+15, two rows per load instruction, 16 lanes x 16 B per row
-    const int warp = tid >> 5, lane = tid & 31;
+  }
+  template <int NSPLIT> __device__ __forceinline__ void store(uint8_t *whi, uint8_t *wlo, int tid) const {
+    const int l = tid & 31, part = l >> 3, r = 8 * (tid >> 5) + (l & 7), blk = part >> 1, h = part & 1;
+    const uint32_t wd[2] = {q.x, q.y};
+    // bytes 8h..8h+7 of the block: low nibbles are elements 8h.., high nibbles elements 16+8h..
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int r = 16 * warp + 2 * j + (lane >> 4), c4 = lane & 15;
-      const int64_t row = (int64_t)n0 + r;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (row < a.N) v = __ldcs(reinterpret_cast<const float4 *>((const float *)a.qs + row * a.K + (int64_t)kc * 64) + c4);
-      const uint32_t off = swz(r, c4 >> 1) + (c4 & 1) * 8;
-      *reinterpret_cast<uint2 *>(whi + off) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
-      if (NSPLIT == 3)
-        *reinterpret_cast<uint2 *>(wlo + off) = make_uint2(pack_bf16(bf16_lo(v.x), bf16_lo(v.y)), pack_bf16(bf16_lo(v.z), bf16_lo(v.w)));
+    for (int hi = 0; hi < 2; ++hi) {
+      float w[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) w[e] = nib_to_float(wd[e >> 2], 8 * (e & 3) + hi * 4) * sc;
+      store8<NSPLIT>(whi, wlo, r, blk * 4 + hi * 2 + h, w);
     }
-  } else if (WT == CATEN_B200_F16) {
-    const int warp = tid >> 5, lane = tid & 31;
+  }
+};
+
+template <> struct WChunk<CATEN_B200_Q8_0> {
+  static constexpr int DEPTH = 3;
+  uint4 q;   // 16 of the block's 32 codes
+  float sc;
+  __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int tid) {
+    const int l = tid & 31, part = l >> 3;
+    const int64_t row = (int64_t)n0 + 8 * (tid >> 5) + (l & 7);
+    const int64_t bi = row * a.nkb + (int64_t)kc * 2 + (part >> 1);
+    if (row < a.N) {
+      q = __ldcs(reinterpret_cast<const uint4 *>(a.qs) + bi * 2 + (part & 1));
+      sc = __half2float(a.d[bi]);
+    } else {
+      q = make_uint4(0, 0, 0, 0);
+      sc = 0.0f;
+    }
+  }
+  template <int NSPLIT> __device__ __forceinline__ void store(uint8_t *whi, uint8_t *wlo, int tid) const {
+    const int l = tid & 31, part = l >> 3, r = 8 * (tid >> 5) + (l & 7), blk = part >> 1, h = part & 1;
+    const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      float w[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) w[e] = (float)(int8_t)(wd[2 * c + (e >> 2)] >> (8 * (e & 3))) * sc;
+      store8<NSPLIT>(whi, wlo, r, blk * 4 + h * 2 + c, w);
+    }
+  }
+};
+
+template <> struct WChunk<CATEN_B200_F32> {
+  static constexpr int DEPTH = 2;
+  float4 v[4];
+  __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int tid) {
+    const int l = tid & 31;
+    const int64_t row = (int64_t)n0 + 8 * (tid >> 5) + (l & 7);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      v[j] = row < a.N ? __ldcs(reinterpret_cast<const float4 *>((const float *)a.qs + row * a.K + (int64_t)kc * 64) + (l >> 3) + 4 * j)
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  template <int NSPLIT> __device__ __forceinline__ void store(uint8_t *whi, uint8_t *wlo, int tid) const {
+    const int l = tid & 31, r = 8 * (tid >> 5) + (l & 7);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int r = 16 * warp + 4 * j + (lane >> 3), c = lane & 7;
-      const int64_t row = (int64_t)n0 + r;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (row < a.N) v = __ldcs(reinterpret_cast<const uint4 *>((const __half *)a.qs + row * a.K + (int64_t)kc * 64) + c);
-      const __half *h = reinterpret_cast<const __half *>(&v);
+      const int c4 = (l >> 3) + 4 * j;
+      const uint32_t off = swz(r, c4 >> 1) + (c4 & 1) * 8;
+      *reinterpret_cast<uint2 *>(whi + off) = make_uint2(pack_bf16(v[j].x, v[j].y), pack_bf16(v[j].z, v[j].w));
+      if (NSPLIT == 3)
+        *reinterpret_cast<uint2 *>(wlo + off) =
+            make_uint2(pack_bf16(bf16_lo(v[j].x), bf16_lo(v[j].y)), pack_bf16(bf16_lo(v[j].z), bf16_lo(v[j].w)));
+    }
+  }
+};
+
+template <> struct WChunk<CATEN_B200_F16> {
+  static constexpr int DEPTH = 3;
+  uint4 v[2];
+  __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int tid) {
+    const int l = tid & 31;
+    const int64_t row = (int64_t)n0 + 8 * (tid >> 5) + (l & 7);
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+      v[j] = row < a.N ? __ldcs(reinterpret_cast<const uint4 *>((const __half *)a.qs + row * a.K + (int64_t)kc * 64) + (l >> 3) + 4 * j)
+                       : make_uint4(0, 0, 0, 0);
+  }
+  template <int NSPLIT> __device__ __forceinline__ void store(uint8_t *whi, uint8_t *wlo, int tid) const {
+    const int l = tid & 31, r = 8 * (tid >> 5) + (l & 7);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const __half *h = reinterpret_cast<const __half *>(&v[j]);
       float w[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) w[e] = __half2float(h[e]);
-      store8<NSPLIT>(whi, wlo, r, c, w);
+      store8<NSPLIT>(whi, wlo, r, (l >> 3) + 4 * j, w);
     }
-  } else {  // WT_F32_T: b[k, n]; thread = (n, half of the 64 k); loads coalesced across n
-    const int r = tid & 127, kh = tid >> 7;
-    const int64_t col = (int64_t)n0 + r;
-    const float *b = (const float *)a.qs + ((int64_t)kc * 64 + kh * 32) * a.N + col;
+  }
+};
+
+// b[k, n] (relu_matmul): thread = (n, quarter of the 64 k); loads coalesced across n
+template <> struct WChunk<WT_F32_T> {
+  static constexpr int DEPTH = 2;
+  float v[16];
+  __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int tid) {
+    const int64_t col = (int64_t)n0 + (tid & 127);
+    const float *b = (const float *)a.qs + ((int64_t)kc * 64 + (tid >> 7) * 16) * a.N + col;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      float w[8];
+    for (int e = 0; e < 16; ++e) v[e] = col < a.N ? __ldcs(b + (int64_t)e * a.N) : 0.0f;
+  }
+  template <int NSPLIT> __device__ __forceinline__ void store(uint8_t *whi, uint8_t *wlo, int tid) const {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) w[e] = col < a.N ? __ldcs(b + (int64_t)(c * 8 + e) * a.N) : 0.0f;
-      store8<NSPLIT>(whi, wlo, r, kh * 4 + c, w);
+    for (int c = 0; c < 2; ++c) store8<NSPLIT>(whi, wlo, tid & 127, (tid >> 7) * 2 + c, v + 8 * c);
+  }
+};
+
+// Epilogue of one 16-column group held in registers: y[m, o] = act(acc + bias) + res.
+template <int ACT>
+__device__ __forceinline__ void epi_store16(const TcArgs &a, const uint32_t *r, float bias, int64_t o, int m_first) {
+  float *yp = a.y + (int64_t)m_first * a.N + o;
+  const float *rp = a.res ? a.res + (int64_t)m_first * a.N + o : nullptr;
+  const int lim = a.M - m_first < 16 ? a.M - m_first : 16;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    if (i < lim) {
+      float v = __uint_as_float(r[i]) + bias;
+      if (ACT == CATEN_B200_ACT_GELU) v = gelu_ref(v);
+      if (ACT == CATEN_B200_ACT_RELU) v = v > 0.0f ? v : 0.0f;
+      if (rp) v = rp[(int64_t)i * a.N] + v;
+      yp[(int64_t)i * a.N] = v;
     }
   }
 }
@@ -237,6 +320,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
   auto empty = [&](int s) { return bar0 + 8u * (2 * S + s); };
   const uint32_t accum_bar = bar0 + 8u * (3 * S);
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
+  // [0] some role gave up a wait; [1] never set (for waits that must not be cut short);
+  // [2], [3] thread 0's verdict for the producer warps (stage free / accumulator ready)
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   auto stage_whi = [&](int s) { return smem + (size_t)s * stage_bytes; };
   auto stage_wlo = [&](int s) { return smem + (size_t)s * stage_bytes + TC_WBYTES; };
@@ -245,20 +330,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * TC_BM, m0 = blockIdx.y * bnx;
-  const int num_k = a.K / TC_BK;
+  const int kc0 = blockIdx.z * a.cps;
+  const int num_k = min(a.K / TC_BK - kc0, a.cps);  // chunks of this CTA: [kc0, kc0 + num_k)
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(full_w(s), 256);
+      mbar_init(full_w(s), 1);
       mbar_init(full_x(s), 1);
       mbar_init(empty(s), 1);
     }
     mbar_init(accum_bar, 1);
     abort_flag[0] = 0;
-    abort_flag[1] = 0;  // second word: a flag nothing sets, for waits that must not be cut short
+    abort_flag[1] = 0;
+    abort_flag[2] = 0;
+    abort_flag[3] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 9) {
+  if (warp == 17) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(a.tmem_cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -267,78 +355,116 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp < 8) {
+  if (warp < 16) {
     // ---------------- weight producers ----------------
-    for (int kc = 0; kc < num_k; ++kc) {
-      const int s = kc % S;
-      const uint32_t ph = (uint32_t)(kc / S) & 1u;
-      if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) {
-        if (!*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 1; a.status[2] = kc; }
-        break;
+    // Only thread 0 polls the stage's `empty` mbarrier; the other producer warps sleep on a
+    // hardware named barrier instead of spinning (spinning warps would take issue slots from the
+    // warps that are dequantising).  Per chunk: [barrier 2] slot is free -> convert + store ->
+    // fence -> [barrier 3] all stores done -> thread 0 signals `full_w`.
+    constexpr int DEPTH = WChunk<WT>::DEPTH;
+    WChunk<WT> ring[DEPTH];
+#pragma unroll
+    for (int j = 0; j < DEPTH; ++j)
+      if (j < num_k) ring[j].load(a, n0, kc0 + j, tid);
+    int s = 0;
+    uint32_t ph = 0;
+    bool alive = true;
+    for (int kb = 0; kb < num_k && alive; kb += DEPTH) {
+#pragma unroll
+      for (int j = 0; j < DEPTH; ++j) {
+        const int kc = kb + j;
+        if (kc < num_k && alive) {
+          if (tid == 0) {
+            const bool got = mbar_wait(empty(s), ph ^ 1u, abort_flag);
+            if (!got && !*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 1; a.status[2] = kc; }
+            abort_flag[2] = (got && !*abort_flag) ? 1 : 0;  // one verdict for all 512 producers
+          }
+          asm volatile("bar.sync 2, 512;" ::: "memory");
+          if (!abort_flag[2]) {
+            alive = false;
+          } else {
+            ring[j].template store<NSPLIT>(stage_whi(s), stage_wlo(s), tid);
+            fence_proxy_async();  // this thread's stores -> visible to the tensor core's (async proxy) reads
+            asm volatile("bar.sync 3, 512;" ::: "memory");
+            if (tid == 0) mbar_arrive(full_w(s));
+            if (kc + DEPTH < num_k) ring[j].load(a, n0, kc0 + kc + DEPTH, tid);
+            if (++s == S) { s = 0; ph ^= 1u; }
+          }
+        }
       }
-      produce_w<WT, NSPLIT>(a, n0, kc, stage_whi(s), stage_wlo(s), tid);
-      fence_proxy_async();
-      mbar_arrive(full_w(s));
     }
     // ---------------- epilogue ----------------
-    bool ok = !*abort_flag && mbar_wait(accum_bar, 0, abort_flag);
-    if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 2; }
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
+    if (tid == 0) {
+      const bool got = !*abort_flag && mbar_wait(accum_bar, 0, abort_flag);
+      if (!got && !*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 2; }
+      abort_flag[3] = got ? 1 : 0;
+    }
+    asm volatile("bar.sync 1, 512;" ::: "memory");
+    if (abort_flag[3]) {
       tc_fence_after();
       const int quad = warp & 3;
       const int64_t o = (int64_t)n0 + quad * 32 + lane;  // output feature of this thread
       const bool o_ok = o < a.N;
       const float bias = (a.bias && o_ok) ? a.bias[o] : 0.0f;
-      const int half_cols = bnx >= 32 ? bnx / 2 : bnx;
-      const int c_begin = (warp >> 2) * half_cols, c_end = bnx >= 32 ? c_begin + half_cols : (warp < 4 ? bnx : 0);
-      for (int c = c_begin; c < c_end; c += 16) {
-        uint32_t r[16];
-        tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int64_t m = (int64_t)m0 + c + i;
-          if (o_ok && m < a.M) {
-            float v = __uint_as_float(r[i]);
-            if (a.bias) v = v + bias;
-            v = apply_act(v, a.act);
-            if (a.res) v = a.res[m * a.N + o] + v;
-            a.y[m * a.N + o] = v;
+      // four warps per TMEM lane quadrant share the columns in groups of at least 16
+      const int ngroups = bnx >= 64 ? 4 : bnx / 16, per_group = bnx / ngroups, cgroup = warp >> 2;
+      const int c_begin = cgroup * per_group, c_end = cgroup < ngroups ? c_begin + per_group : c_begin;
+      const uint32_t trow = tmem_base + ((uint32_t)(quad * 32) << 16);
+      if (a.splits == 1) {
+        for (int c = c_begin; c < c_end; c += 16) {
+          uint32_t r[16];
+          tmem_ld16(trow + (uint32_t)c, r);
+          tmem_ld_wait();
+          if (o_ok && m0 + c < a.M) {
+            if (a.act == CATEN_B200_ACT_GELU) epi_store16<CATEN_B200_ACT_GELU>(a, r, bias, o, m0 + c);
+            else if (a.act == CATEN_B200_ACT_RELU) epi_store16<CATEN_B200_ACT_RELU>(a, r, bias, o, m0 + c);
+            else epi_store16<CATEN_B200_ACT_NONE>(a, r, bias, o, m0 + c);
           }
+        }
+      } else {
+        // partial tile -> part[split][tile][column][row]: a warp stores 128 contiguous bytes
+        const int tiles = gridDim.x * gridDim.y, tile = blockIdx.y * gridDim.x + blockIdx.x;
+        const int rrow = quad * 32 + lane;
+        float *mine = a.part + ((size_t)blockIdx.z * tiles + tile) * bnx * TC_BM + rrow;
+        for (int c = c_begin; c < c_end; c += 16) {
+          uint32_t r[16];
+          tmem_ld16(trow + (uint32_t)c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) mine[(c + i) * TC_BM] = __uint_as_float(r[i]);
         }
       }
     }
     tc_fence_before();
-  } else if (warp == 8) {
+  } else if (warp == 16) {
     // ---------------- activation TMA producer ----------------
     if (lane == 0) {
-      int issued = 0;
+      int issued = 0, s = 0;
+      uint32_t ph = 0;
       for (int kc = 0; kc < num_k; ++kc) {
-        const int s = kc % S;
-        const uint32_t ph = (uint32_t)(kc / S) & 1u;
         if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) {
           if (!*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 3; a.status[2] = kc; }
           break;
         }
         mbar_expect_tx(full_x(s), xbytes * (NSPLIT == 3 ? 2u : 1u));
-        tma_load_2d(smem_u32(stage_xhi(s)), &tm_hi, full_x(s), kc * TC_BK, m0);
-        if (NSPLIT == 3) tma_load_2d(smem_u32(stage_xlo(s)), &tm_lo, full_x(s), kc * TC_BK, m0);
+        tma_load_2d(smem_u32(stage_xhi(s)), &tm_hi, full_x(s), (kc0 + kc) * TC_BK, m0);
+        if (NSPLIT == 3) tma_load_2d(smem_u32(stage_xlo(s)), &tm_lo, full_x(s), (kc0 + kc) * TC_BK, m0);
         issued = kc + 1;
+        if (++s == S) { s = 0; ph ^= 1u; }
       }
       if (*abort_flag) {
         // let the copies this thread started land before the CTA's shared memory is released
         for (int kc = issued > S ? issued - S : 0; kc < issued; ++kc)
-          mbar_wait(full_x(kc % S), (uint32_t)(kc / S) & 1u, abort_flag + 1 /* never set: full wait */);
+          mbar_wait(full_x(kc % S), (uint32_t)(kc / S) & 1u, abort_flag + 1);
       }
     }
   } else {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       bool ok = true;
-      for (int kc = 0; kc < num_k && ok; ++kc) {
-        const int s = kc % S;
-        const uint32_t ph = (uint32_t)(kc / S) & 1u;
+      int s = 0;
+      uint32_t ph = 0;
+      for (int kc = 0; kc < num_k; ++kc) {
         ok = mbar_wait(full_w(s), ph, abort_flag) && mbar_wait(full_x(s), ph, abort_flag);
         if (!ok) {
           if (!*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 4; a.status[2] = kc; }
@@ -356,17 +482,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
             umma_bf16(tmem_base, dwh + adv, dxl + adv, a.idesc, 1u);
           }
         }
-        umma_commit(empty(s));
+        umma_commit(empty(s));  // frees the stage when these MMAs have read it
+        if (++s == S) { s = 0; ph ^= 1u; }
       }
       if (ok) umma_commit(accum_bar);
     }
     __syncwarp();
   }
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 17) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
   }
+}
+
+// Sums the split-K partial tiles part[split][tile][column][row] in split order (so the result is
+// the same on every run) and applies bias / activation / residual.  Consecutive threads own
+// consecutive weight rows: partial reads and y stores are coalesced.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ part, int splits, int tiles_x, int tiles,
+                                                            int bnx, const float *__restrict__ bias, const float *res, float *y,
+                                                            int act, int M, int N) {
+  const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  const int row = (int)(idx & (TC_BM - 1));
+  const int64_t rest = idx >> 7;
+  const int col = (int)(rest % bnx), tile = (int)(rest / bnx);
+  if (tile >= tiles) return;
+  const int64_t o = (int64_t)(tile % tiles_x) * TC_BM + row, m = (int64_t)(tile / tiles_x) * bnx + col;
+  if (o >= N || m >= M) return;
+  const size_t zstride = (size_t)tiles * bnx * TC_BM;
+  const float *p = part + ((size_t)tile * bnx + col) * TC_BM + row;
+  float v = 0.0f;
+  for (int z = 0; z < splits; ++z) v += __ldcs(p + z * zstride);
+  if (bias) v = v + bias[o];
+  v = apply_act(v, act);
+  if (res) v = res[m * N + o] + v;
+  y[m * N + o] = v;
 }
 
 // x -> bf16 hi (and lo) copies, row-major [M, K]
@@ -418,7 +568,7 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
   split_bf16_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, ctx->stream>>>((const float4 *)x, (uint2 *)xhi, (uint2 *)xlo, n4);
   CB_LAUNCH_CHECK(ctx, "split_bf16_kernel");
 
-  const int max_bnx = nsplit == 3 ? 128 : 256;
+  const int max_bnx = 256;
   int bnx = 16;
   while (bnx < max_bnx && bnx < M) bnx *= 2;
   CUtensorMap mh, ml;
@@ -436,23 +586,49 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
   a.stages = stages;
   a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bnx >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
   a.tmem_cols = bnx < 32 ? 32u : (uint32_t)bnx;
-  const size_t smem = 1024 + stage * stages + (3 * stages + 1) * 8 + 16;
+  const size_t smem = 1024 + stage * stages + (3 * stages + 1) * 8 + 32;
   const int64_t gy = (M + bnx - 1) / bnx;
   if (gy > 65535) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_tc: too many rows for one launch (%lld)", (long long)M);
-  const dim3 grid((unsigned)((N + TC_BM - 1) / TC_BM), (unsigned)gy);
+  const int64_t gx = (N + TC_BM - 1) / TC_BM, tiles = gx * gy;
+  // split-K when the output tiles alone cannot occupy the GPU (decode: few activation rows)
+  const int num_k = (int)(K / TC_BK);
+  int splits = 1;
+  if (tiles < ctx->sm_count) {
+    const int by_work = num_k / 4 > 0 ? num_k / 4 : 1;                       // at least 4 chunks per CTA
+    const int by_fill = (int)(ctx->sm_count / tiles);                         // one wave: every CTA resident at once
+    splits = by_work < by_fill ? by_work : by_fill;
+    if (splits > 32) splits = 32;
+  }
+  int cps = (num_k + splits - 1) / splits;
+  splits = (num_k + cps - 1) / cps;
+  a.splits = splits; a.cps = cps; a.part = nullptr;
+  if (splits > 1) {
+    if (int rc = scratch_reserve(ctx, &ctx->wtmp, (size_t)splits * tiles * bnx * TC_BM * sizeof(float))) return rc;
+    a.part = (float *)ctx->wtmp.ptr;
+  }
+  if (a.stages > cps) a.stages = cps;
+  const dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)splits);
 
+  int rc = CATEN_B200_EUNSUPPORTED;
 #define TC_CASE(WT)                                                              \
   case WT:                                                                       \
-    return nsplit == 3 ? launch_tc_t<WT, 3>(ctx, mh, ml, a, grid, smem) : launch_tc_t<WT, 1>(ctx, mh, ml, a, grid, smem)
+    rc = nsplit == 3 ? launch_tc_t<WT, 3>(ctx, mh, ml, a, grid, smem) : launch_tc_t<WT, 1>(ctx, mh, ml, a, grid, smem); \
+    break
   switch (wt) {
     TC_CASE(CATEN_B200_F32);
     TC_CASE(CATEN_B200_F16);
     TC_CASE(CATEN_B200_Q4_0);
     TC_CASE(CATEN_B200_Q8_0);
     TC_CASE(WT_F32_T);
+    default: return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_tc: weight type %d", wt);
   }
 #undef TC_CASE
-  return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_tc: weight type %d", wt);
+  if (rc || splits == 1) return rc;
+  const int64_t total = tiles * bnx * TC_BM;
+  splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(a.part, splits, (int)gx, (int)tiles, bnx, bias, res, y,
+                                                                              act, (int)M, (int)N);
+  CB_LAUNCH_CHECK(ctx, "splitk_reduce_kernel");
+  return 0;
 }
 
 int launch_gemm_tc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,

@@ -14,7 +14,7 @@ struct GemvArgs {
   int act, N, nkb, G;
 };
 
-constexpr int GEMV_MAX_THREADS = 640;
+constexpr int GEMV_MAX_THREADS = 512;
 
 __device__ __forceinline__ uint4 ld_stream(const uint4 *p) { return __ldcs(p); }
 
@@ -116,9 +116,14 @@ __global__ void __launch_bounds__(GEMV_MAX_THREADS) gemv_blocked_kernel(GemvArgs
   const uint4 *qs = reinterpret_cast<const uint4 *>(a.qs);
   const int rows_per_iter = G * RI;
   const int warp = tid >> 5, lane = tid & 31, nwarps = (blockDim.x + 31) >> 5;
-  for (int64_t base = (int64_t)blockIdx.x * rows_per_iter; base < a.N; base += (int64_t)gridDim.x * rows_per_iter) {
-    uint32_t q[RI][W];
-    float sc[RI];
+  const int64_t stride = (int64_t)gridDim.x * rows_per_iter;
+
+  // The loads of iteration i+1 are issued before iteration i is reduced, and the partial sums
+  // alternate between two shared-memory buffers, so there is one barrier per iteration and the
+  // packed stream stays in flight across it.
+  uint32_t qn[RI][W];
+  float scn[RI];
+  auto load = [&](int64_t base) {
 #pragma unroll
     for (int i = 0; i < RI; ++i) {
       const int64_t row = base + i * G + ro;
@@ -127,20 +132,35 @@ __global__ void __launch_bounds__(GEMV_MAX_THREADS) gemv_blocked_kernel(GemvArgs
 #pragma unroll
       for (int j = 0; j < W / 4; ++j) {
         const uint4 v = ok ? ld_stream(qs + bidx * (W / 4) + j) : make_uint4(0, 0, 0, 0);
-        q[i][4 * j] = v.x; q[i][4 * j + 1] = v.y; q[i][4 * j + 2] = v.z; q[i][4 * j + 3] = v.w;
+        qn[i][4 * j] = v.x; qn[i][4 * j + 1] = v.y; qn[i][4 * j + 2] = v.z; qn[i][4 * j + 3] = v.w;
       }
-      sc[i] = ok ? __half2float(a.d[bidx]) : 0.0f;
+      scn[i] = ok ? __half2float(a.d[bidx]) : 0.0f;
     }
+  };
+  int64_t base = (int64_t)blockIdx.x * rows_per_iter;
+  if (base < a.N) load(base);
+  int buf = 0;
+  for (; base < a.N; base += stride) {
+    uint32_t q[RI][W];
+    float sc[RI];
+#pragma unroll
+    for (int i = 0; i < RI; ++i) {
+      sc[i] = scn[i];
+#pragma unroll
+      for (int j = 0; j < W; ++j) q[i][j] = qn[i][j];
+    }
+    if (base + stride < a.N) load(base + stride);
+    float *rb = red + buf * rows_per_iter * nkb;
     if (active) {
 #pragma unroll
-      for (int i = 0; i < RI; ++i) red[(i * G + ro) * nkb + kb] = blk.dot(q[i], sc[i]);
+      for (int i = 0; i < RI; ++i) rb[(i * G + ro) * nkb + kb] = blk.dot(q[i], sc[i]);
     }
     __syncthreads();
     for (int r = warp; r < rows_per_iter; r += nwarps) {
       const int64_t row = base + r;
       if (row >= a.N) break;
       float s = 0.0f;
-      for (int k = lane; k < nkb; k += 32) s += red[r * nkb + k];
+      for (int k = lane; k < nkb; k += 32) s += rb[r * nkb + k];
       s = warp_sum(s);
       if (lane == 0) {
         if (a.bias) s = s + a.bias[row];
@@ -149,7 +169,7 @@ __global__ void __launch_bounds__(GEMV_MAX_THREADS) gemv_blocked_kernel(GemvArgs
         a.y[row] = s;
       }
     }
-    __syncthreads();
+    buf ^= 1;
   }
 }
 
@@ -223,7 +243,7 @@ __global__ void __launch_bounds__(256) gemv_dense_kernel(const T *__restrict__ W
 template <class BLK, int RI>
 static int launch_blocked(caten_b200_ctx *ctx, const GemvArgs &a) {
   const int threads = ((a.G * a.nkb + 31) / 32) * 32;
-  const size_t smem = (size_t)a.G * RI * a.nkb * sizeof(float);
+  const size_t smem = 2 * (size_t)a.G * RI * a.nkb * sizeof(float);
   int occ = 1;
   cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_blocked_kernel<BLK, RI>, threads, smem);
   if (occ < 1) occ = 1;

@@ -72,49 +72,56 @@ int launch_dequant(caten_b200_ctx *ctx, const caten_b200_weight *w, float *out) 
 
 // ---------------------------------------------------------------------------------------------
 // LayerNorm (source/nn/normalization.lisp:48-58): u = sum(x)*(1/d); dl = x - u;
-// var = sum(dl*dl)*(1/d); y = dl * (1/sqrt(var+eps)) * gamma + beta.  One warp per row, the
-// row held in registers so x is read from HBM once.  d % 4 == 0, d <= 2048.
+// var = sum(dl*dl)*(1/d); y = dl * (1/sqrt(var+eps)) * gamma + beta.  One CTA of 256 threads per
+// row, the row held in registers (x is read from HBM once); d % 4 == 0, d <= 2048.
 // ---------------------------------------------------------------------------------------------
-constexpr int LN_MAXV = 16;  // float4 per lane
+constexpr int LN_THREADS = 256, LN_MAXV = 2;  // float4 per thread
 
-__global__ void __launch_bounds__(128) layernorm_kernel(const float *__restrict__ x, const float *__restrict__ g,
-                                                        const float *__restrict__ b, float *__restrict__ y,
-                                                        int64_t rows, int d4, float invd, float eps,
-                                                        int64_t src_stride) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (row >= rows) return;
+__device__ __forceinline__ float ln_block_sum(float v, float *red) {
+  v = warp_sum(v);
+  __syncthreads();  // protects `red` from the previous use
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = red[0];
+#pragma unroll
+  for (int w = 1; w < LN_THREADS / 32; ++w) t += red[w];
+  return t;
+}
+
+__global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__restrict__ x, const float *__restrict__ g,
+                                                               const float *__restrict__ b, float *__restrict__ y,
+                                                               int d4, float invd, float eps, int64_t src_stride) {
+  __shared__ float red[LN_THREADS / 32];
+  const int64_t row = blockIdx.x;
   const int64_t src_row = src_stride > 1 ? (row + 1) * src_stride - 1 : row;
   const float4 *xr = reinterpret_cast<const float4 *>(x) + src_row * d4;
   float4 v[LN_MAXV];
   float sum = 0.0f;
 #pragma unroll
   for (int i = 0; i < LN_MAXV; ++i) {
-    const int c = lane + 32 * i;
+    const int c = threadIdx.x + LN_THREADS * i;
     if (c < d4) {
       v[i] = xr[c];
       sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
     }
   }
-  sum = warp_sum(sum);
-  const float u = sum * invd;
+  const float u = ln_block_sum(sum, red) * invd;
   float sq = 0.0f;
 #pragma unroll
   for (int i = 0; i < LN_MAXV; ++i) {
-    const int c = lane + 32 * i;
+    const int c = threadIdx.x + LN_THREADS * i;
     if (c < d4) {
       v[i].x -= u; v[i].y -= u; v[i].z -= u; v[i].w -= u;
       sq += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
     }
   }
-  sq = warp_sum(sq);
-  const float var = sq * invd;
+  const float var = ln_block_sum(sq, red) * invd;
   const float rs = 1.0f / sqrtf(var + eps);
   const float4 *g4 = reinterpret_cast<const float4 *>(g), *b4 = reinterpret_cast<const float4 *>(b);
   float4 *yr = reinterpret_cast<float4 *>(y) + row * d4;
 #pragma unroll
   for (int i = 0; i < LN_MAXV; ++i) {
-    const int c = lane + 32 * i;
+    const int c = threadIdx.x + LN_THREADS * i;
     if (c < d4) {
       const float4 gg = g4[c], bb = b4[c];
       float4 o;
@@ -130,9 +137,9 @@ __global__ void __launch_bounds__(128) layernorm_kernel(const float *__restrict_
 int launch_layernorm_strided(caten_b200_ctx *ctx, const float *x, const float *g, const float *b, float *y,
                              int64_t rows, int64_t d, float eps, int64_t src_stride) {
   if (rows <= 0) return 0;
-  if (d % 4 || d > 128 * LN_MAXV) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: d=%lld (need d%%4==0, d<=2048)", (long long)d);
-  const int64_t grid = (rows + 3) / 4;
-  layernorm_kernel<<<(unsigned)grid, 128, 0, ctx->stream>>>(x, g, b, y, rows, (int)(d / 4), 1.0f / (float)d, eps, src_stride);
+  if (d % 4 || d > 4 * LN_THREADS * LN_MAXV) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: d=%lld (need d%%4==0, d<=2048)", (long long)d);
+  if (rows > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: too many rows");
+  layernorm_kernel<<<(unsigned)rows, LN_THREADS, 0, ctx->stream>>>(x, g, b, y, (int)(d / 4), 1.0f / (float)d, eps, src_stride);
   CB_LAUNCH_CHECK(ctx, "layernorm_kernel");
   return 0;
 }

@@ -1,0 +1,140 @@
+"""Single-kernel timings through the C ABI (CUDA events on the library's stream).
+
+    python -m caten_b200.microbench attn_decode --batch 64 --heads 25 --context 700
+    python -m caten_b200.microbench gemv --model gpt2-xl --wtype q4_0
+    python -m caten_b200.microbench gemm --rows 256 --n 1600 --k 6400 --wtype q4_0 --precision bf16x3
+    python -m caten_b200.microbench relu_matmul --precision bf16x3
+
+Each prints one JSON line.  Operands are rotated over several copies larger in total than the
+126 MB L2, so every launch streams from HBM.  Events bracket each launch (the profile API of the
+library), so host launch pace does not enter; for kernels of a few microseconds the figure still
+includes launch latency and an `ncu --metrics gpu__time_duration.sum` list is the better source.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import numpy as np
+
+from . import _lib as L
+from . import synthetic as S
+from .runtime import B200Runtime
+
+
+def _peak():
+    import os
+    try:
+        with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")) as f:
+            j = json.load(f)
+            return float(j["hbm_gbs"]), float(j["bf16_tflops"])
+    except Exception:
+        return 6650.0, 1590.0
+
+
+def attn_decode(rt, a):
+    B, H, T, n = a.batch, a.heads, a.context + 8, a.context
+    d = H * 64
+    copies = max(2, int(np.ceil(300e6 / (B * H * T * 64 * 4 * 2))))
+    kv = [(rt.open_buffer((B, H, T, 64)), rt.open_buffer((B, H, T, 64))) for _ in range(copies)]
+    rng = np.random.Generator(np.random.PCG64(0))
+    qkv = rt.transfer_from_array(rng.standard_normal((B, 3 * d), dtype=np.float32))
+    for i in range(a.warmup):
+        rt.attention(qkv, *kv[i % copies], B, 1, n).close()
+    rt.profile_begin(["attn_decode"])
+    for i in range(a.iters):
+        rt.attention(qkv, *kv[i % copies], B, 1, n).close()
+    ms, calls = rt.profile_end()["attn_decode"]
+    nbytes = B * 2 * (n + 1) * d * 4.0
+    hbm, _ = _peak()
+    return {"kernel": "attn_decode_kernel", "batch": B, "heads": H, "context": n + 1, "us": 1e3 * ms / calls,
+            "algorithmic_bytes": nbytes, "GB/s": nbytes / (ms / calls / 1e3) / 1e9, "frac_of_measured_hbm": nbytes / (ms / calls / 1e3) / 1e9 / hbm}
+
+
+def gemv(rt, a):
+    p = S.GPT2_SIZES[a.model]
+    d = p.dim
+    rng = np.random.Generator(np.random.PCG64(0))
+    hbm, _ = _peak()
+    out = {}
+    for name, rows, cols in (("c_attn", 3 * d, d), ("attn.c_proj", d, d), ("c_fc", 4 * d, d), ("mlp.c_proj", d, 4 * d), ("lm_head", p.vocab_size, d)):
+        one = S._rand_packed(rng, rows, cols, a.wtype) if a.wtype != "f32" else rng.standard_normal((rows, cols), dtype=np.float32)
+        w0 = rt.upload_weight(one)
+        copies = max(2, min(48, int(np.ceil(300e6 / w0.packed_nbytes))))
+        ws = [w0] + [rt.upload_weight(one) for _ in range(copies - 1)]
+        x = rt.transfer_from_array(rng.standard_normal((1, cols), dtype=np.float32))
+        y = rt.open_buffer((1, rows))
+        for i in range(copies):
+            rt.linear(ws[i], x, out=y)
+        rt.profile_begin(["gemv"])
+        for i in range(a.iters):
+            rt.linear(ws[i % copies], x, out=y)
+        ms, calls = rt.profile_end()["gemv"]
+        per = ms / calls / 1e3
+        out[f"{name} {rows}x{cols}"] = {"us": per * 1e6, "GB/s": w0.packed_nbytes / per / 1e9, "frac_of_measured_hbm": w0.packed_nbytes / per / 1e9 / hbm}
+        for w in ws:
+            w.close()
+    return {"kernel": "gemv", "model": a.model, "wtype": a.wtype, "shapes": out}
+
+
+def gemm(rt, a):
+    rng = np.random.Generator(np.random.PCG64(0))
+    one = S._rand_packed(rng, a.n, a.k, a.wtype) if a.wtype != "f32" else rng.standard_normal((a.n, a.k), dtype=np.float32)
+    w0 = rt.upload_weight(one)
+    copies = max(2, min(48, int(np.ceil(300e6 / w0.packed_nbytes))))
+    ws = [w0] + [rt.upload_weight(one) for _ in range(copies - 1)]
+    x = rt.transfer_from_array(rng.standard_normal((a.rows, a.k), dtype=np.float32))
+    y = rt.open_buffer((a.rows, a.n))
+    prec = L.PRECISIONS[a.precision]
+    for i in range(min(copies, 4)):
+        rt.linear(ws[i], x, None, None, L.ACT_NONE, prec, out=y)
+    rt.profile_begin(["gemm"])
+    for i in range(a.iters):
+        rt.linear(ws[i % copies], x, None, None, L.ACT_NONE, prec, out=y)
+    ms, calls = rt.profile_end()["gemm"]
+    per = ms / calls / 1e3
+    flops = 2.0 * a.rows * a.n * a.k
+    _, tf = _peak()
+    return {"kernel": "gemm", "rows": a.rows, "n": a.n, "k": a.k, "wtype": a.wtype, "precision": a.precision, "us": per * 1e6,
+            "useful_TFLOP/s": flops / per / 1e12, "frac_of_measured_bf16": flops / per / 1e12 / tf,
+            "weight_GB/s": w0.packed_nbytes / per / 1e9}
+
+
+def relu_matmul(rt, a):
+    A, B = S.synth_relu_gemm(seed=1)
+    da, db = rt.transfer_from_array(A), rt.transfer_from_array(B)
+    prec = L.PRECISIONS[a.precision]
+    for _ in range(a.warmup):
+        rt.relu_matmul(da, db, prec).close()
+    rt.profile_begin(["gemm"])
+    for _ in range(a.iters):
+        rt.relu_matmul(da, db, prec).close()
+    ms, calls = rt.profile_end()["gemm"]
+    per = ms / calls / 1e3
+    flops = 2.0 * 4096 * 768 * 3072
+    _, tf = _peak()
+    return {"kernel": "relu_matmul 4096x768x3072", "precision": a.precision, "us": per * 1e6, "useful_TFLOP/s": flops / per / 1e12,
+            "frac_of_measured_bf16": flops / per / 1e12 / tf}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["attn_decode", "gemv", "gemm", "relu_matmul"])
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--heads", type=int, default=25)
+    ap.add_argument("--context", type=int, default=700)
+    ap.add_argument("--model", default="gpt2-xl")
+    ap.add_argument("--wtype", default="q4_0", choices=["q4_0", "q8_0", "f32"])
+    ap.add_argument("--rows", type=int, default=256)
+    ap.add_argument("--n", type=int, default=1600)
+    ap.add_argument("--k", type=int, default=6400)
+    ap.add_argument("--precision", default="bf16x3", choices=["fp32", "bf16", "bf16x3"])
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+    with B200Runtime(0) as rt:
+        print(json.dumps({"attn_decode": attn_decode, "gemv": gemv, "gemm": gemm, "relu_matmul": relu_matmul}[a.what](rt, a)))
+
+
+if __name__ == "__main__":
+    main()

@@ -193,7 +193,7 @@ def test_gemm_fp32_is_bit_exact(rt, oracle, wtype, M, N, K):
     w.close()
 
 
-TC_CASES = [("q4_0", 8, 128, 64), ("q4_0", 5, 200, 128), ("q4_0", 64, 4800, 1600), ("q8_0", 33, 130, 192),
+TC_CASES = [("q4_0", 256, 1600, 6400), ("q4_0", 32, 1600, 1600), ("q4_0", 8, 128, 64), ("q4_0", 5, 200, 128), ("q4_0", 64, 4800, 1600), ("q8_0", 33, 130, 192),
             ("f32", 130, 256, 128), ("f16", 17, 128, 64), ("q4_0", 300, 384, 256), ("q8_0", 256, 256, 768)]
 
 
@@ -218,6 +218,20 @@ def test_gemm_tensor_core(rt, oracle, wtype, M, N, K, prec):
     tol = 2e-2 if prec == "bf16" else 1e-4   # relative to the largest output
     assert np.abs(got_lin - ref_lin).max() <= tol * np.abs(ref_lin).max()
     assert np.abs(got - ref).max() <= tol * max(1.0, np.abs(ref).max())
+    w.close()
+
+
+def test_gemm_tensor_core_split_k_is_deterministic(rt):
+    """Few output tiles and a long inner dimension: several CTAs share a tile (split-K) and the
+    last one to finish adds the partial tiles in a fixed order, so repeated runs give equal bits."""
+    rng = np.random.Generator(np.random.PCG64(33))
+    up, _, _ = make_weight(rng, 256, 6400, "q4_0")
+    w = rt.upload_weight(up)
+    dx = rt.transfer_from_array(rng.standard_normal((64, 6400), dtype=np.float32))
+    first = rt.linear(w, dx, None, None, L.ACT_NONE, L.PREC_BF16X3).numpy()
+    for _ in range(5):
+        again = rt.linear(w, dx, None, None, L.ACT_NONE, L.PREC_BF16X3).numpy()
+        np.testing.assert_array_equal(first.view(np.uint32), again.view(np.uint32))
     w.close()
 
 
