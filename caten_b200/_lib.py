@@ -64,6 +64,7 @@ SIGNATURES = {
     "caten_b200_weight_nbytes": (_i64, [C.c_int, _i64, _i64]),
     "caten_b200_weight_dequant": (C.c_int, [_vp, _vp, _vp]),
     "caten_b200_linear": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int, _vp, _i64, C.c_int]),
+    "caten_b200_linear_noalloc": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int, _vp, _i64, C.c_int]),
     "caten_b200_relu_matmul": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, C.c_int]),
     "caten_b200_layernorm": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, C.c_float]),
     "caten_b200_embed": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64]),

@@ -319,6 +319,29 @@ int caten_b200_linear(caten_b200_ctx *ctx, const caten_b200_weight *w, const flo
   return fail(ctx, CATEN_B200_EINVAL, "linear: unknown precision %d", precision);
 }
 
+int caten_b200_linear_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *d_x, const float *d_bias,
+                              const float *d_residual, int act, float *d_y, int64_t M, int precision) {
+  NEED_CTX(ctx);
+  if (!w || !d_x || !d_y) return fail(ctx, CATEN_B200_EINVAL, "linear_noalloc: NULL argument");
+  if (M < 0) return fail(ctx, CATEN_B200_EINVAL, "linear_noalloc: M < 0");
+  if (M == 0) return 0;
+  if (act < 0 || act > 2) return fail(ctx, CATEN_B200_EINVAL, "linear_noalloc: unknown activation %d", act);
+  if (!aligned16(d_x) || !aligned16(d_y)) return fail(ctx, CATEN_B200_EINVAL, "linear_noalloc: x and y must be 16-byte aligned");
+  if (M <= 4) {  // the dequant-GEMV uses no scratch memory
+    for (int64_t m = 0; m < M; ++m)
+      if (int rc = launch_gemv(ctx, w, d_x + m * w->cols, d_bias, d_residual ? d_residual + m * w->rows : nullptr, act,
+                               d_y + m * w->rows))
+        return rc;
+    return 0;
+  }
+  switch (precision) {
+    case CATEN_B200_PREC_FP32: return launch_gemm_simt(ctx, w, d_x, d_bias, d_residual, act, d_y, M);  // no scratch either
+    case CATEN_B200_PREC_BF16: return launch_gemm_tc_noalloc(ctx, w, d_x, d_bias, d_residual, act, d_y, M, 1);
+    case CATEN_B200_PREC_BF16X3: return launch_gemm_tc_noalloc(ctx, w, d_x, d_bias, d_residual, act, d_y, M, 3);
+  }
+  return fail(ctx, CATEN_B200_EINVAL, "linear_noalloc: unknown precision %d", precision);
+}
+
 int caten_b200_relu_matmul(caten_b200_ctx *ctx, const float *d_a, const float *d_b, float *d_c, int64_t M, int64_t K,
                            int64_t N, int precision) {
   NEED_CTX(ctx);

@@ -88,6 +88,8 @@ int launch_gemm_simt(caten_b200_ctx *ctx, const caten_b200_weight *w, const floa
                      const float *res, int act, float *y, int64_t M);
 int launch_gemm_tc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
                    const float *res, int act, float *y, int64_t M, int nsplit);
+int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
+                           const float *res, int act, float *y, int64_t M, int nsplit);
 // relu(a.b) with b given [K, N] row-major fp32
 int launch_relu_matmul_simt(caten_b200_ctx *ctx, const float *a, const float *b, float *c, int64_t M, int64_t K, int64_t N);
 int launch_relu_matmul_tc(caten_b200_ctx *ctx, const float *a, const float *b, float *c, int64_t M, int64_t K,

@@ -631,6 +631,109 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
   return 0;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Variant for callers that must not allocate: the same kernels, with the bf16 copy of the
+// activations and the split-K partial tiles placed in a buffer that is part of the library image
+// instead of a grow-on-demand cudaMalloc.  Every GPU that loads the library holds the buffer
+// until the process exits.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t FIXED_SCRATCH_BYTES = (size_t)32 << 20;  // 32 MiB
+static __device__ __align__(256) unsigned char g_fixed_scratch[FIXED_SCRATCH_BYTES];
+
+// The array's name is only a stand-in on the host; its device address is looked up once per
+// device (with that device current) and cached.
+static int fixed_scratch_ptr(caten_b200_ctx *ctx, uint8_t **out) {
+  static uint8_t *cached[64] = {nullptr};
+  if (ctx->device < 0 || ctx->device >= 64) return fail(ctx, CATEN_B200_EUNSUPPORTED, "linear_noalloc: device index %d", ctx->device);
+  if (!cached[ctx->device]) {
+    void *p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_fixed_scratch);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaGetSymbolAddress(g_fixed_scratch)");
+    cached[ctx->device] = (uint8_t *)p;
+  }
+  *out = cached[ctx->device];
+  return 0;
+}
+
+int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
+                           const float *res, int act, float *y, int64_t M, int nsplit) {
+  const int64_t N = w->rows, K = w->cols;
+  if (M <= 0 || N <= 0) return 0;
+  if (!ctx->encode_tiled) return fail(ctx, CATEN_B200_ECUDA, "linear_noalloc: cuTensorMapEncodeTiled is not available");
+  if (K % TC_BK) return fail(ctx, CATEN_B200_EUNSUPPORTED, "linear_noalloc: inner dimension %lld is not a multiple of 64", (long long)K);
+  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "linear_noalloc: dimension too large");
+  if (nsplit != 1 && nsplit != 3) return fail(ctx, CATEN_B200_EINVAL, "linear_noalloc: nsplit must be 1 or 3");
+  uint8_t *base = nullptr;
+  if (int rc = fixed_scratch_ptr(ctx, &base)) return rc;
+
+  int bnx = 16;
+  while (bnx < 256 && bnx < M) bnx *= 2;
+  const size_t stage = (size_t)(TC_WBYTES + bnx * 128) * (nsplit == 3 ? 2 : 1);
+  int stages = (int)((200 * 1024) / stage);
+  if (stages > 8) stages = 8;
+  if (stages > K / TC_BK) stages = (int)(K / TC_BK);
+  if (stages < 1) stages = 1;
+  const int64_t gy = (M + bnx - 1) / bnx, gx = (N + TC_BM - 1) / TC_BM, tiles = gx * gy;
+  if (gy > 65535) return fail(ctx, CATEN_B200_EUNSUPPORTED, "linear_noalloc: too many rows for one launch (%lld)", (long long)M);
+  const int num_k = (int)(K / TC_BK);
+  int splits = 1;
+  if (tiles < ctx->sm_count) {
+    const int by_work = num_k / 4 > 0 ? num_k / 4 : 1, by_fill = (int)(ctx->sm_count / tiles);
+    splits = by_work < by_fill ? by_work : by_fill;
+    if (splits > 32) splits = 32;
+  }
+  const int cps = (num_k + splits - 1) / splits;
+  splits = (num_k + cps - 1) / cps;
+
+  // layout of the fixed buffer: [x_hi | x_lo (split-bf16 only) | split-K partial tiles]
+  const size_t xb_al = ((size_t)M * K * 2 + 1023) & ~(size_t)1023;
+  const size_t x_total = xb_al * (nsplit == 3 ? 2 : 1);
+  const size_t part_bytes = splits > 1 ? (size_t)splits * tiles * bnx * TC_BM * sizeof(float) : 0;
+  if (x_total + part_bytes > FIXED_SCRATCH_BYTES)
+    return fail(ctx, CATEN_B200_EUNSUPPORTED,
+                "linear_noalloc: M=%lld x %lldx%lld needs %zu bytes of scratch, the built-in buffer holds %zu; use caten_b200_linear",
+                (long long)M, (long long)N, (long long)K, x_total + part_bytes, FIXED_SCRATCH_BYTES);
+  uint8_t *xhi = base, *xlo = nsplit == 3 ? base + xb_al : nullptr;
+  // nothing in the buffer has to start at zero: the used part of x_hi/x_lo and every partial tile
+  // that the reduce reads are fully overwritten by this call before they are read
+  const int64_t n4 = M * K / 4;
+  split_bf16_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, ctx->stream>>>((const float4 *)x, (uint2 *)xhi, (uint2 *)xlo, n4);
+  CB_LAUNCH_CHECK(ctx, "split_bf16_kernel");
+  CUtensorMap mh, ml;
+  if (int rc = make_x_map(ctx, &mh, xhi, M, K, bnx)) return rc;
+  if (int rc = make_x_map(ctx, &ml, nsplit == 3 ? xlo : xhi, M, K, bnx)) return rc;
+
+  TcArgs a;
+  a.qs = w->qs; a.d = w->d; a.bias = bias; a.res = res; a.y = y; a.status = ctx->d_status; a.act = act;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.nkb = (int)w->nkb; a.bnx = bnx;
+  a.stages = stages > cps ? cps : stages;
+  a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bnx >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+  a.tmem_cols = bnx < 32 ? 32u : (uint32_t)bnx;
+  a.splits = splits; a.cps = cps;
+  a.part = splits > 1 ? (float *)(base + x_total) : nullptr;
+  const size_t smem = 1024 + stage * stages + (3 * stages + 1) * 8 + 32;
+  const dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)splits);
+  int rc = CATEN_B200_EUNSUPPORTED;
+#define TC_CASE(WT)                                                              \
+  case WT:                                                                       \
+    rc = nsplit == 3 ? launch_tc_t<WT, 3>(ctx, mh, ml, a, grid, smem) : launch_tc_t<WT, 1>(ctx, mh, ml, a, grid, smem); \
+    break
+  switch (w->type) {
+    TC_CASE(CATEN_B200_F32);
+    TC_CASE(CATEN_B200_F16);
+    TC_CASE(CATEN_B200_Q4_0);
+    TC_CASE(CATEN_B200_Q8_0);
+    default: return fail(ctx, CATEN_B200_EUNSUPPORTED, "linear_noalloc: weight type %d", w->type);
+  }
+#undef TC_CASE
+  if (rc || splits == 1) return rc;
+  const int64_t total = tiles * bnx * TC_BM;
+  splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(a.part, splits, (int)gx, (int)tiles, bnx, bias, res, y,
+                                                                              act, (int)M, (int)N);
+  CB_LAUNCH_CHECK(ctx, "splitk_reduce_kernel");
+  return 0;
+}
+
 int launch_gemm_tc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
                    const float *res, int act, float *y, int64_t M, int nsplit) {
   return run_tc(ctx, w->type, w->qs, w->d, w->nkb, x, bias, res, act, y, M, w->rows, w->cols, nsplit);

@@ -172,6 +172,19 @@ class B200Runtime:
                                                      residual.ptr if residual else None, act, y.ptr, M, precision))
         return y
 
+    def linear_noalloc(self, w: B200Weight, x: B200Buffer, out: B200Buffer, bias: Optional[B200Buffer] = None,
+                       residual: Optional[B200Buffer] = None, act: int = L.ACT_NONE, precision: int = L.PREC_BF16X3) -> B200Buffer:
+        """``linear`` for callers that must not trigger an allocation: the caller supplies ``out`` and
+        the library keeps its working memory in a fixed 32 MiB buffer of its own image
+        (``caten_b200_linear_noalloc``).  Larger working sets raise ``B200Error`` (EUNSUPPORTED).
+        Calls that may overlap on the GPU share that buffer and must be serialised by the caller."""
+        M = int(np.prod(x.shape[:-1], dtype=np.int64))
+        if x.shape[-1] != w.cols or out.shape[-1] != w.rows:
+            raise ValueError("linear_noalloc: shape mismatch")
+        L.check(self.ctx, self.lib.caten_b200_linear_noalloc(self.ctx, w.handle, x.ptr, bias.ptr if bias else None,
+                                                             residual.ptr if residual else None, act, out.ptr, M, precision))
+        return out
+
     def relu_matmul(self, a: B200Buffer, b: B200Buffer, precision: int = L.PREC_BF16X3) -> B200Buffer:
         (M, K), (K2, N) = a.shape, b.shape
         if K != K2:

@@ -113,6 +113,25 @@ int caten_b200_weight_dequant(caten_b200_ctx *ctx, const caten_b200_weight *w, f
 int caten_b200_linear(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *d_x,
                       const float *d_bias, const float *d_residual, int act, float *d_y, int64_t M,
                       int precision);
+/* (No counterpart in the reference.)  caten_b200_linear for hosts that cannot let the library
+ * allocate: a runtime whose memory planner accounts for every device buffer up front, a serving
+ * loop that cannot afford cudaMalloc/cudaFree (both can synchronise the whole device) between
+ * tokens, or a process that has sized its KV cache to fill HBM so that a late allocation may
+ * simply fail.  Same arguments and results as caten_b200_linear; the difference is where the
+ * tensor-core path keeps its working memory (the bf16 copy of x and the split-K partial tiles):
+ * in a 32 MiB buffer that is part of the library image (resident on every GPU that loads the
+ * library until the process exits) instead of a buffer grown with cudaMalloc.  The call makes
+ * no allocation of any kind.
+ *   - Shapes whose working set exceeds 32 MiB are refused with CATEN_B200_EUNSUPPORTED and a
+ *     message stating the bytes needed (M x cols x 2 B, doubled for BF16X3, plus partial tiles);
+ *     e.g. 256 rows of a 1600 x 6400 weight in BF16X3 fit, 8192 rows do not.
+ *   - The first call on a device looks up the buffer's address (and loads the kernels); make
+ *     that call before any stream capture begins.
+ *   - All calls on a device share the one buffer, whatever context or stream they use: calls
+ *     whose GPU work may overlap race on it. Nothing in it needs to be zero beforehand. */
+int caten_b200_linear_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *d_x,
+                              const float *d_bias, const float *d_residual, int act, float *d_y,
+                              int64_t M, int precision);
 /* `(!relu (!matmul a b))` with a [M,K] and b [K,N], both row-major fp32 (Readme.md:55-60):
  * c = max(a.b, 0).  precision as above (FP32 or BF16X3 keep the reference's 1e-5 tolerance). */
 int caten_b200_relu_matmul(caten_b200_ctx *ctx, const float *d_a, const float *d_b, float *d_c,
