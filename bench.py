@@ -135,6 +135,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="xl-q4_0-b256", choices=sorted(WORKLOADS))
     ap.add_argument("--precision", default="bf16x3", choices=["fp32", "bf16", "bf16x3"])
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"], help="replay decode steps from a CUDA graph (auto: when the per-GPU batch is <= 64)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill/GEMV/kernel-breakdown side measurements")
     args = ap.parse_args()
@@ -246,24 +247,44 @@ def main():
         return cur, nxt
 
     # ---- timed region 1: device-resident decode
+    # graph mode: one C call per token replaying a captured CUDA graph (what a serving loop uses when
+    # the per-GPU batch is small and kernel launches would otherwise pace the step); eager mode:
+    # one launch per kernel, which lets CUDA events bracket the attention kernel inside the region
+    use_graph = args.graph == "on" or (args.graph == "auto" and nb <= 64)
     hist = rt.open_buffer((W + K, nb), np.int64)
-    rt.lib.caten_b200_h2d(rt.ctx, a.ptr, first_ids.ctypes.data, first_ids.nbytes)
-    cur, nxt = run_device_steps(prompt_len, W, a, b, hist, 0)
+    first_dev = rt.transfer_from_array(first_ids)
+    if use_graph:
+        model.decode_device_buffers(first_dev, prompt_len, max(W, 2), None)   # warm-up; also captures the graph
+        if W:
+            model.decode_device_buffers(first_dev, prompt_len, W, hist)
+        cur = hist.view((W - 1) * nb, (nb,)) if W else first_dev
+    else:
+        rt.lib.caten_b200_h2d(rt.ctx, a.ptr, first_ids.ctypes.data, first_ids.nbytes)
+        cur, nxt = run_device_steps(prompt_len, W, a, b, hist, 0)
     rt.sync(); barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     launches0 = model.launch_count
-    rt.profile_begin(["attn_decode"])
+    if not use_graph:
+        rt.profile_begin(["attn_decode"])
     torch.cuda.synchronize(); barrier()
     e0 = ev()
-    cur, nxt = run_device_steps(prompt_len + W, K, cur, nxt, hist, W)
+    if use_graph:
+        model.decode_device_buffers(cur, prompt_len + W, K, hist.view(W * nb, (K, nb)))
+    else:
+        cur, nxt = run_device_steps(prompt_len + W, K, cur, nxt, hist, W)
     e1 = ev()
     rt.sync(); torch.cuda.synchronize(); barrier()
     dec_ms = max_over_ranks(e0.elapsed_time(e1))
-    prof = rt.profile_end()
     clocks = sampler.stop() if sampler else None
     launches = model.launch_count - launches0
     ids_device_path = hist.numpy()
     value = batch * K / (dec_ms / 1e3)
+    if use_graph:
+        # launches inside a graph cannot be bracketed: time the attention kernel in an eager replay
+        # of the same steps (same inputs, same positions) right after the timed region
+        rt.profile_begin(["attn_decode"])
+        model.decode_device_buffers(cur, prompt_len + W, K, None)
+    prof = rt.profile_end()
 
     # roofline of the attention-decode kernel: average context over the timed steps
     attn_ms, attn_calls = prof.get("attn_decode", (0.0, 0))
@@ -275,6 +296,7 @@ def main():
     roofline = {"bound": "hbm", "kernel": "attn_decode_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": (achieved / peak) if achieved else None, "traffic": None, "peak_source": peak_src,
                 "bytes_per_launch": attn_bytes, "avg_launch_us": attn_avg_s * 1e6, "launches_timed": attn_calls,
+                "timed_in": "eager replay of the timed steps (graph mode)" if use_graph else "the timed region",
                 "share_of_step": (attn_ms / (dec_ms)) if dec_ms else None}
     # whole-step algorithmic bytes (weights once + KV read + small terms), for context
     d, Ln, V = params.dim, params.n_layers, params.vocab_size
@@ -307,6 +329,7 @@ def main():
     if not args.no_extras:
         # per-class breakdown of a few decode steps (all classes timed; not part of `value`)
         rt.lib.caten_b200_h2d(rt.ctx, a.ptr, first_ids.ctypes.data, first_ids.nbytes)
+        rt.sync()
         rt.profile_begin(None)
         run_device_steps(prompt_len + W, min(K, 8), a, b)
         br = rt.profile_end()
@@ -361,7 +384,7 @@ def main():
                 "dtype": "f32 (attention, LayerNorm, accumulation); linears " + {"fp32": "f32", "bf16": "bf16 operands", "bf16x3": "split-bf16 operands (3 products)"}[args.precision] + " on tcgen05",
                 "data": "synthetic",
                 "config": {**config, "parallelism": f"batch-sharded x{world}, weights replicated", "local_batch": nb, "precision": args.precision,
-                           "context_tokens": [prompt_len + W + 1, prompt_len + W + K],
+                           "context_tokens": [prompt_len + W + 1, prompt_len + W + K], "cuda_graph": use_graph,
                            "l2": "inputs larger than L2: every step re-reads the whole KV cache and all weights (>= hundreds of MB)"},
                 "roofline": roofline, "whole_step": {"algorithmic_bytes": step_bytes, "frac_of_hbm_peak": step_frac},
                 "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,

@@ -74,6 +74,7 @@ SIGNATURES = {
     "caten_b200_gpt2_destroy": (C.c_int, [_vp]),
     "caten_b200_gpt2_step": (C.c_int, [_vp, _vp, _i64, _i64, _vp]),
     "caten_b200_gpt2_step_device": (C.c_int, [_vp, _vp, _vp, _i64, _i64, _vp]),
+    "caten_b200_gpt2_decode": (C.c_int, [_vp, _vp, _i64, _i64, _vp]),
     "caten_b200_gpt2_logits": (_vp, [_vp]),
     "caten_b200_gpt2_kv": (C.c_int, [_vp, C.c_int, _PFP, _PFP]),
     "caten_b200_gpt2_launch_count": (_i64, [_vp]),

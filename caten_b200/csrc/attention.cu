@@ -19,7 +19,8 @@ constexpr float kInvLn2 = 1.0f / 0.6931472f;  // (/ (log 2)) in single float, ap
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) attn_decode_kernel(const float *__restrict__ qkv, float *__restrict__ kc,
                                                           float *__restrict__ vc, float *__restrict__ out, int H,
-                                                          int T, int n) {
+                                                          int T, int n, const int *__restrict__ d_n) {
+  if (d_n) n = *d_n;  // position kept on the device (decode replayed from a CUDA graph)
   extern __shared__ float smem[];
   float *q = smem;            // 64
   float *part = smem + 64;    // 16 x 64
@@ -273,19 +274,21 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
 }
 
 int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc, float *out, int64_t B, int64_t s,
-                     int64_t n, int64_t H, int64_t T) {
+                     int64_t n, int64_t H, int64_t T, const int *d_n) {
   if (B <= 0 || s <= 0) return 0;
   if (n < 0 || n + s > T) return fail(ctx, CATEN_B200_EINVAL, "attention: positions [%lld,%lld) outside the cache (T=%lld)", (long long)n, (long long)(n + s), (long long)T);
   if (H > 65535 || B > 65535) return fail(ctx, CATEN_B200_EUNSUPPORTED, "attention: B or H > 65535");
   if (s == 1) {
-    const size_t smem = (64 + 1024 + 32 + (size_t)(n + 1)) * sizeof(float);
+    // with a device-side position the launch is sized for the longest context the cache allows
+    const size_t smem = (64 + 1024 + 32 + (size_t)(d_n ? T : n + 1)) * sizeof(float);
     if (smem > 200 * 1024) return fail(ctx, CATEN_B200_EUNSUPPORTED, "attention: context too long for the decode kernel");
     if (smem > 48 * 1024)
       CB_CUDA(ctx, cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attn_decode_kernel<<<dim3((unsigned)H, (unsigned)B), 256, smem, ctx->stream>>>(qkv, kc, vc, out, (int)H, (int)T, (int)n);
+    attn_decode_kernel<<<dim3((unsigned)H, (unsigned)B), 256, smem, ctx->stream>>>(qkv, kc, vc, out, (int)H, (int)T, (int)n, d_n);
     CB_LAUNCH_CHECK(ctx, "attn_decode_kernel");
     return 0;
   }
+  if (d_n) return fail(ctx, CATEN_B200_EINVAL, "attention: a device-side position is only supported for single-token steps");
   kv_append_kernel<<<(unsigned)(B * s), 128, 0, ctx->stream>>>(qkv, kc, vc, (int)s, (int)n, (int)H, (int)T);
   CB_LAUNCH_CHECK(ctx, "kv_append_kernel");
   const size_t smem = 4 * 64 * PF_LD * sizeof(float);

@@ -406,6 +406,13 @@ struct caten_b200_gpt2 {
   float *h_ids_pinned = nullptr;
   int64_t *h_out_pinned = nullptr;
   int64_t launches0 = 0;
+  // decode replayed from a CUDA graph: position and ids live on the device
+  int *d_pos = nullptr, *h_pos_pinned = nullptr;
+  int64_t *ids_io = nullptr;   // [B] input ids of the next step
+  int64_t *ids_hist = nullptr; // [T, B] row n = ids produced by the step that started at position n
+  cudaGraphExec_t graph = nullptr;
+  void *graph_xbf = nullptr, *graph_wtmp = nullptr;  // scratch pointers baked into the graph
+  int64_t launches_per_step = 0;
 };
 
 static int linear_any(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
@@ -464,6 +471,10 @@ int caten_b200_gpt2_create(caten_b200_ctx *ctx, const caten_b200_gpt2_desc *dsc,
   if (!rc) rc = alloc(&m->logits, B * V);
   if (!rc) rc = alloc(&m->ids_f32, B * T);
   if (!rc) rc = caten_b200_malloc(ctx, (size_t)B * sizeof(int64_t), (void **)&m->out_ids);
+  if (!rc) rc = caten_b200_malloc(ctx, (size_t)B * sizeof(int64_t), (void **)&m->ids_io);
+  if (!rc) rc = caten_b200_malloc(ctx, (size_t)B * T * sizeof(int64_t), (void **)&m->ids_hist);
+  if (!rc) rc = caten_b200_malloc(ctx, sizeof(int), (void **)&m->d_pos);
+  if (!rc && cudaMallocHost(&m->h_pos_pinned, sizeof(int)) != cudaSuccess) rc = fail(ctx, CATEN_B200_ECUDA, "cudaMallocHost(pos)");
   if (!rc && cudaMallocHost(&m->h_ids_pinned, (size_t)B * T * sizeof(float)) != cudaSuccess) rc = fail(ctx, CATEN_B200_ECUDA, "cudaMallocHost(ids)");
   if (!rc && cudaMallocHost(&m->h_out_pinned, (size_t)B * sizeof(int64_t)) != cudaSuccess) rc = fail(ctx, CATEN_B200_ECUDA, "cudaMallocHost(out ids)");
   if (rc) { caten_b200_gpt2_destroy(m); return rc; }
@@ -481,7 +492,12 @@ int caten_b200_gpt2_destroy(caten_b200_gpt2 *m) {
   for (float *p : m->vc) if (p) cudaFree(p);
   float *bufs[] = {m->h, m->h2, m->xn, m->qkv, m->att, m->ff, m->last, m->logits, m->ids_f32};
   for (float *p : bufs) if (p) cudaFree(p);
+  if (m->graph) cudaGraphExecDestroy(m->graph);
   if (m->out_ids) cudaFree(m->out_ids);
+  if (m->ids_io) cudaFree(m->ids_io);
+  if (m->ids_hist) cudaFree(m->ids_hist);
+  if (m->d_pos) cudaFree(m->d_pos);
+  if (m->h_pos_pinned) cudaFreeHost(m->h_pos_pinned);
   if (m->h_ids_pinned) cudaFreeHost(m->h_ids_pinned);
   if (m->h_out_pinned) cudaFreeHost(m->h_out_pinned);
   delete m;
@@ -490,7 +506,7 @@ int caten_b200_gpt2_destroy(caten_b200_gpt2 *m) {
 
 // Runs the Transformer (external/llm/layers.lisp:81-90) on `nb` sequences [b0, b0+nb) of s tokens.
 static int run_chunk(caten_b200_gpt2 *m, const float *ids_f32, const int64_t *ids_i64, int64_t b0, int64_t nb, int64_t s,
-                     int64_t n) {
+                     int64_t n, const int *d_n = nullptr) {
   caten_b200_ctx *ctx = m->ctx;
   const caten_b200_gpt2_desc &c = m->desc;
   const int64_t d = c.d_model, H = c.n_heads, V = c.vocab, T = c.max_seq_len, L = c.n_layers, R = nb * s;
@@ -500,14 +516,14 @@ static int run_chunk(caten_b200_gpt2 *m, const float *ids_f32, const int64_t *id
   {
     ProfScope prof(ctx, CATEN_B200_K_EMBED);
     if (int rc = launch_embed(ctx, ids_f32 ? ids_f32 + b0 * s : nullptr, ids_i64 ? ids_i64 + b0 * s : nullptr, c.wte, c.wpe,
-                              m->h, nb, s, n, d, V, T))
+                              m->h, nb, s, n, d, V, T, d_n))
       return rc;
   }
   for (int64_t l = 0; l < L; ++l) {
     int rc;
     { ProfScope prof(ctx, CATEN_B200_K_LAYERNORM); rc = launch_layernorm(ctx, m->h, m->ln1_g[l], m->ln1_b[l], m->xn, R, d, eps); }
     if (!rc) rc = linear_any(ctx, m->attn_w[l], m->xn, m->attn_b[l], nullptr, CATEN_B200_ACT_NONE, m->qkv, R, prec);
-    if (!rc) { ProfScope prof(ctx, s == 1 ? CATEN_B200_K_ATTN_DECODE : CATEN_B200_K_ATTN_PREFILL); rc = launch_attention(ctx, m->qkv, m->kc[l] + kv_off, m->vc[l] + kv_off, m->att, nb, s, n, H, T); }
+    if (!rc) { ProfScope prof(ctx, s == 1 ? CATEN_B200_K_ATTN_DECODE : CATEN_B200_K_ATTN_PREFILL); rc = launch_attention(ctx, m->qkv, m->kc[l] + kv_off, m->vc[l] + kv_off, m->att, nb, s, n, H, T, d_n); }
     if (!rc) rc = linear_any(ctx, m->proj_w[l], m->att, m->proj_b[l], m->h, CATEN_B200_ACT_NONE, m->h2, R, prec);
     if (!rc) { ProfScope prof(ctx, CATEN_B200_K_LAYERNORM); rc = launch_layernorm(ctx, m->h2, m->ln2_g[l], m->ln2_b[l], m->xn, R, d, eps); }
     if (!rc) rc = linear_any(ctx, m->fc_w[l], m->xn, m->fc_b[l], nullptr, CATEN_B200_ACT_GELU, m->ff, R, prec);
@@ -557,6 +573,72 @@ int caten_b200_gpt2_step(caten_b200_gpt2 *m, const float *h_ids_f32, int64_t s, 
   CB_CUDA(ctx, cudaMemcpyAsync(m->h_out_pinned, m->out_ids, (size_t)B * sizeof(int64_t), cudaMemcpyDeviceToHost, ctx->stream));
   if (int rc = caten_b200_sync(ctx)) return rc;
   memcpy(h_out_ids, m->h_out_pinned, (size_t)B * sizeof(int64_t));
+  return 0;
+}
+
+// One decode step whose position and ids are read from device memory, so that the identical
+// launch sequence can be replayed from a CUDA graph.
+static int decode_step_device_pos(caten_b200_gpt2 *m, int64_t n_host) {
+  caten_b200_ctx *ctx = m->ctx;
+  const caten_b200_gpt2_desc &c = m->desc;
+  if (int rc = run_chunk(m, nullptr, m->ids_io, 0, c.batch, 1, n_host, m->d_pos)) return rc;
+  if (int rc = linear_any(ctx, c.lm_head, m->last, nullptr, nullptr, CATEN_B200_ACT_NONE, m->logits, c.batch, c.precision)) return rc;
+  if (int rc = launch_argmax(ctx, m->logits, c.batch, c.vocab, m->out_ids)) return rc;
+  return launch_finish_step(ctx, m->out_ids, m->ids_io, m->ids_hist, m->d_pos, c.batch);
+}
+
+int caten_b200_gpt2_decode(caten_b200_gpt2 *m, const int64_t *d_first_ids, int64_t n, int64_t steps, int64_t *d_out_ids) {
+  if (!m) return fail(nullptr, CATEN_B200_EINVAL, "gpt2_decode: model is NULL");
+  caten_b200_ctx *ctx = m->ctx;
+  cudaSetDevice(ctx->device);
+  const caten_b200_gpt2_desc &c = m->desc;
+  const int64_t B = c.batch;
+  if (!d_first_ids) return fail(ctx, CATEN_B200_EINVAL, "gpt2_decode: ids is NULL");
+  if (steps < 0 || n < 0 || n + steps > c.max_seq_len)
+    return fail(ctx, CATEN_B200_EINVAL, "gpt2_decode: positions [%lld, %lld) outside the cache (max_seq_len=%d)", (long long)n, (long long)(n + steps), c.max_seq_len);
+  if (steps == 0) return 0;
+  CB_CUDA(ctx, cudaMemcpyAsync(m->ids_io, d_first_ids, (size_t)B * sizeof(int64_t), cudaMemcpyDeviceToDevice, ctx->stream));
+  *m->h_pos_pinned = (int)n;
+  CB_CUDA(ctx, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+  CB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the pinned word may be rewritten by the next call
+  int64_t done = 0;
+  const bool use_graph = ctx->prof_mask == 0;  // event brackets cannot be placed inside a graph
+  if (use_graph && m->graph && (m->graph_xbf != ctx->xbf.ptr || m->graph_wtmp != ctx->wtmp.ptr)) {
+    cudaGraphExecDestroy(m->graph);  // scratch was re-allocated since the capture: its pointers are stale
+    m->graph = nullptr;
+  }
+  if (use_graph && !m->graph) {
+    // the first step runs eagerly: it sizes the scratch buffers and sets kernel attributes, which
+    // must not happen during capture
+    if (int rc = decode_step_device_pos(m, n)) return rc;
+    done = 1;
+    if (steps > 1) {
+      cudaGraph_t g = nullptr;
+      CB_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+      const int64_t before = ctx->launches;
+      const int rc = decode_step_device_pos(m, n + 1);
+      const cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+      m->launches_per_step = ctx->launches - before;
+      ctx->launches = before;  // captured, not launched
+      if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+      if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaStreamEndCapture");
+      const cudaError_t e2 = cudaGraphInstantiate(&m->graph, g, 0);
+      cudaGraphDestroy(g);
+      if (e2 != cudaSuccess) { m->graph = nullptr; return cuda_fail(ctx, e2, "cudaGraphInstantiate"); }
+      m->graph_xbf = ctx->xbf.ptr;
+      m->graph_wtmp = ctx->wtmp.ptr;
+    }
+  }
+  for (; done < steps; ++done) {
+    if (use_graph && m->graph) {
+      CB_CUDA(ctx, cudaGraphLaunch(m->graph, ctx->stream));
+      ctx->launches += m->launches_per_step;
+    } else if (int rc = decode_step_device_pos(m, n + done)) {
+      return rc;
+    }
+  }
+  if (d_out_ids)
+    CB_CUDA(ctx, cudaMemcpyAsync(d_out_ids, m->ids_hist + n * B, (size_t)(steps * B) * sizeof(int64_t), cudaMemcpyDeviceToDevice, ctx->stream));
   return 0;
 }
 

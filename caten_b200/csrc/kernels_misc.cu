@@ -156,7 +156,8 @@ int launch_layernorm(caten_b200_ctx *ctx, const float *x, const float *g, const 
 // ---------------------------------------------------------------------------------------------
 __global__ void embed_kernel(const float *__restrict__ ids_f32, const int64_t *__restrict__ ids_i64,
                              const float *__restrict__ wte, const float *__restrict__ wpe, float *__restrict__ out,
-                             int64_t s, int64_t n, int d4, int64_t V, int64_t T) {
+                             int64_t s, int64_t n, const int *__restrict__ d_n, int d4, int64_t V, int64_t T) {
+  if (d_n) n = *d_n;  // position kept on the device (decode replayed from a CUDA graph)
   const int64_t r = blockIdx.x;
   int64_t tok = -1;
   if (ids_i64) {
@@ -180,11 +181,11 @@ __global__ void embed_kernel(const float *__restrict__ ids_f32, const int64_t *_
 }
 
 int launch_embed(caten_b200_ctx *ctx, const float *ids_f32, const int64_t *ids_i64, const float *wte,
-                 const float *wpe, float *out, int64_t B, int64_t s, int64_t n, int64_t d, int64_t V, int64_t T) {
+                 const float *wpe, float *out, int64_t B, int64_t s, int64_t n, int64_t d, int64_t V, int64_t T, const int *d_n) {
   if (B * s <= 0) return 0;
   if (d % 4) return fail(ctx, CATEN_B200_EUNSUPPORTED, "embed: d %% 4 != 0");
   if ((ids_f32 == nullptr) == (ids_i64 == nullptr)) return fail(ctx, CATEN_B200_EINVAL, "embed: pass exactly one id array");
-  embed_kernel<<<(unsigned)(B * s), 128, 0, ctx->stream>>>(ids_f32, ids_i64, wte, wpe, out, s, n, (int)(d / 4), V, T);
+  embed_kernel<<<(unsigned)(B * s), 128, 0, ctx->stream>>>(ids_f32, ids_i64, wte, wpe, out, s, n, d_n, (int)(d / 4), V, T);
   CB_LAUNCH_CHECK(ctx, "embed_kernel");
   return 0;
 }
@@ -222,6 +223,26 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ x
     __syncthreads();
   }
   if (threadIdx.x == 0) out[blockIdx.x] = si[0] == V ? 0 : si[0];
+}
+
+// End of a graph-replayed decode step: the new ids become the next step's input, are recorded in
+// the per-position history, and the device-side position advances.
+__global__ void finish_step_kernel(const int64_t *__restrict__ out_ids, int64_t *__restrict__ ids_io,
+                                   int64_t *__restrict__ hist, int *__restrict__ d_pos, int B) {
+  const int pos = *d_pos;
+  for (int b = threadIdx.x; b < B; b += blockDim.x) {
+    const int64_t v = out_ids[b];
+    ids_io[b] = v;
+    hist[(int64_t)pos * B + b] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *d_pos = pos + 1;
+}
+
+int launch_finish_step(caten_b200_ctx *ctx, const int64_t *out_ids, int64_t *ids_io, int64_t *hist, int *d_pos, int64_t B) {
+  finish_step_kernel<<<1, 256, 0, ctx->stream>>>(out_ids, ids_io, hist, d_pos, (int)B);
+  CB_LAUNCH_CHECK(ctx, "finish_step_kernel");
+  return 0;
 }
 
 int launch_argmax(caten_b200_ctx *ctx, const float *x, int64_t rows, int64_t V, int64_t *out) {

@@ -104,20 +104,20 @@ class GPT2:
         L.check(self.rt.ctx, self.rt.lib.caten_b200_gpt2_step_device(self._h, f32, i64, int(s), int(n), out.ptr))
 
     def decode_device(self, first_ids: np.ndarray, start_pos: int, steps: int) -> np.ndarray:
-        """Greedy decode ``steps`` tokens with ids staying on the GPU; returns [batch, steps]."""
-        a = self._dev_ids.view(0, (self.batch, 1))
-        b = self._dev_ids.view(self.batch, (self.batch, 1))
-        ids0 = np.ascontiguousarray(first_ids, dtype=np.int64).reshape(self.batch)
-        L.check(self.rt.ctx, self.rt.lib.caten_b200_h2d(self.rt.ctx, a.ptr, ids0.ctypes.data, ids0.nbytes))
+        """Greedy decode ``steps`` tokens with ids and position staying on the GPU (one C call; the
+        step is replayed from a CUDA graph); returns [batch, steps]."""
+        ids0 = self.rt.transfer_from_array(np.ascontiguousarray(first_ids, dtype=np.int64).reshape(self.batch))
         hist = self.rt.open_buffer((steps, self.batch), np.int64)
-        cur, nxt = a, b
-        for i in range(steps):
-            self.forward_device(cur, 1, start_pos + i, nxt)
-            L.check(self.rt.ctx, self.rt.lib.caten_b200_d2d(self.rt.ctx, hist.ptr + i * self.batch * 8, nxt.ptr, self.batch * 8))
-            cur, nxt = nxt, cur
+        self.decode_device_buffers(ids0, start_pos, steps, hist)
         out = hist.numpy().T.copy()
         hist.close()
+        ids0.close()
         return out
+
+    def decode_device_buffers(self, first_ids: B200Buffer, start_pos: int, steps: int, out: Optional[B200Buffer] = None) -> None:
+        """Asynchronous form of :meth:`decode_device` on device buffers (``out``: [steps, batch] int64)."""
+        L.check(self.rt.ctx, self.rt.lib.caten_b200_gpt2_decode(self._h, first_ids.ptr, int(start_pos), int(steps),
+                                                                out.ptr if out is not None else None))
 
     def logits(self) -> np.ndarray:
         """[batch, vocab] fp32 logits of the last step."""

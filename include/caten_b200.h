@@ -187,6 +187,15 @@ int caten_b200_gpt2_step(caten_b200_gpt2 *m, const float *h_ids_f32, int64_t s, 
  * [B] int64 (may be the next step's d_ids_i64). Asynchronous. */
 int caten_b200_gpt2_step_device(caten_b200_gpt2 *m, const float *d_ids_f32, const int64_t *d_ids_i64,
                                 int64_t s, int64_t n, int64_t *d_out_ids);
+/* `steps` consecutive single-token steps (the body of the loop of apps/gpt2/gpt2.lisp:102-109 after
+ * the prompt) with ids and position kept on the device: step i reads the ids step i-1 produced,
+ * starting from d_first_ids [B] at position n.  The launch sequence of one step is captured in a
+ * CUDA graph on first use and replayed, so the host issues one call per token instead of several
+ * hundred launches.  d_out_ids: NULL or [steps, B] int64 (row i = ids produced by step i).
+ * Asynchronous.  While per-kernel timing is on (caten_b200_profile_begin) the steps are launched
+ * one kernel at a time instead. */
+int caten_b200_gpt2_decode(caten_b200_gpt2 *m, const int64_t *d_first_ids, int64_t n, int64_t steps,
+                           int64_t *d_out_ids);
 /* Device pointer to the [B, V] fp32 logits of the last step (valid until the next step). */
 const float *caten_b200_gpt2_logits(caten_b200_gpt2 *m);
 /* Device pointers to layer l's caches, [B, H, T, 64] fp32. */

@@ -120,6 +120,31 @@ def test_device_resident_decode_matches_host_loop(rt):
     a.close(); b.close()
 
 
+@pytest.mark.parametrize("precision,batch", [("fp32", 1), ("bf16x3", 6)])
+def test_graph_replayed_decode_is_repeatable(rt, precision, batch):
+    """`caten_b200_gpt2_decode` captures the step once and replays it: a second call (graph reuse),
+    a call under per-kernel timing (eager launches) and the host loop must give the same ids."""
+    sd = S.synth_state_dict(TINY, "q8_0", seed=11, max_seq_len=40, trivial_affine=False, weight_std=0.08)
+    prompt = S.synth_prompts(batch, 5, TINY.vocab_size, seed=7)
+    ref = GPT2(rt, TINY, sd, max_seq_len=40, batch=batch, precision=precision)
+    want = gpt2_generate(ref, prompt, max_length=12)[:, 5:]
+    m = GPT2(rt, TINY, sd, max_seq_len=40, batch=batch, precision=precision)
+    first = m.forward(prompt, 5, 0)
+    np.testing.assert_array_equal(first, want[:, 0])
+    a = m.decode_device(first, 5, 11)          # eager first step + capture + replays
+    b = m.decode_device(first, 5, 11)          # replays only
+    rt.profile_begin(["attn_decode"])
+    c = m.decode_device(first, 5, 4)           # eager launches while timing is on
+    prof = rt.profile_end()
+    assert prof["attn_decode"][1] == 4 * TINY.n_layers
+    np.testing.assert_array_equal(a, want[:, 1:])
+    np.testing.assert_array_equal(b, a)
+    np.testing.assert_array_equal(c, a[:, :4])
+    with pytest.raises(B200Error):
+        m.decode_device(first, 38, 5)          # would run past the cache
+    ref.close(); m.close()
+
+
 def test_prefill_in_chunks_equals_one_pass(rt):
     """max_rows forces the prefill to run sequence group by sequence group."""
     sd = S.synth_state_dict(TINY, "q8_0", seed=6, max_seq_len=32, trivial_affine=False, weight_std=0.08)
