@@ -135,7 +135,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="xl-q4_0-b256", choices=sorted(WORKLOADS))
     ap.add_argument("--precision", default="bf16x3", choices=["fp32", "bf16", "bf16x3"])
-    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"], help="replay decode steps from a CUDA graph (auto: when the per-GPU batch is <= 64)")
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"], help="replay decode steps from a CUDA graph (auto = on; off launches kernel by kernel)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill/GEMV/kernel-breakdown side measurements")
     args = ap.parse_args()
@@ -250,7 +250,7 @@ def main():
     # graph mode: one C call per token replaying a captured CUDA graph (what a serving loop uses when
     # the per-GPU batch is small and kernel launches would otherwise pace the step); eager mode:
     # one launch per kernel, which lets CUDA events bracket the attention kernel inside the region
-    use_graph = args.graph == "on" or (args.graph == "auto" and nb <= 64)
+    use_graph = args.graph != "off"
     hist = rt.open_buffer((W + K, nb), np.int64)
     first_dev = rt.transfer_from_array(first_ids)
     if use_graph:

@@ -560,6 +560,8 @@ int caten_b200_gpt2_step_device(caten_b200_gpt2 *m, const float *d_ids_f32, cons
   return launch_argmax(ctx, m->logits, B, c.vocab, d_out_ids);
 }
 
+static int decode_run(caten_b200_gpt2 *m, int64_t n, int64_t steps);
+
 int caten_b200_gpt2_step(caten_b200_gpt2 *m, const float *h_ids_f32, int64_t s, int64_t n, int64_t *h_out_ids) {
   if (!m) return fail(nullptr, CATEN_B200_EINVAL, "gpt2_step: model is NULL");
   caten_b200_ctx *ctx = m->ctx;
@@ -569,7 +571,16 @@ int caten_b200_gpt2_step(caten_b200_gpt2 *m, const float *h_ids_f32, int64_t s, 
   if (s < 1 || s > m->desc.max_seq_len) return fail(ctx, CATEN_B200_EINVAL, "gpt2_step: s=%lld", (long long)s);
   memcpy(m->h_ids_pinned, h_ids_f32, (size_t)(B * s) * sizeof(float));
   CB_CUDA(ctx, cudaMemcpyAsync(m->ids_f32, m->h_ids_pinned, (size_t)(B * s) * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
-  if (int rc = caten_b200_gpt2_step_device(m, m->ids_f32, nullptr, s, n, m->out_ids)) return rc;
+  if (s == 1 && ctx->prof_mask == 0) {
+    // single-token step: the captured graph of the step is replayed (ids and position are loaded
+    // into the device-side state first); the result is the same as the kernel-by-kernel path
+    if (n < 0 || n + 1 > m->desc.max_seq_len)
+      return fail(ctx, CATEN_B200_EINVAL, "gpt2_step: s=1 n=%lld outside the cache (max_seq_len=%d)", (long long)n, m->desc.max_seq_len);
+    if (int rc = launch_begin_steps(ctx, m->ids_f32, nullptr, m->ids_io, m->d_pos, n, B)) return rc;
+    if (int rc = decode_run(m, n, 1)) return rc;
+  } else if (int rc = caten_b200_gpt2_step_device(m, m->ids_f32, nullptr, s, n, m->out_ids)) {
+    return rc;
+  }
   CB_CUDA(ctx, cudaMemcpyAsync(m->h_out_pinned, m->out_ids, (size_t)B * sizeof(int64_t), cudaMemcpyDeviceToHost, ctx->stream));
   if (int rc = caten_b200_sync(ctx)) return rc;
   memcpy(h_out_ids, m->h_out_pinned, (size_t)B * sizeof(int64_t));
@@ -587,20 +598,11 @@ static int decode_step_device_pos(caten_b200_gpt2 *m, int64_t n_host) {
   return launch_finish_step(ctx, m->out_ids, m->ids_io, m->ids_hist, m->d_pos, c.batch);
 }
 
-int caten_b200_gpt2_decode(caten_b200_gpt2 *m, const int64_t *d_first_ids, int64_t n, int64_t steps, int64_t *d_out_ids) {
-  if (!m) return fail(nullptr, CATEN_B200_EINVAL, "gpt2_decode: model is NULL");
+// Runs `steps` single-token steps from the device-side state (ids_io, d_pos already loaded).
+// The launch sequence of a step is captured into a CUDA graph the first time and replayed.
+static int decode_run(caten_b200_gpt2 *m, int64_t n, int64_t steps) {
   caten_b200_ctx *ctx = m->ctx;
-  cudaSetDevice(ctx->device);
-  const caten_b200_gpt2_desc &c = m->desc;
-  const int64_t B = c.batch;
-  if (!d_first_ids) return fail(ctx, CATEN_B200_EINVAL, "gpt2_decode: ids is NULL");
-  if (steps < 0 || n < 0 || n + steps > c.max_seq_len)
-    return fail(ctx, CATEN_B200_EINVAL, "gpt2_decode: positions [%lld, %lld) outside the cache (max_seq_len=%d)", (long long)n, (long long)(n + steps), c.max_seq_len);
-  if (steps == 0) return 0;
-  CB_CUDA(ctx, cudaMemcpyAsync(m->ids_io, d_first_ids, (size_t)B * sizeof(int64_t), cudaMemcpyDeviceToDevice, ctx->stream));
-  *m->h_pos_pinned = (int)n;
-  CB_CUDA(ctx, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
-  CB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the pinned word may be rewritten by the next call
+  const int64_t T = m->desc.max_seq_len;
   int64_t done = 0;
   const bool use_graph = ctx->prof_mask == 0;  // event brackets cannot be placed inside a graph
   if (use_graph && m->graph && (m->graph_xbf != ctx->xbf.ptr || m->graph_wtmp != ctx->wtmp.ptr)) {
@@ -612,22 +614,20 @@ int caten_b200_gpt2_decode(caten_b200_gpt2 *m, const int64_t *d_first_ids, int64
     // must not happen during capture
     if (int rc = decode_step_device_pos(m, n)) return rc;
     done = 1;
-    if (steps > 1) {
-      cudaGraph_t g = nullptr;
-      CB_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
-      const int64_t before = ctx->launches;
-      const int rc = decode_step_device_pos(m, n + 1);
-      const cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
-      m->launches_per_step = ctx->launches - before;
-      ctx->launches = before;  // captured, not launched
-      if (rc) { if (g) cudaGraphDestroy(g); return rc; }
-      if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaStreamEndCapture");
-      const cudaError_t e2 = cudaGraphInstantiate(&m->graph, g, 0);
-      cudaGraphDestroy(g);
-      if (e2 != cudaSuccess) { m->graph = nullptr; return cuda_fail(ctx, e2, "cudaGraphInstantiate"); }
-      m->graph_xbf = ctx->xbf.ptr;
-      m->graph_wtmp = ctx->wtmp.ptr;
-    }
+    cudaGraph_t g = nullptr;
+    CB_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    const int64_t before = ctx->launches;
+    const int rc = decode_step_device_pos(m, n + 1 < T ? n + 1 : T - 1);  // host-side position only feeds argument checks
+    const cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+    m->launches_per_step = ctx->launches - before;
+    ctx->launches = before;  // captured, not launched
+    if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaStreamEndCapture");
+    const cudaError_t e2 = cudaGraphInstantiate(&m->graph, g, 0);
+    cudaGraphDestroy(g);
+    if (e2 != cudaSuccess) { m->graph = nullptr; return cuda_fail(ctx, e2, "cudaGraphInstantiate"); }
+    m->graph_xbf = ctx->xbf.ptr;
+    m->graph_wtmp = ctx->wtmp.ptr;
   }
   for (; done < steps; ++done) {
     if (use_graph && m->graph) {
@@ -637,6 +637,21 @@ int caten_b200_gpt2_decode(caten_b200_gpt2 *m, const int64_t *d_first_ids, int64
       return rc;
     }
   }
+  return 0;
+}
+
+int caten_b200_gpt2_decode(caten_b200_gpt2 *m, const int64_t *d_first_ids, int64_t n, int64_t steps, int64_t *d_out_ids) {
+  if (!m) return fail(nullptr, CATEN_B200_EINVAL, "gpt2_decode: model is NULL");
+  caten_b200_ctx *ctx = m->ctx;
+  cudaSetDevice(ctx->device);
+  const caten_b200_gpt2_desc &c = m->desc;
+  const int64_t B = c.batch;
+  if (!d_first_ids) return fail(ctx, CATEN_B200_EINVAL, "gpt2_decode: ids is NULL");
+  if (steps < 0 || n < 0 || n + steps > c.max_seq_len)
+    return fail(ctx, CATEN_B200_EINVAL, "gpt2_decode: positions [%lld, %lld) outside the cache (max_seq_len=%d)", (long long)n, (long long)(n + steps), c.max_seq_len);
+  if (steps == 0) return 0;
+  if (int rc = launch_begin_steps(ctx, nullptr, d_first_ids, m->ids_io, m->d_pos, n, B)) return rc;
+  if (int rc = decode_run(m, n, steps)) return rc;
   if (d_out_ids)
     CB_CUDA(ctx, cudaMemcpyAsync(d_out_ids, m->ids_hist + n * B, (size_t)(steps * B) * sizeof(int64_t), cudaMemcpyDeviceToDevice, ctx->stream));
   return 0;

@@ -80,6 +80,8 @@ int launch_layernorm_strided(caten_b200_ctx *ctx, const float *x, const float *g
 int launch_embed(caten_b200_ctx *ctx, const float *ids_f32, const int64_t *ids_i64, const float *wte,
                  const float *wpe, float *out, int64_t B, int64_t s, int64_t n, int64_t d, int64_t V, int64_t T,
                  const int *d_n = nullptr);
+int launch_begin_steps(caten_b200_ctx *ctx, const float *ids_f32, const int64_t *ids_i64, int64_t *ids_io, int *d_pos,
+                       int64_t n, int64_t B);
 int launch_finish_step(caten_b200_ctx *ctx, const int64_t *out_ids, int64_t *ids_io, int64_t *hist, int *d_pos, int64_t B);
 int launch_argmax(caten_b200_ctx *ctx, const float *x, int64_t rows, int64_t V, int64_t *out);
 int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc, float *out, int64_t B,

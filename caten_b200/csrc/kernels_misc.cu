@@ -239,6 +239,29 @@ __global__ void finish_step_kernel(const int64_t *__restrict__ out_ids, int64_t 
   if (threadIdx.x == 0) *d_pos = pos + 1;
 }
 
+// Start of a run of graph-replayed steps: loads the input ids (int64, or float32 as the reference's
+// caller passes them; an id that is not an integer selects no embedding row, kept as -1) and the
+// start position into the device-side state.
+__global__ void begin_steps_kernel(const float *__restrict__ ids_f32, const int64_t *__restrict__ ids_i64,
+                                   int64_t *__restrict__ ids_io, int *__restrict__ d_pos, int n, int B) {
+  for (int b = threadIdx.x; b < B; b += blockDim.x) {
+    if (ids_i64) {
+      ids_io[b] = ids_i64[b];
+    } else {
+      const float t = ids_f32[b];
+      ids_io[b] = (t >= 0.0f && t < 9.0e15f && truncf(t) == t) ? (int64_t)t : -1;
+    }
+  }
+  if (threadIdx.x == 0) *d_pos = n;
+}
+
+int launch_begin_steps(caten_b200_ctx *ctx, const float *ids_f32, const int64_t *ids_i64, int64_t *ids_io, int *d_pos,
+                       int64_t n, int64_t B) {
+  begin_steps_kernel<<<1, 256, 0, ctx->stream>>>(ids_f32, ids_i64, ids_io, d_pos, (int)n, (int)B);
+  CB_LAUNCH_CHECK(ctx, "begin_steps_kernel");
+  return 0;
+}
+
 int launch_finish_step(caten_b200_ctx *ctx, const int64_t *out_ids, int64_t *ids_io, int64_t *hist, int *d_pos, int64_t B) {
   finish_step_kernel<<<1, 256, 0, ctx->stream>>>(out_ids, ids_io, hist, d_pos, (int)B);
   CB_LAUNCH_CHECK(ctx, "finish_step_kernel");
