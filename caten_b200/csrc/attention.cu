@@ -19,7 +19,8 @@ constexpr float kInvLn2 = 1.0f / 0.6931472f;  // (/ (log 2)) in single float, ap
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) attn_decode_kernel(const float *__restrict__ qkv, float *__restrict__ kc,
                                                           float *__restrict__ vc, float *__restrict__ out, int H,
-                                                          int T, int n, const int *__restrict__ d_n) {
+                                                          int T, int n, const int *__restrict__ d_n,
+                                                          __nv_bfloat16 *__restrict__ ohi, __nv_bfloat16 *__restrict__ olo) {
   if (d_n) n = *d_n;  // position kept on the device (decode replayed from a CUDA graph)
   extern __shared__ float smem[];
   float *q = smem;            // 64
@@ -108,7 +109,14 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float *__restric
     float o = 0.0f;
 #pragma unroll
     for (int w = 0; w < 16; ++w) o += part[w * 64 + tid];
-    out[(int64_t)b * d + h * 64 + tid] = o;
+    const int64_t at = (int64_t)b * d + h * 64 + tid;
+    if (ohi) {  // split bf16 operand of the projection GEMM
+      const __nv_bfloat16 hh = __float2bfloat16_rn(o);
+      ohi[at] = hh;
+      if (olo) olo[at] = __float2bfloat16_rn(o - __bfloat162float(hh));
+    } else {
+      out[at] = o;
+    }
   }
 }
 
@@ -137,7 +145,8 @@ constexpr int PF_LD = 68;  // padded leading dimension of the 64x64 tiles (float
 // transposed ([c][row]) so the inner products read float4s without bank conflicts.
 __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restrict__ qkv, const float *__restrict__ kc,
                                                            const float *__restrict__ vc, float *__restrict__ out,
-                                                           int s, int n, int H, int T) {
+                                                           int s, int n, int H, int T, __nv_bfloat16 *__restrict__ ohi,
+                                                           __nv_bfloat16 *__restrict__ olo) {
   extern __shared__ float smem[];
   float *Qt = smem;                 // [64 c][PF_LD i]
   float *Kt = Qt + 64 * PF_LD;      // [64 c][PF_LD j]
@@ -268,13 +277,20 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
     if (qi < s) {
       const float inv = 1.0f / l_run[a];
       float4 r = make_float4(o[a][0] * inv, o[a][1] * inv, o[a][2] * inv, o[a][3] * inv);
-      *reinterpret_cast<float4 *>(out + ((int64_t)b * s + qi) * d + h * 64 + 4 * tx) = r;
+      const int64_t at = ((int64_t)b * s + qi) * d + h * 64 + 4 * tx;
+      if (ohi) {
+        *reinterpret_cast<uint2 *>(ohi + at) = make_uint2(pack_bf16(r.x, r.y), pack_bf16(r.z, r.w));
+        if (olo)
+          *reinterpret_cast<uint2 *>(olo + at) = make_uint2(pack_bf16(bf16_lo(r.x), bf16_lo(r.y)), pack_bf16(bf16_lo(r.z), bf16_lo(r.w)));
+      } else {
+        *reinterpret_cast<float4 *>(out + at) = r;
+      }
     }
   }
 }
 
 int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc, float *out, int64_t B, int64_t s,
-                     int64_t n, int64_t H, int64_t T, const int *d_n) {
+                     int64_t n, int64_t H, int64_t T, const int *d_n, BfOut bf) {
   if (B <= 0 || s <= 0) return 0;
   if (n < 0 || n + s > T) return fail(ctx, CATEN_B200_EINVAL, "attention: positions [%lld,%lld) outside the cache (T=%lld)", (long long)n, (long long)(n + s), (long long)T);
   if (H > 65535 || B > 65535) return fail(ctx, CATEN_B200_EUNSUPPORTED, "attention: B or H > 65535");
@@ -284,7 +300,7 @@ int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc
     if (smem > 200 * 1024) return fail(ctx, CATEN_B200_EUNSUPPORTED, "attention: context too long for the decode kernel");
     if (smem > 48 * 1024)
       CB_CUDA(ctx, cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attn_decode_kernel<<<dim3((unsigned)H, (unsigned)B), 256, smem, ctx->stream>>>(qkv, kc, vc, out, (int)H, (int)T, (int)n, d_n);
+    attn_decode_kernel<<<dim3((unsigned)H, (unsigned)B), 256, smem, ctx->stream>>>(qkv, kc, vc, out, (int)H, (int)T, (int)n, d_n, bf.hi, bf.lo);
     CB_LAUNCH_CHECK(ctx, "attn_decode_kernel");
     return 0;
   }
@@ -294,7 +310,7 @@ int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc
   const size_t smem = 4 * 64 * PF_LD * sizeof(float);
   CB_CUDA(ctx, cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   attn_prefill_kernel<<<dim3((unsigned)((s + 63) / 64), (unsigned)H, (unsigned)B), 256, smem, ctx->stream>>>(
-      qkv, kc, vc, out, (int)s, (int)n, (int)H, (int)T);
+      qkv, kc, vc, out, (int)s, (int)n, (int)H, (int)T, bf.hi, bf.lo);
   CB_LAUNCH_CHECK(ctx, "attn_prefill_kernel");
   return 0;
 }

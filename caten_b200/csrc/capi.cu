@@ -401,6 +401,10 @@ struct caten_b200_gpt2 {
   int64_t max_rows = 0;
   float *h = nullptr, *h2 = nullptr, *xn = nullptr, *qkv = nullptr, *att = nullptr, *ff = nullptr;
   float *last = nullptr, *logits = nullptr;
+  // split bf16 (hi, lo) copies of the activations that feed tensor-core GEMMs, written directly by
+  // the kernels that produce them (LayerNorm, attention, the GELU epilogue); unused with PREC_FP32
+  cb::BfOut xn_bf, att_bf, ff_bf, last_bf;
+  void *bf_arena = nullptr;
   float *ids_f32 = nullptr;  // staging for host ids [B * T]
   int64_t *out_ids = nullptr;
   float *h_ids_pinned = nullptr;
@@ -414,6 +418,18 @@ struct caten_b200_gpt2 {
   void *graph_xbf = nullptr, *graph_wtmp = nullptr;  // scratch pointers baked into the graph
   int64_t launches_per_step = 0;
 };
+
+// Linear inside the model: with a tensor-core precision and more than 4 rows the input arrives
+// already split into bf16 (hi, lo) from its producer and the output can be requested the same way.
+static int model_linear(caten_b200_gpt2 *m, const caten_b200_weight *w, const float *x, cb::BfOut xbf, const float *bias,
+                        const float *res, int act, float *y, cb::BfOut ybf, int64_t M) {
+  caten_b200_ctx *ctx = m->ctx;
+  const int prec = m->desc.precision;
+  if (prec == CATEN_B200_PREC_FP32 || M <= 4) return caten_b200_linear(ctx, w, x, bias, res, act, y, M, prec);
+  ProfScope prof(ctx, CATEN_B200_K_GEMM);
+  const int nsplit = prec == CATEN_B200_PREC_BF16X3 ? 3 : 1;
+  return launch_gemm_tc_ex(ctx, w, nullptr, xbf.hi, nsplit == 3 ? xbf.lo : nullptr, bias, res, act, y, ybf, M, nsplit);
+}
 
 static int linear_any(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
                       const float *res, int act, float *y, int64_t M, int prec) {
@@ -469,6 +485,19 @@ int caten_b200_gpt2_create(caten_b200_ctx *ctx, const caten_b200_gpt2_desc *dsc,
   if (!rc) rc = alloc(&m->ff, max_rows * 4 * d);
   if (!rc) rc = alloc(&m->last, B * d);
   if (!rc) rc = alloc(&m->logits, B * V);
+  if (!rc && dsc->precision != CATEN_B200_PREC_FP32) {
+    auto al = [](int64_t n) { return (size_t)((n * 2 + 1023) & ~(int64_t)1023); };
+    const size_t sz_d = al(max_rows * d), sz_ff = al(max_rows * 4 * d), sz_last = al(B * d);
+    rc = caten_b200_malloc(ctx, 4 * sz_d + 2 * sz_ff + 2 * sz_last, &m->bf_arena);
+    if (!rc) {
+      uint8_t *p = (uint8_t *)m->bf_arena;
+      auto take = [&](size_t n) { __nv_bfloat16 *q = (__nv_bfloat16 *)p; p += n; return q; };
+      m->xn_bf.hi = take(sz_d); m->xn_bf.lo = take(sz_d);
+      m->att_bf.hi = take(sz_d); m->att_bf.lo = take(sz_d);
+      m->ff_bf.hi = take(sz_ff); m->ff_bf.lo = take(sz_ff);
+      m->last_bf.hi = take(sz_last); m->last_bf.lo = take(sz_last);
+    }
+  }
   if (!rc) rc = alloc(&m->ids_f32, B * T);
   if (!rc) rc = caten_b200_malloc(ctx, (size_t)B * sizeof(int64_t), (void **)&m->out_ids);
   if (!rc) rc = caten_b200_malloc(ctx, (size_t)B * sizeof(int64_t), (void **)&m->ids_io);
@@ -493,6 +522,7 @@ int caten_b200_gpt2_destroy(caten_b200_gpt2 *m) {
   float *bufs[] = {m->h, m->h2, m->xn, m->qkv, m->att, m->ff, m->last, m->logits, m->ids_f32};
   for (float *p : bufs) if (p) cudaFree(p);
   if (m->graph) cudaGraphExecDestroy(m->graph);
+  if (m->bf_arena) cudaFree(m->bf_arena);
   if (m->out_ids) cudaFree(m->out_ids);
   if (m->ids_io) cudaFree(m->ids_io);
   if (m->ids_hist) cudaFree(m->ids_hist);
@@ -519,21 +549,28 @@ static int run_chunk(caten_b200_gpt2 *m, const float *ids_f32, const int64_t *id
                               m->h, nb, s, n, d, V, T, d_n))
       return rc;
   }
+  // tensor-core precisions: producers write the split bf16 operand of the next GEMM themselves
+  const bool fused = prec != CATEN_B200_PREC_FP32 && R > 4;
+  const bool x3 = prec == CATEN_B200_PREC_BF16X3;
+  auto bf = [&](cb::BfOut b) { cb::BfOut o; if (fused) { o.hi = b.hi; o.lo = x3 ? b.lo : nullptr; } return o; };
+  const cb::BfOut none;
   for (int64_t l = 0; l < L; ++l) {
     int rc;
-    { ProfScope prof(ctx, CATEN_B200_K_LAYERNORM); rc = launch_layernorm(ctx, m->h, m->ln1_g[l], m->ln1_b[l], m->xn, R, d, eps); }
-    if (!rc) rc = linear_any(ctx, m->attn_w[l], m->xn, m->attn_b[l], nullptr, CATEN_B200_ACT_NONE, m->qkv, R, prec);
-    if (!rc) { ProfScope prof(ctx, s == 1 ? CATEN_B200_K_ATTN_DECODE : CATEN_B200_K_ATTN_PREFILL); rc = launch_attention(ctx, m->qkv, m->kc[l] + kv_off, m->vc[l] + kv_off, m->att, nb, s, n, H, T, d_n); }
-    if (!rc) rc = linear_any(ctx, m->proj_w[l], m->att, m->proj_b[l], m->h, CATEN_B200_ACT_NONE, m->h2, R, prec);
-    if (!rc) { ProfScope prof(ctx, CATEN_B200_K_LAYERNORM); rc = launch_layernorm(ctx, m->h2, m->ln2_g[l], m->ln2_b[l], m->xn, R, d, eps); }
-    if (!rc) rc = linear_any(ctx, m->fc_w[l], m->xn, m->fc_b[l], nullptr, CATEN_B200_ACT_GELU, m->ff, R, prec);
-    if (!rc) rc = linear_any(ctx, m->mproj_w[l], m->ff, m->mproj_b[l], m->h2, CATEN_B200_ACT_NONE, m->h, R, prec);
+    { ProfScope prof(ctx, CATEN_B200_K_LAYERNORM); rc = launch_layernorm_strided(ctx, m->h, m->ln1_g[l], m->ln1_b[l], m->xn, R, d, eps, 1, bf(m->xn_bf)); }
+    if (!rc) rc = model_linear(m, m->attn_w[l], m->xn, m->xn_bf, m->attn_b[l], nullptr, CATEN_B200_ACT_NONE, m->qkv, none, R);
+    if (!rc) { ProfScope prof(ctx, s == 1 ? CATEN_B200_K_ATTN_DECODE : CATEN_B200_K_ATTN_PREFILL); rc = launch_attention(ctx, m->qkv, m->kc[l] + kv_off, m->vc[l] + kv_off, m->att, nb, s, n, H, T, d_n, bf(m->att_bf)); }
+    if (!rc) rc = model_linear(m, m->proj_w[l], m->att, m->att_bf, m->proj_b[l], m->h, CATEN_B200_ACT_NONE, m->h2, none, R);
+    if (!rc) { ProfScope prof(ctx, CATEN_B200_K_LAYERNORM); rc = launch_layernorm_strided(ctx, m->h2, m->ln2_g[l], m->ln2_b[l], m->xn, R, d, eps, 1, bf(m->xn_bf)); }
+    if (!rc) rc = model_linear(m, m->fc_w[l], m->xn, m->xn_bf, m->fc_b[l], nullptr, CATEN_B200_ACT_GELU, m->ff, bf(m->ff_bf), R);
+    if (!rc) rc = model_linear(m, m->mproj_w[l], m->ff, m->ff_bf, m->mproj_b[l], m->h2, CATEN_B200_ACT_NONE, m->h, none, R);
     if (rc) return rc;
   }
   // ln_f on the last position of every sequence only (the reference views the last row of the
   // logits, layers.lisp:90), gathered into rows [b0, b0+nb) of `last`
   ProfScope prof(ctx, CATEN_B200_K_LAYERNORM);
-  return launch_layernorm_strided(ctx, m->h, c.lnf_g, c.lnf_b, m->last + b0 * d, nb, d, eps, s);
+  cb::BfOut lb;
+  if (prec != CATEN_B200_PREC_FP32 && c.batch > 4) { lb.hi = m->last_bf.hi + b0 * d; lb.lo = x3 ? m->last_bf.lo + b0 * d : nullptr; }
+  return launch_layernorm_strided(ctx, m->h, c.lnf_g, c.lnf_b, m->last + b0 * d, nb, d, eps, s, lb);
 }
 
 int caten_b200_gpt2_step_device(caten_b200_gpt2 *m, const float *d_ids_f32, const int64_t *d_ids_i64, int64_t s, int64_t n,
@@ -555,7 +592,7 @@ int caten_b200_gpt2_step_device(caten_b200_gpt2 *m, const float *d_ids_f32, cons
     if (int rc = run_chunk(m, d_ids_f32, d_ids_i64, b0, nb, s, n)) return rc;
   }
   // lm_head (no bias, layers.lisp:79) + argmax over the vocabulary
-  if (int rc = linear_any(ctx, c.lm_head, m->last, nullptr, nullptr, CATEN_B200_ACT_NONE, m->logits, B, c.precision)) return rc;
+  if (int rc = model_linear(m, c.lm_head, m->last, m->last_bf, nullptr, nullptr, CATEN_B200_ACT_NONE, m->logits, cb::BfOut(), B)) return rc;
   ProfScope prof(ctx, CATEN_B200_K_ARGMAX);
   return launch_argmax(ctx, m->logits, B, c.vocab, d_out_ids);
 }
@@ -593,7 +630,7 @@ static int decode_step_device_pos(caten_b200_gpt2 *m, int64_t n_host) {
   caten_b200_ctx *ctx = m->ctx;
   const caten_b200_gpt2_desc &c = m->desc;
   if (int rc = run_chunk(m, nullptr, m->ids_io, 0, c.batch, 1, n_host, m->d_pos)) return rc;
-  if (int rc = linear_any(ctx, c.lm_head, m->last, nullptr, nullptr, CATEN_B200_ACT_NONE, m->logits, c.batch, c.precision)) return rc;
+  if (int rc = model_linear(m, c.lm_head, m->last, m->last_bf, nullptr, nullptr, CATEN_B200_ACT_NONE, m->logits, cb::BfOut(), c.batch)) return rc;
   if (int rc = launch_argmax(ctx, m->logits, c.batch, c.vocab, m->out_ids)) return rc;
   return launch_finish_step(ctx, m->out_ids, m->ids_io, m->ids_hist, m->d_pos, c.batch);
 }

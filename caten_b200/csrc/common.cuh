@@ -17,6 +17,12 @@ namespace cb {
 // Device-side status word layout (ctx->d_status, 4 ints): [0] error code, [1..3] detail.
 enum DevErr : int { DEV_OK = 0, DEV_WAIT_TIMEOUT = 1, DEV_BAD_INDEX = 2 };
 
+// Optional bf16 (hi, lo) destination of a kernel whose output feeds a tensor-core GEMM: when `hi`
+// is set the producer writes the split operand itself and the fp32 copy is not needed.
+struct BfOut {
+  __nv_bfloat16 *hi = nullptr, *lo = nullptr;
+};
+
 struct Scratch {
   void *ptr = nullptr;
   size_t bytes = 0;
@@ -76,7 +82,7 @@ int launch_layernorm(caten_b200_ctx *ctx, const float *x, const float *g, const 
                      int64_t rows, int64_t d, float eps);
 // src_rows: optional gather — row r of the output reads row (r+1)*src_stride-1 of x when src_stride > 1
 int launch_layernorm_strided(caten_b200_ctx *ctx, const float *x, const float *g, const float *b, float *y,
-                             int64_t rows, int64_t d, float eps, int64_t src_stride);
+                             int64_t rows, int64_t d, float eps, int64_t src_stride, cb::BfOut bf = cb::BfOut());
 int launch_embed(caten_b200_ctx *ctx, const float *ids_f32, const int64_t *ids_i64, const float *wte,
                  const float *wpe, float *out, int64_t B, int64_t s, int64_t n, int64_t d, int64_t V, int64_t T,
                  const int *d_n = nullptr);
@@ -85,13 +91,18 @@ int launch_begin_steps(caten_b200_ctx *ctx, const float *ids_f32, const int64_t 
 int launch_finish_step(caten_b200_ctx *ctx, const int64_t *out_ids, int64_t *ids_io, int64_t *hist, int *d_pos, int64_t B);
 int launch_argmax(caten_b200_ctx *ctx, const float *x, int64_t rows, int64_t V, int64_t *out);
 int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc, float *out, int64_t B,
-                     int64_t s, int64_t n, int64_t H, int64_t T, const int *d_n = nullptr);
+                     int64_t s, int64_t n, int64_t H, int64_t T, const int *d_n = nullptr, cb::BfOut bf = cb::BfOut());
 int launch_gemv(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
                 const float *res, int act, float *y);
 int launch_gemm_simt(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
                      const float *res, int act, float *y, int64_t M);
 int launch_gemm_tc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
                    const float *res, int act, float *y, int64_t M, int nsplit);
+// x given as fp32 (split by a pre-pass) or, when xhi is set, already as bf16 hi/lo; output as fp32 y
+// or, when ybf.hi is set, as bf16 hi/lo for the next GEMM
+int launch_gemm_tc_ex(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const __nv_bfloat16 *xhi,
+                      const __nv_bfloat16 *xlo, const float *bias, const float *res, int act, float *y, cb::BfOut ybf,
+                      int64_t M, int nsplit);
 int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
                            const float *res, int act, float *y, int64_t M, int nsplit);
 // relu(a.b) with b given [K, N] row-major fp32
@@ -127,6 +138,13 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   if (act == CATEN_B200_ACT_RELU) return v > 0.0f ? v : 0.0f;
   return v;
 }
+
+// bf16 operand split used by the tensor-core GEMM: hi = bf16(v), lo = bf16(v - hi)
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);  // .x = a in the low half
+  return *reinterpret_cast<const uint32_t *>(&v);
+}
+__device__ __forceinline__ float bf16_lo(float w) { return w - __bfloat162float(__float2bfloat16_rn(w)); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

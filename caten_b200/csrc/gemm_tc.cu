@@ -46,6 +46,8 @@ struct TcArgs {
   // to `part` and splitk_reduce_kernel adds them in split order and applies the epilogue
   int splits, cps;
   float *part;
+  // when yhi is set the epilogue writes the result as split bf16 (operand of the next GEMM), not y
+  __nv_bfloat16 *yhi, *ylo;
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -124,12 +126,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *r) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---- operand split and swizzled stores ----------------------------------------------------------
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);  // .x = a in the low half
-  return *reinterpret_cast<const uint32_t *>(&v);
-}
-// residual of the bf16 rounding, itself rounded to bf16
-__device__ __forceinline__ float bf16_lo(float w) { return w - __bfloat162float(__float2bfloat16_rn(w)); }
 
 // byte offset of 16-byte chunk `c` (0..7) of row `r` inside a [rows x 128 B] tile, Swizzle<3,4,3>
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
@@ -299,7 +295,14 @@ __device__ __forceinline__ void epi_store16(const TcArgs &a, const uint32_t *r, 
       if (ACT == CATEN_B200_ACT_GELU) v = gelu_ref(v);
       if (ACT == CATEN_B200_ACT_RELU) v = v > 0.0f ? v : 0.0f;
       if (rp) v = rp[(int64_t)i * a.N] + v;
-      yp[(int64_t)i * a.N] = v;
+      if (a.yhi) {
+        const int64_t at = ((int64_t)m_first + i) * a.N + o;
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        a.yhi[at] = h;
+        if (a.ylo) a.ylo[at] = __float2bfloat16_rn(v - __bfloat162float(h));
+      } else {
+        yp[(int64_t)i * a.N] = v;
+      }
     }
   }
 }
@@ -497,26 +500,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
 }
 
 // Sums the split-K partial tiles part[split][tile][column][row] in split order (so the result is
-// the same on every run) and applies bias / activation / residual.  Consecutive threads own
-// consecutive weight rows: partial reads and y stores are coalesced.
+// the same on every run) and applies bias / activation / residual.  A thread owns four consecutive
+// weight rows (one float4 per split, four splits in flight): partial reads and y stores are
+// coalesced and the loads of different splits overlap.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ part, int splits, int tiles_x, int tiles,
                                                             int bnx, const float *__restrict__ bias, const float *res, float *y,
-                                                            int act, int M, int N) {
+                                                            __nv_bfloat16 *yhi, __nv_bfloat16 *ylo, int act, int M, int N) {
   const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  const int row = (int)(idx & (TC_BM - 1));
-  const int64_t rest = idx >> 7;
+  const int row = (int)(idx & 31) * 4;
+  const int64_t rest = idx >> 5;
   const int col = (int)(rest % bnx), tile = (int)(rest / bnx);
   if (tile >= tiles) return;
   const int64_t o = (int64_t)(tile % tiles_x) * TC_BM + row, m = (int64_t)(tile / tiles_x) * bnx + col;
   if (o >= N || m >= M) return;
   const size_t zstride = (size_t)tiles * bnx * TC_BM;
   const float *p = part + ((size_t)tile * bnx + col) * TC_BM + row;
-  float v = 0.0f;
-  for (int z = 0; z < splits; ++z) v += __ldcs(p + z * zstride);
-  if (bias) v = v + bias[o];
-  v = apply_act(v, act);
-  if (res) v = res[m * N + o] + v;
-  y[m * N + o] = v;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  int z = 0;
+  for (; z + 4 <= splits; z += 4) {
+    const float4 a0 = __ldcs(reinterpret_cast<const float4 *>(p + (size_t)z * zstride));
+    const float4 a1 = __ldcs(reinterpret_cast<const float4 *>(p + (size_t)(z + 1) * zstride));
+    const float4 a2 = __ldcs(reinterpret_cast<const float4 *>(p + (size_t)(z + 2) * zstride));
+    const float4 a3 = __ldcs(reinterpret_cast<const float4 *>(p + (size_t)(z + 3) * zstride));
+    v.x += a0.x; v.y += a0.y; v.z += a0.z; v.w += a0.w;
+    v.x += a1.x; v.y += a1.y; v.z += a1.z; v.w += a1.w;
+    v.x += a2.x; v.y += a2.y; v.z += a2.z; v.w += a2.w;
+    v.x += a3.x; v.y += a3.y; v.z += a3.z; v.w += a3.w;
+  }
+  for (; z < splits; ++z) {
+    const float4 a0 = __ldcs(reinterpret_cast<const float4 *>(p + (size_t)z * zstride));
+    v.x += a0.x; v.y += a0.y; v.z += a0.z; v.w += a0.w;
+  }
+  float r[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    if (o + e < N) {
+      float t = r[e];
+      if (bias) t = t + bias[o + e];
+      t = apply_act(t, act);
+      if (res) t = res[m * N + o + e] + t;
+      if (yhi) {
+        const __nv_bfloat16 h = __float2bfloat16_rn(t);
+        yhi[m * N + o + e] = h;
+        if (ylo) ylo[m * N + o + e] = __float2bfloat16_rn(t - __bfloat162float(h));
+      } else {
+        y[m * N + o + e] = t;
+      }
+    }
+  }
 }
 
 // x -> bf16 hi (and lo) copies, row-major [M, K]
@@ -553,20 +584,31 @@ static int launch_tc_t(caten_b200_ctx *ctx, const CUtensorMap &mh, const CUtenso
 }
 
 static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, int64_t nkb, const float *x,
-                  const float *bias, const float *res, int act, float *y, int64_t M, int64_t N, int64_t K, int nsplit) {
+                  const float *bias, const float *res, int act, float *y, int64_t M, int64_t N, int64_t K, int nsplit,
+                  const __nv_bfloat16 *xhi_pre = nullptr, const __nv_bfloat16 *xlo_pre = nullptr, BfOut ybf = BfOut()) {
   if (M <= 0 || N <= 0) return 0;
   if (!ctx->encode_tiled) return fail(ctx, CATEN_B200_ECUDA, "gemm_tc: cuTensorMapEncodeTiled is not available");
   if (K % TC_BK) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_tc: inner dimension %lld is not a multiple of 64", (long long)K);
   if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_tc: dimension too large");
   if (nsplit != 1 && nsplit != 3) return fail(ctx, CATEN_B200_EINVAL, "gemm_tc: nsplit must be 1 or 3");
-  // activations -> bf16 (hi[, lo]) in the context's scratch buffer
-  const size_t xb = (size_t)M * K * 2;
-  const size_t xb_al = (xb + 1023) & ~(size_t)1023;
-  if (int rc = scratch_reserve(ctx, &ctx->xbf, xb_al * (nsplit == 3 ? 2 : 1))) return rc;
-  uint8_t *xhi = (uint8_t *)ctx->xbf.ptr, *xlo = nsplit == 3 ? xhi + xb_al : nullptr;
-  const int64_t n4 = M * K / 4;
-  split_bf16_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, ctx->stream>>>((const float4 *)x, (uint2 *)xhi, (uint2 *)xlo, n4);
-  CB_LAUNCH_CHECK(ctx, "split_bf16_kernel");
+  uint8_t *xhi, *xlo;
+  if (xhi_pre) {
+    // the producer of x already wrote the split bf16 operand
+    if (nsplit == 3 && !xlo_pre) return fail(ctx, CATEN_B200_EINVAL, "gemm_tc: split-bf16 needs the lo part of x");
+    if (((uintptr_t)xhi_pre | (uintptr_t)xlo_pre) & 15) return fail(ctx, CATEN_B200_EINVAL, "gemm_tc: bf16 operand must be 16-byte aligned");
+    xhi = (uint8_t *)xhi_pre;
+    xlo = (uint8_t *)xlo_pre;
+  } else {
+    // activations -> bf16 (hi[, lo]) in the context's scratch buffer
+    const size_t xb = (size_t)M * K * 2;
+    const size_t xb_al = (xb + 1023) & ~(size_t)1023;
+    if (int rc = scratch_reserve(ctx, &ctx->xbf, xb_al * (nsplit == 3 ? 2 : 1))) return rc;
+    xhi = (uint8_t *)ctx->xbf.ptr;
+    xlo = nsplit == 3 ? xhi + xb_al : nullptr;
+    const int64_t n4 = M * K / 4;
+    split_bf16_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, ctx->stream>>>((const float4 *)x, (uint2 *)xhi, (uint2 *)xlo, n4);
+    CB_LAUNCH_CHECK(ctx, "split_bf16_kernel");
+  }
 
   const int max_bnx = 256;
   int bnx = 16;
@@ -577,6 +619,7 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
 
   TcArgs a;
   a.qs = qs; a.d = d; a.bias = bias; a.res = res; a.y = y; a.status = ctx->d_status; a.act = act;
+  a.yhi = ybf.hi; a.ylo = ybf.lo;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.nkb = (int)nkb; a.bnx = bnx;
   const size_t stage = (size_t)(TC_WBYTES + bnx * 128) * (nsplit == 3 ? 2 : 1);
   int stages = (int)((200 * 1024) / stage);
@@ -624,9 +667,9 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
   }
 #undef TC_CASE
   if (rc || splits == 1) return rc;
-  const int64_t total = tiles * bnx * TC_BM;
+  const int64_t total = tiles * bnx * (TC_BM / 4);
   splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(a.part, splits, (int)gx, (int)tiles, bnx, bias, res, y,
-                                                                              act, (int)M, (int)N);
+                                                                              a.yhi, a.ylo, act, (int)M, (int)N);
   CB_LAUNCH_CHECK(ctx, "splitk_reduce_kernel");
   return 0;
 }
@@ -705,6 +748,7 @@ int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, cons
 
   TcArgs a;
   a.qs = w->qs; a.d = w->d; a.bias = bias; a.res = res; a.y = y; a.status = ctx->d_status; a.act = act;
+  a.yhi = nullptr; a.ylo = nullptr;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.nkb = (int)w->nkb; a.bnx = bnx;
   a.stages = stages > cps ? cps : stages;
   a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bnx >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
@@ -727,9 +771,9 @@ int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, cons
   }
 #undef TC_CASE
   if (rc || splits == 1) return rc;
-  const int64_t total = tiles * bnx * TC_BM;
+  const int64_t total = tiles * bnx * (TC_BM / 4);
   splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(a.part, splits, (int)gx, (int)tiles, bnx, bias, res, y,
-                                                                              act, (int)M, (int)N);
+                                                                              a.yhi, a.ylo, act, (int)M, (int)N);
   CB_LAUNCH_CHECK(ctx, "splitk_reduce_kernel");
   return 0;
 }
@@ -737,6 +781,12 @@ int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, cons
 int launch_gemm_tc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
                    const float *res, int act, float *y, int64_t M, int nsplit) {
   return run_tc(ctx, w->type, w->qs, w->d, w->nkb, x, bias, res, act, y, M, w->rows, w->cols, nsplit);
+}
+
+int launch_gemm_tc_ex(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const __nv_bfloat16 *xhi,
+                      const __nv_bfloat16 *xlo, const float *bias, const float *res, int act, float *y, BfOut ybf, int64_t M,
+                      int nsplit) {
+  return run_tc(ctx, w->type, w->qs, w->d, w->nkb, x, bias, res, act, y, M, w->rows, w->cols, nsplit, xhi, xlo, ybf);
 }
 
 int launch_relu_matmul_tc(caten_b200_ctx *ctx, const float *a, const float *b, float *c, int64_t M, int64_t K, int64_t N, int nsplit) {

@@ -90,7 +90,8 @@ __device__ __forceinline__ float ln_block_sum(float v, float *red) {
 
 __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__restrict__ x, const float *__restrict__ g,
                                                                const float *__restrict__ b, float *__restrict__ y,
-                                                               int d4, float invd, float eps, int64_t src_stride) {
+                                                               int d4, float invd, float eps, int64_t src_stride,
+                                                               uint2 *__restrict__ yhi, uint2 *__restrict__ ylo) {
   __shared__ float red[LN_THREADS / 32];
   const int64_t row = blockIdx.x;
   const int64_t src_row = src_stride > 1 ? (row + 1) * src_stride - 1 : row;
@@ -129,24 +130,30 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__re
       o.y = (v[i].y * rs) * gg.y + bb.y;
       o.z = (v[i].z * rs) * gg.z + bb.z;
       o.w = (v[i].w * rs) * gg.w + bb.w;
-      yr[c] = o;
+      if (yhi) {  // split bf16 operand of the GEMM that consumes this row
+        yhi[row * d4 + c] = make_uint2(pack_bf16(o.x, o.y), pack_bf16(o.z, o.w));
+        if (ylo) ylo[row * d4 + c] = make_uint2(pack_bf16(bf16_lo(o.x), bf16_lo(o.y)), pack_bf16(bf16_lo(o.z), bf16_lo(o.w)));
+      } else {
+        yr[c] = o;
+      }
     }
   }
 }
 
 int launch_layernorm_strided(caten_b200_ctx *ctx, const float *x, const float *g, const float *b, float *y,
-                             int64_t rows, int64_t d, float eps, int64_t src_stride) {
+                             int64_t rows, int64_t d, float eps, int64_t src_stride, BfOut bf) {
   if (rows <= 0) return 0;
   if (d % 4 || d > 4 * LN_THREADS * LN_MAXV) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: d=%lld (need d%%4==0, d<=2048)", (long long)d);
   if (rows > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: too many rows");
-  layernorm_kernel<<<(unsigned)rows, LN_THREADS, 0, ctx->stream>>>(x, g, b, y, (int)(d / 4), 1.0f / (float)d, eps, src_stride);
+  layernorm_kernel<<<(unsigned)rows, LN_THREADS, 0, ctx->stream>>>(x, g, b, y, (int)(d / 4), 1.0f / (float)d, eps, src_stride,
+                                                                   (uint2 *)bf.hi, (uint2 *)bf.lo);
   CB_LAUNCH_CHECK(ctx, "layernorm_kernel");
   return 0;
 }
 
 int launch_layernorm(caten_b200_ctx *ctx, const float *x, const float *g, const float *b, float *y, int64_t rows,
                      int64_t d, float eps) {
-  return launch_layernorm_strided(ctx, x, g, b, y, rows, d, eps, 1);
+  return launch_layernorm_strided(ctx, x, g, b, y, rows, d, eps, 1, BfOut());
 }
 
 // ---------------------------------------------------------------------------------------------
