@@ -63,6 +63,18 @@ SIGNATURES = {
     "caten_b200_weight_free": (C.c_int, [_vp, _vp]),
     "caten_b200_weight_nbytes": (_i64, [C.c_int, _i64, _i64]),
     "caten_b200_weight_dequant": (C.c_int, [_vp, _vp, _vp]),
+    "caten_b200_gguf_open": (C.c_int, [C.c_char_p, _PFP]),
+    "caten_b200_gguf_close": (C.c_int, [_vp]),
+    "caten_b200_gguf_version": (C.c_int, [_vp]),
+    "caten_b200_gguf_alignment": (_i64, [_vp]),
+    "caten_b200_gguf_tensor_count": (_i64, [_vp]),
+    "caten_b200_gguf_meta_count": (_i64, [_vp]),
+    "caten_b200_gguf_tensor": (C.c_int, [_vp, _i64, C.POINTER(C.c_char_p), C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                         C.POINTER(_i64), _PFP, C.POINTER(_i64)]),
+    "caten_b200_gguf_find_tensor": (_i64, [_vp, C.c_char_p]),
+    "caten_b200_gguf_meta": (C.c_int, [_vp, _i64, C.POINTER(C.c_char_p), C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                       C.POINTER(_i64), _PFP, C.POINTER(_i64)]),
+    "caten_b200_gguf_upload": (C.c_int, [_vp, _vp, _i64, _PFP]),
     "caten_b200_linear": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int, _vp, _i64, C.c_int]),
     "caten_b200_linear_noalloc": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int, _vp, _i64, C.c_int]),
     "caten_b200_relu_matmul": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, C.c_int]),

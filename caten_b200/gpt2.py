@@ -174,3 +174,28 @@ def gpt2_generate(gpt2: GPT2, prompt_ids, max_length: int = 100) -> np.ndarray:
         start_pos = tokens.shape[1]
         tokens = np.concatenate([tokens, out.reshape(-1, 1)], axis=1)
     return tokens
+
+
+def make_gpt2_from_gguf(path: str, runtime: Optional[B200Runtime] = None, max_seq_len: Optional[int] = None, batch: int = 1,
+                        precision: str = "fp32", **kw) -> GPT2:
+    """`make-gpt2` (apps/gpt2/gpt2.lisp:82-93) from a local GGUF file: parse, remap the tensor names,
+    upload (quantised tensors stay packed) and build the model.  Sizes come from the file's
+    metadata (`gpt2.block_count`, `gpt2.embedding_length`, `gpt2.attention.head_count`, ...) where the
+    reference hard-codes them per model name (gpt2.lisp:38-41)."""
+    from .gguf import gguf_to_state_dict, load_gguf
+    g = load_gguf(path)
+    try:
+        sd = gguf_to_state_dict(g)
+        md = g.metadata
+        vocab, dim = sd["wte.weight"].shape
+        n_layers = int(md.get("gpt2.block_count", 1 + max(int(k.split(".")[1]) for k in sd if k.startswith("h."))))
+        n_heads = int(md.get("gpt2.attention.head_count", dim // 64))
+        eps = float(md.get("gpt2.attention.layer_norm_epsilon", 1e-5))
+        T = int(max_seq_len or md.get("gpt2.context_length", sd["wpe.weight"].shape[0]))
+        if "lm_head.weight" not in sd:   # GGUF exports of GPT-2 may tie the output matrix to the embeddings
+            sd["lm_head.weight"] = sd["wte.weight"]
+        params = GPT2Params(n_layers, n_heads, int(dim), int(vocab), eps)
+        sd["wpe.weight"] = sd["wpe.weight"][:T]
+        return GPT2(runtime or B200Runtime(0), params, sd, max_seq_len=T, batch=batch, precision=precision, **kw)
+    finally:
+        g.close()

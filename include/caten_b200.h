@@ -100,6 +100,37 @@ int64_t caten_b200_weight_nbytes(int ggml_type, int64_t rows, int64_t cols);
  * (float)code * (float)scale, to d_out. */
 int caten_b200_weight_dequant(caten_b200_ctx *ctx, const caten_b200_weight *w, float *d_out);
 
+/* ---- GGUF files ------------------------------------------------------------------------------------
+ * Replaces `load-gguf` / `make-gguf` (external/gguf/gguf-file.lisp:48-91), `parse-metadata-kv`
+ * (external/gguf/metadata.lisp:3-87) and `parse-tensor-info` (external/gguf/tensor-info.lisp:79-102):
+ * the file is memory-mapped and only its header, key/value table and tensor table are decoded;
+ * tensor bytes stay where they are until uploaded.  GGUF versions 2 and 3; tensor offsets follow
+ * `general.alignment` (default 32).  Returned name/key/data pointers point into the handle and
+ * are valid until caten_b200_gguf_close. */
+typedef struct caten_b200_gguf caten_b200_gguf;
+int caten_b200_gguf_open(const char *path, caten_b200_gguf **g);
+int caten_b200_gguf_close(caten_b200_gguf *g);
+int caten_b200_gguf_version(const caten_b200_gguf *g);
+int64_t caten_b200_gguf_alignment(const caten_b200_gguf *g);
+int64_t caten_b200_gguf_tensor_count(const caten_b200_gguf *g);
+int64_t caten_b200_gguf_meta_count(const caten_b200_gguf *g);
+/* Tensor i: name, ggml type id, number of dims, dims4[4] in file order (dims4[0] is the contiguous
+ * dimension; unused entries are 1), pointer to its bytes in the mapping and their count (-1 for
+ * a ggml type this library does not hold).  Any out pointer may be NULL. */
+int caten_b200_gguf_tensor(const caten_b200_gguf *g, int64_t i, const char **name, int *ggml_type, int *n_dims,
+                           int64_t *dims4, const void **data, int64_t *nbytes);
+/* Index of the tensor called `name`, or -1. */
+int64_t caten_b200_gguf_find_tensor(const caten_b200_gguf *g, const char *name);
+/* Metadata entry i: key, value type id (0 u8, 1 i8, 2 u16, 3 i16, 4 u32, 5 i32, 6 f32, 7 bool,
+ * 8 string, 9 array, 10 u64, 11 i64, 12 f64), element type and length for arrays, pointer to the
+ * little-endian value (strings: first byte, *str_len bytes; arrays: first element; string arrays
+ * are sequences of u64 length + bytes). */
+int caten_b200_gguf_meta(const caten_b200_gguf *g, int64_t i, const char **key, int *type, int *elem_type,
+                         int64_t *count, const void **value, int64_t *str_len);
+/* Uploads 2-D tensor i as a Linear weight [dims4[1], dims4[0]] straight from the mapping
+ * (`tensor-info->tensor`, external/gguf/tensor-info.lisp:104-120, without dequantising). */
+int caten_b200_gguf_upload(caten_b200_ctx *ctx, const caten_b200_gguf *g, int64_t i, caten_b200_weight **w);
+
 /* ---- kernels of the GPT-2 graph -----------------------------------------------------------------
  * One entry per fused kernel the scheduler produces for external/llm/layers.lisp
  * ([Embedding_Embedding_ADD] [LayerNorm] [Matmul+GELU] [Attention], source/codegen/jit.lisp:8);
