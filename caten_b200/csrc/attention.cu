@@ -21,6 +21,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float *__restric
                                                           float *__restrict__ vc, float *__restrict__ out, int H,
                                                           int T, int n, const int *__restrict__ d_n,
                                                           __nv_bfloat16 *__restrict__ ohi, __nv_bfloat16 *__restrict__ olo) {
+  pdl_enter();
   if (d_n) n = *d_n;  // position kept on the device (decode replayed from a CUDA graph)
   extern __shared__ float smem[];
   float *q = smem;            // 64
@@ -125,6 +126,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float *__restric
 // ---------------------------------------------------------------------------------------------
 __global__ void kv_append_kernel(const float *__restrict__ qkv, float *__restrict__ kc, float *__restrict__ vc,
                                  int s, int n, int H, int T) {
+  pdl_enter();
   const int64_t r = blockIdx.x;  // row of qkv = b*s + i
   const int64_t b = r / s;
   const int i = (int)(r % s);
@@ -148,6 +150,7 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
                                                            int s, int n, int H, int T, __nv_bfloat16 *__restrict__ ohi,
                                                            __nv_bfloat16 *__restrict__ olo) {
   extern __shared__ float smem[];
+  pdl_enter();
   float *Qt = smem;                 // [64 c][PF_LD i]
   float *Kt = Qt + 64 * PF_LD;      // [64 c][PF_LD j]
   float *Vs = Kt + 64 * PF_LD;      // [64 j][PF_LD c]
@@ -300,16 +303,16 @@ int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc
     if (smem > 200 * 1024) return fail(ctx, CATEN_B200_EUNSUPPORTED, "attention: context too long for the decode kernel");
     if (smem > 48 * 1024)
       CB_CUDA(ctx, cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attn_decode_kernel<<<dim3((unsigned)H, (unsigned)B), 256, smem, ctx->stream>>>(qkv, kc, vc, out, (int)H, (int)T, (int)n, d_n, bf.hi, bf.lo);
+    launch_k(ctx, attn_decode_kernel, dim3((unsigned)H, (unsigned)B), dim3(256), smem, qkv, kc, vc, out, (int)H, (int)T, (int)n, d_n, bf.hi, bf.lo);
     CB_LAUNCH_CHECK(ctx, "attn_decode_kernel");
     return 0;
   }
   if (d_n) return fail(ctx, CATEN_B200_EINVAL, "attention: a device-side position is only supported for single-token steps");
-  kv_append_kernel<<<(unsigned)(B * s), 128, 0, ctx->stream>>>(qkv, kc, vc, (int)s, (int)n, (int)H, (int)T);
+  launch_k(ctx, kv_append_kernel, dim3((unsigned)(B * s)), dim3(128), 0, qkv, kc, vc, (int)s, (int)n, (int)H, (int)T);
   CB_LAUNCH_CHECK(ctx, "kv_append_kernel");
   const size_t smem = 4 * 64 * PF_LD * sizeof(float);
   CB_CUDA(ctx, cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  attn_prefill_kernel<<<dim3((unsigned)((s + 63) / 64), (unsigned)H, (unsigned)B), 256, smem, ctx->stream>>>(
+  launch_k(ctx, attn_prefill_kernel, dim3((unsigned)((s + 63) / 64), (unsigned)H, (unsigned)B), dim3(256), smem, 
       qkv, kc, vc, out, (int)s, (int)n, (int)H, (int)T, bf.hi, bf.lo);
   CB_LAUNCH_CHECK(ctx, "attn_prefill_kernel");
   return 0;

@@ -2,6 +2,7 @@
 // the whole GPT-2 step.  See include/caten_b200.h for the contract of every function.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <new>
 #include <vector>
@@ -105,6 +106,7 @@ int caten_b200_init(int device, caten_b200_ctx **out) {
   if (!ctx) return fail(nullptr, CATEN_B200_ECUDA, "out of host memory");
   ctx->device = device;
   ctx->sm_count = prop.multiProcessorCount;
+  if (const char *e = getenv("CATEN_B200_PDL")) ctx->use_pdl = atoi(e) != 0;
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaStreamCreate"); }
   if ((e = cudaMalloc(&ctx->d_status, 4 * sizeof(int))) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaMalloc"); }
   cudaMemset(ctx->d_status, 0, 4 * sizeof(int));

@@ -41,6 +41,7 @@ struct caten_b200_ctx {
   cb::Scratch wtmp;          // split-K partial tiles of the tensor-core GEMM
   void *encode_tiled = nullptr;  // cuTensorMapEncodeTiled, resolved at init
   int64_t launches = 0;
+  bool use_pdl = true;       // programmatic dependent launch between consecutive kernels (CATEN_B200_PDL=0 turns it off)
   // per-kernel-class event timing (caten_b200_profile_begin / _end)
   unsigned prof_mask = 0;
   struct ProfRec { int klass; cudaEvent_t a, b; };
@@ -110,7 +111,33 @@ int launch_relu_matmul_simt(caten_b200_ctx *ctx, const float *a, const float *b,
 int launch_relu_matmul_tc(caten_b200_ctx *ctx, const float *a, const float *b, float *c, int64_t M, int64_t K,
                           int64_t N, int nsplit);
 
+// Kernel launch with programmatic dependent launch allowed: the next kernel in the stream may be
+// scheduled (and run its prologue) while this one drains; every kernel launched this way calls
+// pdl_wait() before it touches memory another kernel produces or still reads.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(caten_b200_ctx *ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = ctx->use_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ---- device helpers ----
+
+// Blocks until the kernels this launch depends on have completed and their writes are visible
+// (no-op when the kernel was not launched as a programmatic dependent).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel in the stream start being scheduled.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() { pdl_wait(); pdl_launch_dependents(); }
+
 
 // GeLU exactly as the reference composes it (source/nn/activations.lisp:202-204 with
 // tanh(z) = 2*sigmoid(2z) - 1 and sigmoid(y) = 1/(1 + exp2(y * -1/ln2))), every step in fp32.

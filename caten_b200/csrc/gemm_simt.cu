@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const void *__restrict__
                                                         int64_t K, int64_t nkb) {
   __shared__ __align__(16) float Xs[SG_BK * SG_LD];  // [k][m]
   __shared__ __align__(16) float Ws[SG_BK * SG_LD];  // [k][n]
+  pdl_enter();
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int64_t m0 = (int64_t)blockIdx.y * SG_BM, n0 = (int64_t)blockIdx.x * SG_BN;
   const int lrow = tid & 63, part = tid >> 6;
@@ -125,7 +126,7 @@ static int launch_simt(caten_b200_ctx *ctx, const void *qs, const __half *d, con
   if (K % 32) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm: inner dimension %lld is not a multiple of 32", (long long)K);
   const int64_t gx = (N + SG_BN - 1) / SG_BN, gy = (M + SG_BM - 1) / SG_BM;
   if (gy > 65535) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm: too many rows for one launch (%lld)", (long long)M);
-  gemm_simt_kernel<WT><<<dim3((unsigned)gx, (unsigned)gy), 256, 0, ctx->stream>>>(qs, d, x, bias, res, y, act, M, N, K, K / 32);
+  launch_k(ctx, gemm_simt_kernel<WT>, dim3((unsigned)gx, (unsigned)gy), dim3(256), 0, qs, d, x, bias, res, y, act, M, N, K, K / 32);
   CB_LAUNCH_CHECK(ctx, "gemm_simt_kernel");
   return 0;
 }

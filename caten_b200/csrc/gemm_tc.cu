@@ -357,6 +357,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // The packed weights do not depend on the preceding kernel: the producers start streaming them
+  // at once.  Only the activation loads and the epilogue (residual reads, output / partial-tile
+  // writes) wait for it.
+  pdl_launch_dependents();
 
   if (warp < 16) {
     // ---------------- weight producers ----------------
@@ -397,6 +401,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
       }
     }
     // ---------------- epilogue ----------------
+    pdl_wait();
     if (tid == 0) {
       const bool got = !*abort_flag && mbar_wait(accum_bar, 0, abort_flag);
       if (!got && !*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 2; }
@@ -442,6 +447,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
   } else if (warp == 16) {
     // ---------------- activation TMA producer ----------------
     if (lane == 0) {
+      pdl_wait();  // x is written by the preceding kernel
       int issued = 0, s = 0;
       uint32_t ph = 0;
       for (int kc = 0; kc < num_k; ++kc) {
@@ -506,6 +512,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ part, int splits, int tiles_x, int tiles,
                                                             int bnx, const float *__restrict__ bias, const float *res, float *y,
                                                             __nv_bfloat16 *yhi, __nv_bfloat16 *ylo, int act, int M, int N) {
+  pdl_enter();
   const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
   const int row = (int)(idx & 31) * 4;
   const int64_t rest = idx >> 5;
@@ -552,6 +559,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
 
 // x -> bf16 hi (and lo) copies, row-major [M, K]
 __global__ void split_bf16_kernel(const float4 *__restrict__ x, uint2 *__restrict__ hi, uint2 *__restrict__ lo, int64_t n4) {
+  pdl_enter();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n4) return;
   const float4 v = x[i];
@@ -578,7 +586,7 @@ static int make_x_map(caten_b200_ctx *ctx, CUtensorMap *map, void *base, int64_t
 template <int WT, int NSPLIT>
 static int launch_tc_t(caten_b200_ctx *ctx, const CUtensorMap &mh, const CUtensorMap &ml, const TcArgs &a, dim3 grid, size_t smem) {
   CB_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<WT, NSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  gemm_tc_kernel<WT, NSPLIT><<<grid, TC_THREADS, smem, ctx->stream>>>(mh, ml, a);
+  launch_k(ctx, gemm_tc_kernel<WT, NSPLIT>, dim3(grid), dim3(TC_THREADS), smem, mh, ml, a);
   CB_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
   return 0;
 }
@@ -606,7 +614,7 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
     xhi = (uint8_t *)ctx->xbf.ptr;
     xlo = nsplit == 3 ? xhi + xb_al : nullptr;
     const int64_t n4 = M * K / 4;
-    split_bf16_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, ctx->stream>>>((const float4 *)x, (uint2 *)xhi, (uint2 *)xlo, n4);
+    launch_k(ctx, split_bf16_kernel, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, (const float4 *)x, (uint2 *)xhi, (uint2 *)xlo, n4);
     CB_LAUNCH_CHECK(ctx, "split_bf16_kernel");
   }
 
@@ -668,7 +676,7 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
 #undef TC_CASE
   if (rc || splits == 1) return rc;
   const int64_t total = tiles * bnx * (TC_BM / 4);
-  splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(a.part, splits, (int)gx, (int)tiles, bnx, bias, res, y,
+  launch_k(ctx, splitk_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, a.part, splits, (int)gx, (int)tiles, bnx, bias, res, y,
                                                                               a.yhi, a.ylo, act, (int)M, (int)N);
   CB_LAUNCH_CHECK(ctx, "splitk_reduce_kernel");
   return 0;
@@ -740,7 +748,7 @@ int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, cons
   // nothing in the buffer has to start at zero: the used part of x_hi/x_lo and every partial tile
   // that the reduce reads are fully overwritten by this call before they are read
   const int64_t n4 = M * K / 4;
-  split_bf16_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, ctx->stream>>>((const float4 *)x, (uint2 *)xhi, (uint2 *)xlo, n4);
+  launch_k(ctx, split_bf16_kernel, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, (const float4 *)x, (uint2 *)xhi, (uint2 *)xlo, n4);
   CB_LAUNCH_CHECK(ctx, "split_bf16_kernel");
   CUtensorMap mh, ml;
   if (int rc = make_x_map(ctx, &mh, xhi, M, K, bnx)) return rc;
@@ -772,7 +780,7 @@ int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, cons
 #undef TC_CASE
   if (rc || splits == 1) return rc;
   const int64_t total = tiles * bnx * (TC_BM / 4);
-  splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(a.part, splits, (int)gx, (int)tiles, bnx, bias, res, y,
+  launch_k(ctx, splitk_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, a.part, splits, (int)gx, (int)tiles, bnx, bias, res, y,
                                                                               a.yhi, a.ylo, act, (int)M, (int)N);
   CB_LAUNCH_CHECK(ctx, "splitk_reduce_kernel");
   return 0;

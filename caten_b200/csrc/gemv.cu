@@ -98,6 +98,7 @@ struct BlkQ8 {
 template <class BLK, int RI>
 __global__ void __launch_bounds__(GEMV_MAX_THREADS) gemv_blocked_kernel(GemvArgs a) {
   extern __shared__ float red[];
+  pdl_enter();
   constexpr int W = BLK::WORDS;
   const int tid = threadIdx.x, nkb = a.nkb, G = a.G;
   const bool active = tid < G * nkb;
@@ -200,6 +201,7 @@ __global__ void __launch_bounds__(256) gemv_dense_kernel(const T *__restrict__ W
                                                          const float *__restrict__ bias, const float *__restrict__ res,
                                                          float *__restrict__ y, int act, int N, int K) {
   extern __shared__ float xs[];
+  pdl_enter();
   constexpr int VEC = DenseLoad<T>::VEC;
   for (int i = threadIdx.x; i < K; i += blockDim.x) xs[i] = x[i];
   __syncthreads();
@@ -250,7 +252,7 @@ static int launch_blocked(caten_b200_ctx *ctx, const GemvArgs &a) {
   const int64_t slabs = ((int64_t)a.N + a.G * RI - 1) / (a.G * RI);
   int64_t grid = (int64_t)ctx->sm_count * occ;
   if (grid > slabs) grid = slabs;
-  gemv_blocked_kernel<BLK, RI><<<(unsigned)grid, threads, smem, ctx->stream>>>(a);
+  launch_k(ctx, gemv_blocked_kernel<BLK, RI>, dim3((unsigned)grid), dim3(threads), smem, a);
   CB_LAUNCH_CHECK(ctx, "gemv_blocked_kernel");
   return 0;
 }
@@ -278,11 +280,11 @@ int launch_gemv(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x,
   if (w->type == CATEN_B200_F32) {
     if (K % 4) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv f32: cols %% 4 != 0");
     if (smem > 48 * 1024) cudaFuncSetAttribute(gemv_dense_kernel<float, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    gemv_dense_kernel<float, 2><<<(unsigned)grid, 256, smem, ctx->stream>>>((const float *)w->qs, x, bias, res, y, act, N, K);
+    launch_k(ctx, gemv_dense_kernel<float, 2>, dim3((unsigned)grid), dim3(256), smem, (const float *)w->qs, x, bias, res, y, act, N, K);
   } else if (w->type == CATEN_B200_F16) {
     if (K % 8) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv f16: cols %% 8 != 0");
     if (smem > 48 * 1024) cudaFuncSetAttribute(gemv_dense_kernel<__half, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    gemv_dense_kernel<__half, 2><<<(unsigned)grid, 256, smem, ctx->stream>>>((const __half *)w->qs, x, bias, res, y, act, N, K);
+    launch_k(ctx, gemv_dense_kernel<__half, 2>, dim3((unsigned)grid), dim3(256), smem, (const __half *)w->qs, x, bias, res, y, act, N, K);
   } else {
     return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv: weight type %d", w->type);
   }

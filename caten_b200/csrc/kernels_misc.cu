@@ -93,6 +93,7 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__re
                                                                int d4, float invd, float eps, int64_t src_stride,
                                                                uint2 *__restrict__ yhi, uint2 *__restrict__ ylo) {
   __shared__ float red[LN_THREADS / 32];
+  pdl_enter();
   const int64_t row = blockIdx.x;
   const int64_t src_row = src_stride > 1 ? (row + 1) * src_stride - 1 : row;
   const float4 *xr = reinterpret_cast<const float4 *>(x) + src_row * d4;
@@ -145,7 +146,7 @@ int launch_layernorm_strided(caten_b200_ctx *ctx, const float *x, const float *g
   if (rows <= 0) return 0;
   if (d % 4 || d > 4 * LN_THREADS * LN_MAXV) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: d=%lld (need d%%4==0, d<=2048)", (long long)d);
   if (rows > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: too many rows");
-  layernorm_kernel<<<(unsigned)rows, LN_THREADS, 0, ctx->stream>>>(x, g, b, y, (int)(d / 4), 1.0f / (float)d, eps, src_stride,
+  launch_k(ctx, layernorm_kernel, dim3((unsigned)rows), dim3(LN_THREADS), 0, x, g, b, y, (int)(d / 4), 1.0f / (float)d, eps, src_stride,
                                                                    (uint2 *)bf.hi, (uint2 *)bf.lo);
   CB_LAUNCH_CHECK(ctx, "layernorm_kernel");
   return 0;
@@ -164,6 +165,7 @@ int launch_layernorm(caten_b200_ctx *ctx, const float *x, const float *g, const 
 __global__ void embed_kernel(const float *__restrict__ ids_f32, const int64_t *__restrict__ ids_i64,
                              const float *__restrict__ wte, const float *__restrict__ wpe, float *__restrict__ out,
                              int64_t s, int64_t n, const int *__restrict__ d_n, int d4, int64_t V, int64_t T) {
+  pdl_enter();
   if (d_n) n = *d_n;  // position kept on the device (decode replayed from a CUDA graph)
   const int64_t r = blockIdx.x;
   int64_t tok = -1;
@@ -192,7 +194,7 @@ int launch_embed(caten_b200_ctx *ctx, const float *ids_f32, const int64_t *ids_i
   if (B * s <= 0) return 0;
   if (d % 4) return fail(ctx, CATEN_B200_EUNSUPPORTED, "embed: d %% 4 != 0");
   if ((ids_f32 == nullptr) == (ids_i64 == nullptr)) return fail(ctx, CATEN_B200_EINVAL, "embed: pass exactly one id array");
-  embed_kernel<<<(unsigned)(B * s), 128, 0, ctx->stream>>>(ids_f32, ids_i64, wte, wpe, out, s, n, d_n, (int)(d / 4), V, T);
+  launch_k(ctx, embed_kernel, dim3((unsigned)(B * s)), dim3(128), 0, ids_f32, ids_i64, wte, wpe, out, s, n, d_n, (int)(d / 4), V, T);
   CB_LAUNCH_CHECK(ctx, "embed_kernel");
   return 0;
 }
@@ -202,6 +204,7 @@ int launch_embed(caten_b200_ctx *ctx, const float *ids_f32, const int64_t *ids_i
 // (source/api/high-level-ops.lisp:321-325).
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ x, int64_t V, int64_t *__restrict__ out) {
+  pdl_enter();
   const float *xr = x + (int64_t)blockIdx.x * V;
   float best = -INFINITY;
   int64_t bi = V;  // V = "nothing seen"
@@ -236,6 +239,7 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ x
 // the per-position history, and the device-side position advances.
 __global__ void finish_step_kernel(const int64_t *__restrict__ out_ids, int64_t *__restrict__ ids_io,
                                    int64_t *__restrict__ hist, int *__restrict__ d_pos, int B) {
+  pdl_enter();
   const int pos = *d_pos;
   for (int b = threadIdx.x; b < B; b += blockDim.x) {
     const int64_t v = out_ids[b];
@@ -251,6 +255,7 @@ __global__ void finish_step_kernel(const int64_t *__restrict__ out_ids, int64_t 
 // start position into the device-side state.
 __global__ void begin_steps_kernel(const float *__restrict__ ids_f32, const int64_t *__restrict__ ids_i64,
                                    int64_t *__restrict__ ids_io, int *__restrict__ d_pos, int n, int B) {
+  pdl_enter();
   for (int b = threadIdx.x; b < B; b += blockDim.x) {
     if (ids_i64) {
       ids_io[b] = ids_i64[b];
@@ -264,13 +269,13 @@ __global__ void begin_steps_kernel(const float *__restrict__ ids_f32, const int6
 
 int launch_begin_steps(caten_b200_ctx *ctx, const float *ids_f32, const int64_t *ids_i64, int64_t *ids_io, int *d_pos,
                        int64_t n, int64_t B) {
-  begin_steps_kernel<<<1, 256, 0, ctx->stream>>>(ids_f32, ids_i64, ids_io, d_pos, (int)n, (int)B);
+  launch_k(ctx, begin_steps_kernel, dim3(1), dim3(256), 0, ids_f32, ids_i64, ids_io, d_pos, (int)n, (int)B);
   CB_LAUNCH_CHECK(ctx, "begin_steps_kernel");
   return 0;
 }
 
 int launch_finish_step(caten_b200_ctx *ctx, const int64_t *out_ids, int64_t *ids_io, int64_t *hist, int *d_pos, int64_t B) {
-  finish_step_kernel<<<1, 256, 0, ctx->stream>>>(out_ids, ids_io, hist, d_pos, (int)B);
+  launch_k(ctx, finish_step_kernel, dim3(1), dim3(256), 0, out_ids, ids_io, hist, d_pos, (int)B);
   CB_LAUNCH_CHECK(ctx, "finish_step_kernel");
   return 0;
 }
@@ -278,7 +283,7 @@ int launch_finish_step(caten_b200_ctx *ctx, const int64_t *out_ids, int64_t *ids
 int launch_argmax(caten_b200_ctx *ctx, const float *x, int64_t rows, int64_t V, int64_t *out) {
   if (rows <= 0) return 0;
   if (V <= 0) return fail(ctx, CATEN_B200_EINVAL, "argmax: V <= 0");
-  argmax_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(x, V, out);
+  launch_k(ctx, argmax_kernel, dim3((unsigned)rows), dim3(256), 0, x, V, out);
   CB_LAUNCH_CHECK(ctx, "argmax_kernel");
   return 0;
 }
