@@ -107,6 +107,7 @@ int caten_b200_init(int device, caten_b200_ctx **out) {
   ctx->device = device;
   ctx->sm_count = prop.multiProcessorCount;
   if (const char *e = getenv("CATEN_B200_PDL")) ctx->use_pdl = atoi(e) != 0;
+  if (const char *e = getenv("CATEN_B200_SPLITK_CLUSTER")) ctx->splitk_cluster = atoi(e) != 0;
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaStreamCreate"); }
   if ((e = cudaMalloc(&ctx->d_status, 4 * sizeof(int))) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaMalloc"); }
   cudaMemset(ctx->d_status, 0, 4 * sizeof(int));

@@ -41,6 +41,10 @@ struct caten_b200_ctx {
   cb::Scratch wtmp;          // split-K partial tiles of the tensor-core GEMM
   void *encode_tiled = nullptr;  // cuTensorMapEncodeTiled, resolved at init
   int64_t launches = 0;
+  // split-K partial tiles: reduced by a second kernel through global scratch (default: it overlaps
+  // with its neighbours under programmatic dependent launch and measured faster), or inside a
+  // thread-block cluster through distributed shared memory (CATEN_B200_SPLITK_CLUSTER=1)
+  bool splitk_cluster = false;
   bool use_pdl = true;       // programmatic dependent launch between consecutive kernels (CATEN_B200_PDL=0 turns it off)
   // per-kernel-class event timing (caten_b200_profile_begin / _end)
   unsigned prof_mask = 0;

@@ -45,6 +45,7 @@ struct TcArgs {
   // split-K: grid.z CTAs share one output tile, each covering `cps` K-chunks; partial tiles go
   // to `part` and splitk_reduce_kernel adds them in split order and applies the epilogue
   int splits, cps;
+  int cluster;  // 1: the `splits` CTAs of a tile form a thread-block cluster and reduce through distributed shared memory
   float *part;
   // when yhi is set the epilogue writes the result as split bf16 (operand of the next GEMM), not y
   __nv_bfloat16 *yhi, *ylo;
@@ -315,8 +316,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
   const int S = a.stages, bnx = a.bnx;
   const uint32_t xbytes = (uint32_t)bnx * 128u;
   const uint32_t stage_bytes = (TC_WBYTES + xbytes) * (NSPLIT == 3 ? 2u : 1u);
-  // barriers + bookkeeping live after the stage buffers
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)S * stage_bytes);
+  // first 1 KB: barriers + bookkeeping; then the stage buffers (reused as the split-K staging tile)
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
+  smem += 1024;
   const uint32_t bar0 = smem_u32(bars);
   auto full_w = [&](int s) { return bar0 + 8u * s; };
   auto full_x = [&](int s) { return bar0 + 8u * (S + s); };
@@ -429,6 +431,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
             else epi_store16<CATEN_B200_ACT_NONE>(a, r, bias, o, m0 + c);
           }
         }
+      } else if (a.cluster) {
+        // partial tile -> this CTA's shared memory, [column][row]; the stage buffers are free now
+        // (the accumulator barrier fired: every MMA has read them and every TMA copy has landed)
+        float *stg = reinterpret_cast<float *>(smem) + quad * 32 + lane;
+        for (int c = c_begin; c < c_end; c += 16) {
+          uint32_t r[16];
+          tmem_ld16(trow + (uint32_t)c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) stg[(c + i) * TC_BM] = __uint_as_float(r[i]);
+        }
       } else {
         // partial tile -> part[split][tile][column][row]: a warp stores 128 contiguous bytes
         const int tiles = gridDim.x * gridDim.y, tile = blockIdx.y * gridDim.x + blockIdx.x;
@@ -499,6 +512,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
     __syncwarp();
   }
   __syncthreads();
+  if (a.cluster) {
+    // Split-K reduction inside the cluster.  Both cluster barriers are executed by every thread
+    // of every CTA unconditionally (also after a timed-out wait), so no CTA can be left waiting.
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (tid < TC_PRODUCERS && abort_flag[3]) {
+      const int rank = blockIdx.z, nsp = a.splits;
+      const uint32_t stg0 = smem_u32(smem);
+      const int mine = (bnx - rank + nsp - 1) / nsp;  // columns rank, rank + nsp, ... of the tile
+      for (int item = tid; item < mine * 32; item += TC_PRODUCERS) {
+        const int col = rank + (item >> 5) * nsp, r4 = (item & 31) * 4;
+        const int64_t m = (int64_t)m0 + col;
+        if (m >= a.M) continue;
+        const uint32_t local = stg0 + (uint32_t)(col * TC_BM + r4) * 4u;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int z = 0; z < nsp; ++z) {  // fixed order: the sum does not depend on timing
+          uint32_t remote;
+          float4 p;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(z));
+          asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(p.x), "=f"(p.y), "=f"(p.z), "=f"(p.w) : "r"(remote) : "memory");
+          v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+        }
+        const float r[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int64_t o = (int64_t)n0 + r4 + e;
+          if (o < a.N) {
+            float t = r[e];
+            if (a.bias) t = t + a.bias[o];
+            t = apply_act(t, a.act);
+            if (a.res) t = a.res[m * a.N + o] + t;
+            if (a.yhi) {
+              const __nv_bfloat16 h = __float2bfloat16_rn(t);
+              a.yhi[m * a.N + o] = h;
+              if (a.ylo) a.ylo[m * a.N + o] = __float2bfloat16_rn(t - __bfloat162float(h));
+            } else {
+              a.y[m * a.N + o] = t;
+            }
+          }
+        }
+      }
+    }
+    // peers may still be reading this CTA's shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
   if (warp == 17) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
@@ -586,7 +643,28 @@ static int make_x_map(caten_b200_ctx *ctx, CUtensorMap *map, void *base, int64_t
 template <int WT, int NSPLIT>
 static int launch_tc_t(caten_b200_ctx *ctx, const CUtensorMap &mh, const CUtensorMap &ml, const TcArgs &a, dim3 grid, size_t smem) {
   CB_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<WT, NSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  launch_k(ctx, gemm_tc_kernel<WT, NSPLIT>, dim3(grid), dim3(TC_THREADS), smem, mh, ml, a);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute at[2];
+  int na = 0;
+  if (ctx->use_pdl) {
+    at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (a.cluster) {  // the CTAs that share an output tile (same x, y; all z) are one cluster
+    at[na].id = cudaLaunchAttributeClusterDimension;
+    at[na].val.clusterDim.x = 1;
+    at[na].val.clusterDim.y = 1;
+    at[na].val.clusterDim.z = grid.z;
+    ++na;
+  }
+  cfg.attrs = at;
+  cfg.numAttrs = na;
+  CB_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_kernel<WT, NSPLIT>, mh, ml, a));
   CB_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
   return 0;
 }
@@ -637,7 +715,6 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
   a.stages = stages;
   a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bnx >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
   a.tmem_cols = bnx < 32 ? 32u : (uint32_t)bnx;
-  const size_t smem = 1024 + stage * stages + (3 * stages + 1) * 8 + 32;
   const int64_t gy = (M + bnx - 1) / bnx;
   if (gy > 65535) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_tc: too many rows for one launch (%lld)", (long long)M);
   const int64_t gx = (N + TC_BM - 1) / TC_BM, tiles = gx * gy;
@@ -648,16 +725,22 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
     const int by_work = num_k / 4 > 0 ? num_k / 4 : 1;                       // at least 4 chunks per CTA
     const int by_fill = (int)(ctx->sm_count / tiles);                         // one wave: every CTA resident at once
     splits = by_work < by_fill ? by_work : by_fill;
-    if (splits > 32) splits = 32;
+    const int cap = ctx->splitk_cluster ? 8 : 32;                             // 8 = portable cluster size
+    if (splits > cap) splits = cap;
   }
   int cps = (num_k + splits - 1) / splits;
   splits = (num_k + cps - 1) / cps;
   a.splits = splits; a.cps = cps; a.part = nullptr;
-  if (splits > 1) {
+  a.cluster = (splits > 1 && ctx->splitk_cluster) ? 1 : 0;
+  if (splits > 1 && !a.cluster) {
     if (int rc = scratch_reserve(ctx, &ctx->wtmp, (size_t)splits * tiles * bnx * TC_BM * sizeof(float))) return rc;
     a.part = (float *)ctx->wtmp.ptr;
   }
   if (a.stages > cps) a.stages = cps;
+  // 1 KB alignment slack + 1 KB bookkeeping + the stage ring (which the split-K staging tile reuses)
+  size_t ring = stage * (size_t)a.stages;
+  if (a.cluster && ring < (size_t)bnx * TC_BM * sizeof(float)) ring = (size_t)bnx * TC_BM * sizeof(float);
+  const size_t smem = 2048 + ring;
   const dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)splits);
 
   int rc = CATEN_B200_EUNSUPPORTED;
@@ -674,7 +757,7 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
     default: return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_tc: weight type %d", wt);
   }
 #undef TC_CASE
-  if (rc || splits == 1) return rc;
+  if (rc || splits == 1 || a.cluster) return rc;
   const int64_t total = tiles * bnx * (TC_BM / 4);
   launch_k(ctx, splitk_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, a.part, splits, (int)gx, (int)tiles, bnx, bias, res, y,
                                                                               a.yhi, a.ylo, act, (int)M, (int)N);
@@ -761,9 +844,9 @@ int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, cons
   a.stages = stages > cps ? cps : stages;
   a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bnx >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
   a.tmem_cols = bnx < 32 ? 32u : (uint32_t)bnx;
-  a.splits = splits; a.cps = cps;
+  a.splits = splits; a.cps = cps; a.cluster = 0;  // partial tiles go through the fixed buffer
   a.part = splits > 1 ? (float *)(base + x_total) : nullptr;
-  const size_t smem = 1024 + stage * stages + (3 * stages + 1) * 8 + 32;
+  const size_t smem = 2048 + stage * (size_t)stages;
   const dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)splits);
   int rc = CATEN_B200_EUNSUPPORTED;
 #define TC_CASE(WT)                                                              \

@@ -341,3 +341,31 @@ def test_open_buffer_is_zero_filled_and_roundtrips(rt):
     np.testing.assert_array_equal(c.numpy(), a)
     e = rt.open_buffer((0,))
     assert e.numpy().size == 0
+
+
+def test_gemm_split_k_cluster_reduction_matches_global_reduction(oracle, monkeypatch):
+    """CATEN_B200_SPLITK_CLUSTER=1 reduces split-K partial tiles inside a thread-block cluster
+    (distributed shared memory) instead of a second kernel: same splits order, same epilogue."""
+    from caten_b200.runtime import B200Runtime
+    rng = np.random.Generator(np.random.PCG64(77))
+    up, t, raw = make_weight(rng, 1600, 1600, "q4_0")
+    x = rng.standard_normal((40, 1600), dtype=np.float32)
+    bias = rng.standard_normal(1600, dtype=np.float32) * 0.1
+    res = rng.standard_normal((40, 1600), dtype=np.float32) * 0.1
+    outs = []
+    for flag in ("0", "1"):
+        monkeypatch.setenv("CATEN_B200_SPLITK_CLUSTER", flag)
+        with B200Runtime(0) as r2:
+            w = r2.upload_weight(up)
+            y = r2.linear(w, r2.transfer_from_array(x), r2.transfer_from_array(bias), r2.transfer_from_array(res), L.ACT_GELU,
+                          L.PREC_BF16X3).numpy()
+            r2.sync()
+            outs.append(y)
+            w.close()
+    Wf = oracle.dequant(t, raw, 1600 * 1600).reshape(1600, 1600)
+    oracle.set_threads(8)
+    ref = oracle.linear(x, Wf, bias, res, 1, mode=0)
+    oracle.set_threads(1)
+    for y in outs:
+        assert np.abs(y - ref).max() <= 1e-4 * max(1.0, np.abs(ref).max())
+    assert np.abs(outs[0] - outs[1]).max() <= 1e-5
