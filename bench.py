@@ -294,7 +294,11 @@ def main():
     attn_avg_s = (attn_ms / attn_calls / 1e3) if attn_calls else float("nan")
     achieved = attn_bytes / attn_avg_s / 1e9 if attn_calls else None
     roofline = {"bound": "hbm", "kernel": "attn_decode_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": (achieved / peak) if achieved else None, "traffic": None, "peak_source": peak_src,
+                "frac": (achieved / peak) if achieved else None,
+                # DRAM bytes per launch: ncu measured dram read+write = 1.008 x algorithmic on a 64-sequence launch of
+                # this kernel (profiles/attn_decode_kernel_b64_h25_t701.md); traffic grows with sequences x context
+                "traffic": attn_bytes * 1.008, "traffic_source": "ncu capture of a smaller launch, scaled by sequences x context",
+                "peak_source": peak_src,
                 "bytes_per_launch": attn_bytes, "avg_launch_us": attn_avg_s * 1e6, "launches_timed": attn_calls,
                 "timed_in": "eager replay of the timed steps (graph mode)" if use_graph else "the timed region",
                 "share_of_step": (attn_ms / (dec_ms)) if dec_ms else None}
