@@ -434,11 +434,6 @@ static int model_linear(caten_b200_gpt2 *m, const caten_b200_weight *w, const fl
   return launch_gemm_tc_ex(ctx, w, nullptr, xbf.hi, nsplit == 3 ? xbf.lo : nullptr, bias, res, act, y, ybf, M, nsplit);
 }
 
-static int linear_any(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
-                      const float *res, int act, float *y, int64_t M, int prec) {
-  return caten_b200_linear(ctx, w, x, bias, res, act, y, M, prec);
-}
-
 extern "C" {
 
 int caten_b200_gpt2_create(caten_b200_ctx *ctx, const caten_b200_gpt2_desc *dsc, caten_b200_gpt2 **out) {

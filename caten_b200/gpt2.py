@@ -17,8 +17,6 @@ from . import _lib as L
 from .runtime import B200Buffer, B200Runtime, B200Weight
 from .synthetic import GPT2_SIZES, GPT2Params, Packed
 
-_LINEAR_KEYS = ("attn.c_attn", "attn.c_proj", "mlp.c_fc", "mlp.c_proj")
-
 
 class GPT2:
     def __init__(self, runtime: B200Runtime, params: GPT2Params, state_dict: dict, max_seq_len: int = 1024,
