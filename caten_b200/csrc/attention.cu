@@ -20,7 +20,8 @@ constexpr float kInvLn2 = 1.0f / 0.6931472f;  // (/ (log 2)) in single float, ap
 __global__ void __launch_bounds__(256) attn_decode_kernel(const float *__restrict__ qkv, float *__restrict__ kc,
                                                           float *__restrict__ vc, float *__restrict__ out, int H,
                                                           int T, int n, const int *__restrict__ d_n,
-                                                          __nv_bfloat16 *__restrict__ ohi, __nv_bfloat16 *__restrict__ olo) {
+                                                          __nv_bfloat16 *__restrict__ ohi, __nv_bfloat16 *__restrict__ olo,
+                                                          const PartIn pin) {
   pdl_enter();
   if (d_n) n = *d_n;  // position kept on the device (decode replayed from a CUDA graph)
   extern __shared__ float smem[];
@@ -33,7 +34,16 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float *__restric
   const float *row = qkv + (int64_t)b * 3 * d;
   float *kb = kc + ((int64_t)b * H + h) * T * 64;
   float *vb = vc + ((int64_t)b * H + h) * T * 64;
-  if (tid < 64) {
+  if (pin.splits > 0) {
+    // the qkv linear left split-K partial tiles: sum this head's q, k, v entries here
+    if (tid < 192) {
+      const int which = tid >> 6, e = tid & 63;
+      const float val = partin_load1(pin, b, which * d + h * 64 + e);
+      if (which == 0) q[e] = val;
+      else if (which == 1) kb[(int64_t)n * 64 + e] = val;
+      else vb[(int64_t)n * 64 + e] = val;
+    }
+  } else if (tid < 64) {
     q[tid] = row[h * 64 + tid];
     kb[(int64_t)n * 64 + tid] = row[d + h * 64 + tid];
     vb[(int64_t)n * 64 + tid] = row[2 * d + h * 64 + tid];
@@ -293,8 +303,9 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
 }
 
 int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc, float *out, int64_t B, int64_t s,
-                     int64_t n, int64_t H, int64_t T, const int *d_n, BfOut bf) {
+                     int64_t n, int64_t H, int64_t T, const int *d_n, BfOut bf, const PartIn *pending_qkv) {
   if (B <= 0 || s <= 0) return 0;
+  if (pending_qkv && pending_qkv->splits > 0 && s != 1) return fail(ctx, CATEN_B200_EINVAL, "attention: a pending qkv is only supported for single-token steps");
   if (n < 0 || n + s > T) return fail(ctx, CATEN_B200_EINVAL, "attention: positions [%lld,%lld) outside the cache (T=%lld)", (long long)n, (long long)(n + s), (long long)T);
   if (H > 65535 || B > 65535) return fail(ctx, CATEN_B200_EUNSUPPORTED, "attention: B or H > 65535");
   if (s == 1) {
@@ -303,7 +314,8 @@ int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc
     if (smem > 200 * 1024) return fail(ctx, CATEN_B200_EUNSUPPORTED, "attention: context too long for the decode kernel");
     if (smem > 48 * 1024)
       CB_CUDA(ctx, cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    launch_k(ctx, attn_decode_kernel, dim3((unsigned)H, (unsigned)B), dim3(256), smem, qkv, kc, vc, out, (int)H, (int)T, (int)n, d_n, bf.hi, bf.lo);
+    launch_k(ctx, attn_decode_kernel, dim3((unsigned)H, (unsigned)B), dim3(256), smem, qkv, kc, vc, out, (int)H, (int)T, (int)n, d_n, bf.hi, bf.lo,
+             pending_qkv ? *pending_qkv : PartIn());
     CB_LAUNCH_CHECK(ctx, "attn_decode_kernel");
     return 0;
   }

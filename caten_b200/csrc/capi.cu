@@ -420,18 +420,20 @@ struct caten_b200_gpt2 {
   cudaGraphExec_t graph = nullptr;
   void *graph_xbf = nullptr, *graph_wtmp = nullptr;  // scratch pointers baked into the graph
   int64_t launches_per_step = 0;
+  bool defer_reduce = true;  // CATEN_B200_DEFER_REDUCE=0 keeps a reduction kernel behind every split-K linear
 };
 
 // Linear inside the model: with a tensor-core precision and more than 4 rows the input arrives
 // already split into bf16 (hi, lo) from its producer and the output can be requested the same way.
 static int model_linear(caten_b200_gpt2 *m, const caten_b200_weight *w, const float *x, cb::BfOut xbf, const float *bias,
-                        const float *res, int act, float *y, cb::BfOut ybf, int64_t M) {
+                        const float *res, int act, float *y, cb::BfOut ybf, int64_t M, cb::PartIn *defer = nullptr) {
+  if (defer) *defer = cb::PartIn();
   caten_b200_ctx *ctx = m->ctx;
   const int prec = m->desc.precision;
   if (prec == CATEN_B200_PREC_FP32 || M <= 4) return caten_b200_linear(ctx, w, x, bias, res, act, y, M, prec);
   ProfScope prof(ctx, CATEN_B200_K_GEMM);
   const int nsplit = prec == CATEN_B200_PREC_BF16X3 ? 3 : 1;
-  return launch_gemm_tc_ex(ctx, w, nullptr, xbf.hi, nsplit == 3 ? xbf.lo : nullptr, bias, res, act, y, ybf, M, nsplit);
+  return launch_gemm_tc_ex(ctx, w, nullptr, xbf.hi, nsplit == 3 ? xbf.lo : nullptr, bias, res, act, y, ybf, M, nsplit, defer);
 }
 
 extern "C" {
@@ -448,6 +450,7 @@ int caten_b200_gpt2_create(caten_b200_ctx *ctx, const caten_b200_gpt2_desc *dsc,
   caten_b200_gpt2 *m = new (std::nothrow) caten_b200_gpt2();
   if (!m) return fail(ctx, CATEN_B200_ECUDA, "out of host memory");
   m->ctx = ctx;
+  if (const char *e = getenv("CATEN_B200_DEFER_REDUCE")) m->defer_reduce = atoi(e) != 0;
   m->desc = *dsc;
   for (int64_t l = 0; l < L; ++l) {
     const caten_b200_weight *ws[4] = {dsc->attn_w[l], dsc->proj_w[l], dsc->fc_w[l], dsc->mproj_w[l]};
@@ -552,23 +555,32 @@ static int run_chunk(caten_b200_gpt2 *m, const float *ids_f32, const int64_t *id
   const bool x3 = prec == CATEN_B200_PREC_BF16X3;
   auto bf = [&](cb::BfOut b) { cb::BfOut o; if (fused) { o.hi = b.hi; o.lo = x3 ? b.lo : nullptr; } return o; };
   const cb::BfOut none;
+  // Single-token steps: a split-K linear whose consumer can sum the partial tiles while loading
+  // (LayerNorm for the two projections, attention for qkv) skips its reduction kernel.
+  const bool defer_ok = fused && s == 1 && m->defer_reduce;
+  cb::PartIn pend_h, pend_qkv, pend_h2;  // pending outputs of mlp.c_proj (-> h), c_attn, attn.c_proj (-> h2)
+  auto layernorm = [&](const cb::PartIn &pin, const float *res, float *x, const float *g, const float *b, float *y, int64_t rows,
+                       int64_t stride, cb::BfOut o) {
+    ProfScope prof(ctx, CATEN_B200_K_LAYERNORM);
+    // pending: x = res + linear output is formed (and stored) by the LayerNorm kernel itself
+    return pin.splits > 0 ? launch_layernorm_pending(ctx, pin, res, x, g, b, y, rows, d, eps, stride, o)
+                          : launch_layernorm_strided(ctx, x, g, b, y, rows, d, eps, stride, o);
+  };
   for (int64_t l = 0; l < L; ++l) {
-    int rc;
-    { ProfScope prof(ctx, CATEN_B200_K_LAYERNORM); rc = launch_layernorm_strided(ctx, m->h, m->ln1_g[l], m->ln1_b[l], m->xn, R, d, eps, 1, bf(m->xn_bf)); }
-    if (!rc) rc = model_linear(m, m->attn_w[l], m->xn, m->xn_bf, m->attn_b[l], nullptr, CATEN_B200_ACT_NONE, m->qkv, none, R);
-    if (!rc) { ProfScope prof(ctx, s == 1 ? CATEN_B200_K_ATTN_DECODE : CATEN_B200_K_ATTN_PREFILL); rc = launch_attention(ctx, m->qkv, m->kc[l] + kv_off, m->vc[l] + kv_off, m->att, nb, s, n, H, T, d_n, bf(m->att_bf)); }
-    if (!rc) rc = model_linear(m, m->proj_w[l], m->att, m->att_bf, m->proj_b[l], m->h, CATEN_B200_ACT_NONE, m->h2, none, R);
-    if (!rc) { ProfScope prof(ctx, CATEN_B200_K_LAYERNORM); rc = launch_layernorm_strided(ctx, m->h2, m->ln2_g[l], m->ln2_b[l], m->xn, R, d, eps, 1, bf(m->xn_bf)); }
+    int rc = layernorm(pend_h, m->h2, m->h, m->ln1_g[l], m->ln1_b[l], m->xn, R, 1, bf(m->xn_bf));
+    if (!rc) rc = model_linear(m, m->attn_w[l], m->xn, m->xn_bf, m->attn_b[l], nullptr, CATEN_B200_ACT_NONE, m->qkv, none, R, defer_ok ? &pend_qkv : nullptr);
+    if (!rc) { ProfScope prof(ctx, s == 1 ? CATEN_B200_K_ATTN_DECODE : CATEN_B200_K_ATTN_PREFILL); rc = launch_attention(ctx, m->qkv, m->kc[l] + kv_off, m->vc[l] + kv_off, m->att, nb, s, n, H, T, d_n, bf(m->att_bf), &pend_qkv); }
+    if (!rc) rc = model_linear(m, m->proj_w[l], m->att, m->att_bf, m->proj_b[l], m->h, CATEN_B200_ACT_NONE, m->h2, none, R, defer_ok ? &pend_h2 : nullptr);
+    if (!rc) rc = layernorm(pend_h2, m->h, m->h2, m->ln2_g[l], m->ln2_b[l], m->xn, R, 1, bf(m->xn_bf));
     if (!rc) rc = model_linear(m, m->fc_w[l], m->xn, m->xn_bf, m->fc_b[l], nullptr, CATEN_B200_ACT_GELU, m->ff, bf(m->ff_bf), R);
-    if (!rc) rc = model_linear(m, m->mproj_w[l], m->ff, m->ff_bf, m->mproj_b[l], m->h2, CATEN_B200_ACT_NONE, m->h, none, R);
+    if (!rc) rc = model_linear(m, m->mproj_w[l], m->ff, m->ff_bf, m->mproj_b[l], m->h2, CATEN_B200_ACT_NONE, m->h, none, R, defer_ok ? &pend_h : nullptr);
     if (rc) return rc;
   }
   // ln_f on the last position of every sequence only (the reference views the last row of the
   // logits, layers.lisp:90), gathered into rows [b0, b0+nb) of `last`
-  ProfScope prof(ctx, CATEN_B200_K_LAYERNORM);
   cb::BfOut lb;
   if (prec != CATEN_B200_PREC_FP32 && c.batch > 4) { lb.hi = m->last_bf.hi + b0 * d; lb.lo = x3 ? m->last_bf.lo + b0 * d : nullptr; }
-  return launch_layernorm_strided(ctx, m->h, c.lnf_g, c.lnf_b, m->last + b0 * d, nb, d, eps, s, lb);
+  return layernorm(pend_h, m->h2, m->h, c.lnf_g, c.lnf_b, m->last + b0 * d, nb, s, lb);
 }
 
 int caten_b200_gpt2_step_device(caten_b200_gpt2 *m, const float *d_ids_f32, const int64_t *d_ids_i64, int64_t s, int64_t n,

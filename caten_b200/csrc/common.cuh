@@ -23,6 +23,43 @@ struct BfOut {
   __nv_bfloat16 *hi = nullptr, *lo = nullptr;
 };
 
+// Output of a split-K linear that has not been summed yet.  The GEMM leaves its partial tiles
+// part[split][tile][column = m % bnx][row = o % 128] in scratch memory and the kernel that
+// consumes the result adds them (in split order, then the bias) while it loads its input:
+//   y[m, o] = (sum_z part[z][tile(m, o)][m % bnx][o % 128]) + bias[o]
+// splits == 0 means "nothing pending": the consumer reads the finished tensor instead.
+struct PartIn {
+  const float *part = nullptr, *bias = nullptr;
+  int splits = 0, tiles_x = 0, bnx = 0;
+  long long zstride = 0;  // floats between consecutive splits
+};
+
+#ifdef __CUDACC__
+// four consecutive output features o..o+3 (o a multiple of 4) of activation row m
+__device__ __forceinline__ float4 partin_load4(const PartIn &p, long long m, int o) {
+  const long long tile = (m / p.bnx) * p.tiles_x + (o >> 7);
+  const float *src = p.part + (tile * p.bnx + (m % p.bnx)) * 128 + (o & 127);
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int z = 0; z < p.splits; ++z) {
+    const float4 a = __ldcs(reinterpret_cast<const float4 *>(src + (long long)z * p.zstride));
+    v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+  }
+  if (p.bias) {
+    const float4 b = *reinterpret_cast<const float4 *>(p.bias + o);
+    v.x = v.x + b.x; v.y = v.y + b.y; v.z = v.z + b.z; v.w = v.w + b.w;
+  }
+  return v;
+}
+__device__ __forceinline__ float partin_load1(const PartIn &p, long long m, int o) {
+  const long long tile = (m / p.bnx) * p.tiles_x + (o >> 7);
+  const float *src = p.part + (tile * p.bnx + (m % p.bnx)) * 128 + (o & 127);
+  float v = 0.f;
+  for (int z = 0; z < p.splits; ++z) v += __ldcs(src + (long long)z * p.zstride);
+  if (p.bias) v = v + p.bias[o];
+  return v;
+}
+#endif
+
 struct Scratch {
   void *ptr = nullptr;
   size_t bytes = 0;
@@ -88,6 +125,10 @@ int launch_layernorm(caten_b200_ctx *ctx, const float *x, const float *g, const 
 // src_rows: optional gather — row r of the output reads row (r+1)*src_stride-1 of x when src_stride > 1
 int launch_layernorm_strided(caten_b200_ctx *ctx, const float *x, const float *g, const float *b, float *y,
                              int64_t rows, int64_t d, float eps, int64_t src_stride, cb::BfOut bf = cb::BfOut());
+// LayerNorm of x = res + pending linear output; also stores x (the new residual stream) to xout
+int launch_layernorm_pending(caten_b200_ctx *ctx, const cb::PartIn &pin, const float *res, float *xout, const float *g,
+                             const float *b, float *y, int64_t rows, int64_t d, float eps, int64_t src_stride,
+                             cb::BfOut bf = cb::BfOut());
 int launch_embed(caten_b200_ctx *ctx, const float *ids_f32, const int64_t *ids_i64, const float *wte,
                  const float *wpe, float *out, int64_t B, int64_t s, int64_t n, int64_t d, int64_t V, int64_t T,
                  const int *d_n = nullptr);
@@ -96,7 +137,8 @@ int launch_begin_steps(caten_b200_ctx *ctx, const float *ids_f32, const int64_t 
 int launch_finish_step(caten_b200_ctx *ctx, const int64_t *out_ids, int64_t *ids_io, int64_t *hist, int *d_pos, int64_t B);
 int launch_argmax(caten_b200_ctx *ctx, const float *x, int64_t rows, int64_t V, int64_t *out);
 int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc, float *out, int64_t B,
-                     int64_t s, int64_t n, int64_t H, int64_t T, const int *d_n = nullptr, cb::BfOut bf = cb::BfOut());
+                     int64_t s, int64_t n, int64_t H, int64_t T, const int *d_n = nullptr, cb::BfOut bf = cb::BfOut(),
+                     const cb::PartIn *pending_qkv = nullptr);
 int launch_gemv(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
                 const float *res, int act, float *y);
 int launch_gemm_simt(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
@@ -107,7 +149,10 @@ int launch_gemm_tc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float 
 // or, when ybf.hi is set, as bf16 hi/lo for the next GEMM
 int launch_gemm_tc_ex(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const __nv_bfloat16 *xhi,
                       const __nv_bfloat16 *xlo, const float *bias, const float *res, int act, float *y, cb::BfOut ybf,
-                      int64_t M, int nsplit);
+                      int64_t M, int nsplit, cb::PartIn *defer = nullptr);
+// `defer`: when the launch is split-K with no activation, skip the reduction kernel and describe the
+// partial tiles in *defer instead (bias and residual are then the consumer's job); otherwise
+// defer->splits stays 0 and y is complete
 int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
                            const float *res, int act, float *y, int64_t M, int nsplit);
 // relu(a.b) with b given [K, N] row-major fp32

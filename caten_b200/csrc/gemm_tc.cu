@@ -148,49 +148,78 @@ __device__ __forceinline__ void store8(uint8_t *whi, uint8_t *wlo, int r, int c,
 // convert-and-store step so that the loads of later chunks are in flight while the current one
 // is dequantised (DEPTH chunks of look-ahead hide the HBM latency of the packed stream).
 //
-// 512 producer threads.  For the row-major formats warp w owns rows 8w..8w+7 and lane l is
-// (row 8w + (l & 7), part l >> 3): one warp-wide load reads 8 rows x one contiguous run per row
-// (whole 32-byte sectors), and the 8 lanes that store together write 8 different rows, which the
-// 128-byte swizzle spreads over all banks.
+// The 512 producer threads form GROUPS groups that take the chunks in turn; `t` is the thread's
+// index inside its group.  With one group (all formats but Q4_0) warp w owns rows 8w..8w+7 and
+// lane l is (row 8w + (l & 7), part l >> 3): one warp-wide load reads 8 rows x one contiguous run
+// per row (whole 32-byte sectors), and the 8 lanes that store together write 8 different rows,
+// which the 128-byte swizzle spreads over all banks.
 template <int WT> struct WChunk;
 
-// exact (float)(nibble - 8): 0x4B000000 | nibble is the float 2^23 + nibble
-__device__ __forceinline__ float nib_to_float(uint32_t word, int shift) {
-  return __uint_as_float(((word >> shift) & 0xFu) | 0x4B000000u) - 8388616.0f;
-}
-
+// Q4_0, converted with packed bf16 arithmetic (two weights per instruction, no fp32 detour).
+// The producers work as two groups of 256 threads that take alternate chunks; a thread owns one
+// whole block (16 code bytes = 32 weights) of one row: warp w of the group holds rows
+// 16w..16w+15, lane l is (row 16w + (l & 15), block l >> 4).
+//   A  = code - 8                      exact in bf16 (|A| <= 8)
+//   d  = dh + dl, dh = bf16(d)         exact: an fp16 scale has 11 significant bits, dl at most 3
+//   hi = bf16(A * dh)                  one rounding
+//   lo = bf16(A * dl + (A * dh - hi))  the inner difference is exact; hi + lo = A * d to 2^-17
+// NSPLIT = 1 stores bf16(A * d) (correctly rounded: A * dl is exact, then one fused rounding).
 template <> struct WChunk<CATEN_B200_Q4_0> {
-  static constexpr int DEPTH = 4;
-  uint2 q;   // 8 of the block's 16 code bytes: low nibbles = 8 elements, high nibbles = 8 more
-  float sc;
-  __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int tid) {
-    const int l = tid & 31, part = l >> 3;
-    const int64_t row = (int64_t)n0 + 8 * (tid >> 5) + (l & 7);
-    const int64_t bi = row * a.nkb + (int64_t)kc * 2 + (part >> 1);
+  static constexpr int DEPTH = 4, GROUPS = 2;
+  uint4 q;      // byte j: low nibble = element j, high nibble = element j + 16
+  __half sc;
+  __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int t) {
+    const int l = t & 31;
+    const int64_t row = (int64_t)n0 + 16 * (t >> 5) + (l & 15);
+    const int64_t bi = row * a.nkb + (int64_t)kc * 2 + (l >> 4);
     if (row < a.N) {
-      q = __ldcs(reinterpret_cast<const uint2 *>(a.qs) + bi * 2 + (part & 1));
-      sc = __half2float(a.d[bi]);
+      q = __ldcs(reinterpret_cast<const uint4 *>(a.qs) + bi);
+      sc = a.d[bi];
     } else {
-      q = make_uint2(0x88888888u, 0x88888888u);
-      sc = 0.0f;
+      q = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+      sc = __ushort_as_half((unsigned short)0);
     }
   }
-  template <int NSPLIT> __device__ __forceinline__ void store(uint8_t *whi, uint8_t *wlo, int tid) const {
-    const int l = tid & 31, part = l >> 3, r = 8 * (tid >> 5) + (l & 7), blk = part >> 1, h = part & 1;
-    const uint32_t wd[2] = {q.x, q.y};
-    // bytes 8h..8h+7 of the block: low nibbles are elements 8h.., high nibbles elements 16+8h..
+  // the two code bytes `first`, `first + 1` of `word` (already shifted so that the wanted nibbles
+  // are the low ones) -> bf16x2 (code0 - 8, code1 - 8); 0x4300 | n is the bf16 value 128 + n
+  template <int FIRST> static __device__ __forceinline__ __nv_bfloat162 codes2(uint32_t word) {
+    const uint32_t two = __byte_perm(word, 0u, FIRST == 0 ? 0x4140u : 0x4342u);
+    const uint32_t bits = (two & 0x000F000Fu) | 0x43004300u;
+    const uint32_t off = 0x43084308u;  // bf16x2 (136, 136)
+    return __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&bits), *reinterpret_cast<const __nv_bfloat162 *>(&off));
+  }
+  template <int NSPLIT> __device__ __forceinline__ void store(uint8_t *whi, uint8_t *wlo, int t) const {
+    const int l = t & 31, r = 16 * (t >> 5) + (l & 15), blk = l >> 4;
+    const float d = __half2float(sc);
+    const __nv_bfloat16 dh1 = __float2bfloat16_rn(d);
+    const __nv_bfloat16 dl1 = __float2bfloat16_rn(d - __bfloat162float(dh1));
+    const __nv_bfloat162 dh = __halves2bfloat162(dh1, dh1), dl = __halves2bfloat162(dl1, dl1);
+    const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-    for (int hi = 0; hi < 2; ++hi) {
-      float w[8];
+    for (int part = 0; part < 4; ++part) {  // elements 8 * part .. 8 * part + 7 of the block
+      uint32_t h[4], lo[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) w[e] = nib_to_float(wd[e >> 2], 8 * (e & 3) + hi * 4) * sc;
-      store8<NSPLIT>(whi, wlo, r, blk * 4 + hi * 2 + h, w);
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t word = wd[(part & 1) * 2 + (j >> 1)] >> (part >= 2 ? 4 : 0);
+        const __nv_bfloat162 A = (j & 1) ? codes2<2>(word) : codes2<0>(word);
+        if (NSPLIT == 3) {
+          const __nv_bfloat162 hv = __hmul2(A, dh);
+          const __nv_bfloat162 lv = __hfma2(A, dl, __hfma2(A, dh, __hneg2(hv)));
+          h[j] = *reinterpret_cast<const uint32_t *>(&hv);
+          lo[j] = *reinterpret_cast<const uint32_t *>(&lv);
+        } else {
+          const __nv_bfloat162 hv = __hfma2(A, dh, __hmul2(A, dl));
+          h[j] = *reinterpret_cast<const uint32_t *>(&hv);
+        }
+      }
+      *reinterpret_cast<uint4 *>(whi + swz(r, blk * 4 + part)) = make_uint4(h[0], h[1], h[2], h[3]);
+      if (NSPLIT == 3) *reinterpret_cast<uint4 *>(wlo + swz(r, blk * 4 + part)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
   }
 };
 
 template <> struct WChunk<CATEN_B200_Q8_0> {
-  static constexpr int DEPTH = 3;
+  static constexpr int DEPTH = 3, GROUPS = 1;
   uint4 q;   // 16 of the block's 32 codes
   float sc;
   __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int tid) {
@@ -219,7 +248,7 @@ template <> struct WChunk<CATEN_B200_Q8_0> {
 };
 
 template <> struct WChunk<CATEN_B200_F32> {
-  static constexpr int DEPTH = 2;
+  static constexpr int DEPTH = 2, GROUPS = 1;
   float4 v[4];
   __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int tid) {
     const int l = tid & 31;
@@ -244,7 +273,7 @@ template <> struct WChunk<CATEN_B200_F32> {
 };
 
 template <> struct WChunk<CATEN_B200_F16> {
-  static constexpr int DEPTH = 3;
+  static constexpr int DEPTH = 3, GROUPS = 1;
   uint4 v[2];
   __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int tid) {
     const int l = tid & 31;
@@ -269,7 +298,7 @@ template <> struct WChunk<CATEN_B200_F16> {
 
 // b[k, n] (relu_matmul): thread = (n, quarter of the 64 k); loads coalesced across n
 template <> struct WChunk<WT_F32_T> {
-  static constexpr int DEPTH = 2;
+  static constexpr int DEPTH = 2, GROUPS = 1;
   float v[16];
   __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int tid) {
     const int64_t col = (int64_t)n0 + (tid & 127);
@@ -326,7 +355,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
   const uint32_t accum_bar = bar0 + 8u * (3 * S);
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
   // [0] some role gave up a wait; [1] never set (for waits that must not be cut short);
-  // [2], [3] thread 0's verdict for the producer warps (stage free / accumulator ready)
+  // [3] thread 0's verdict for the producer warps: accumulator ready
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   auto stage_whi = [&](int s) { return smem + (size_t)s * stage_bytes; };
   auto stage_wlo = [&](int s) { return smem + (size_t)s * stage_bytes + TC_WBYTES; };
@@ -340,7 +369,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(full_w(s), 1);
+      mbar_init(full_w(s), TC_PRODUCERS / 32 / WChunk<WT>::GROUPS);  // one arrival per warp of a producer group
       mbar_init(full_x(s), 1);
       mbar_init(empty(s), 1);
     }
@@ -366,38 +395,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
 
   if (warp < 16) {
     // ---------------- weight producers ----------------
-    // Only thread 0 polls the stage's `empty` mbarrier; the other producer warps sleep on a
-    // hardware named barrier instead of spinning (spinning warps would take issue slots from the
-    // warps that are dequantising).  Per chunk: [barrier 2] slot is free -> convert + store ->
-    // fence -> [barrier 3] all stores done -> thread 0 signals `full_w`.
-    constexpr int DEPTH = WChunk<WT>::DEPTH;
+    // The producer warps run independently of one another.  They form GROUPS groups that take the
+    // chunks in turn; for its chunk a warp's lane 0 polls the stage's `empty` mbarrier, the warp
+    // converts and stores its rows, and lane 0 arrives on `full_w` (which counts one arrival per
+    // warp of a group).  A warp that is ahead starts on its next stage while others are still
+    // storing, so conversion, barrier latency and the MMAs overlap.
+    constexpr int DEPTH = WChunk<WT>::DEPTH, GROUPS = WChunk<WT>::GROUPS, GSIZE = TC_PRODUCERS / GROUPS;
+    const int g = tid / GSIZE, t = tid % GSIZE;
     WChunk<WT> ring[DEPTH];
 #pragma unroll
     for (int j = 0; j < DEPTH; ++j)
-      if (j < num_k) ring[j].load(a, n0, kc0 + j, tid);
-    int s = 0;
+      if (j * GROUPS + g < num_k) ring[j].load(a, n0, kc0 + j * GROUPS + g, t);
+    int s = g;
     uint32_t ph = 0;
+    while (s >= S) { s -= S; ph ^= 1u; }
     bool alive = true;
-    for (int kb = 0; kb < num_k && alive; kb += DEPTH) {
+    for (int kb = 0; kb * GROUPS + g < num_k && alive; kb += DEPTH) {
 #pragma unroll
       for (int j = 0; j < DEPTH; ++j) {
-        const int kc = kb + j;
+        const int kc = (kb + j) * GROUPS + g;
         if (kc < num_k && alive) {
-          if (tid == 0) {
-            const bool got = mbar_wait(empty(s), ph ^ 1u, abort_flag);
+          int got = 0;
+          if (lane == 0) {
+            got = mbar_wait(empty(s), ph ^ 1u, abort_flag) ? 1 : 0;
             if (!got && !*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 1; a.status[2] = kc; }
-            abort_flag[2] = (got && !*abort_flag) ? 1 : 0;  // one verdict for all 512 producers
           }
-          asm volatile("bar.sync 2, 512;" ::: "memory");
-          if (!abort_flag[2]) {
+          got = __shfl_sync(0xffffffffu, got, 0);
+          if (!got) {
             alive = false;
           } else {
-            ring[j].template store<NSPLIT>(stage_whi(s), stage_wlo(s), tid);
+            ring[j].template store<NSPLIT>(stage_whi(s), stage_wlo(s), t);
             fence_proxy_async();  // this thread's stores -> visible to the tensor core's (async proxy) reads
-            asm volatile("bar.sync 3, 512;" ::: "memory");
-            if (tid == 0) mbar_arrive(full_w(s));
-            if (kc + DEPTH < num_k) ring[j].load(a, n0, kc0 + kc + DEPTH, tid);
-            if (++s == S) { s = 0; ph ^= 1u; }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_w(s));
+            if (kc + DEPTH * GROUPS < num_k) ring[j].load(a, n0, kc0 + kc + DEPTH * GROUPS, t);
+            s += GROUPS;
+            while (s >= S) { s -= S; ph ^= 1u; }
           }
         }
       }
@@ -671,7 +704,9 @@ static int launch_tc_t(caten_b200_ctx *ctx, const CUtensorMap &mh, const CUtenso
 
 static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, int64_t nkb, const float *x,
                   const float *bias, const float *res, int act, float *y, int64_t M, int64_t N, int64_t K, int nsplit,
-                  const __nv_bfloat16 *xhi_pre = nullptr, const __nv_bfloat16 *xlo_pre = nullptr, BfOut ybf = BfOut()) {
+                  const __nv_bfloat16 *xhi_pre = nullptr, const __nv_bfloat16 *xlo_pre = nullptr, BfOut ybf = BfOut(),
+                  PartIn *defer = nullptr) {
+  if (defer) *defer = PartIn();
   if (M <= 0 || N <= 0) return 0;
   if (!ctx->encode_tiled) return fail(ctx, CATEN_B200_ECUDA, "gemm_tc: cuTensorMapEncodeTiled is not available");
   if (K % TC_BK) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_tc: inner dimension %lld is not a multiple of 64", (long long)K);
@@ -758,6 +793,12 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
   }
 #undef TC_CASE
   if (rc || splits == 1 || a.cluster) return rc;
+  if (defer && act == CATEN_B200_ACT_NONE && !a.yhi && N % 4 == 0) {
+    // the consumer of this linear sums the partial tiles itself (and adds bias / residual)
+    defer->part = a.part; defer->bias = bias; defer->splits = splits; defer->tiles_x = (int)gx; defer->bnx = bnx;
+    defer->zstride = (long long)tiles * bnx * TC_BM;
+    return 0;
+  }
   const int64_t total = tiles * bnx * (TC_BM / 4);
   launch_k(ctx, splitk_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, a.part, splits, (int)gx, (int)tiles, bnx, bias, res, y,
                                                                               a.yhi, a.ylo, act, (int)M, (int)N);
@@ -876,8 +917,8 @@ int launch_gemm_tc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float 
 
 int launch_gemm_tc_ex(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const __nv_bfloat16 *xhi,
                       const __nv_bfloat16 *xlo, const float *bias, const float *res, int act, float *y, BfOut ybf, int64_t M,
-                      int nsplit) {
-  return run_tc(ctx, w->type, w->qs, w->d, w->nkb, x, bias, res, act, y, M, w->rows, w->cols, nsplit, xhi, xlo, ybf);
+                      int nsplit, PartIn *defer) {
+  return run_tc(ctx, w->type, w->qs, w->d, w->nkb, x, bias, res, act, y, M, w->rows, w->cols, nsplit, xhi, xlo, ybf, defer);
 }
 
 int launch_relu_matmul_tc(caten_b200_ctx *ctx, const float *a, const float *b, float *c, int64_t M, int64_t K, int64_t N, int nsplit) {

@@ -91,7 +91,8 @@ __device__ __forceinline__ float ln_block_sum(float v, float *red) {
 __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__restrict__ x, const float *__restrict__ g,
                                                                const float *__restrict__ b, float *__restrict__ y,
                                                                int d4, float invd, float eps, int64_t src_stride,
-                                                               uint2 *__restrict__ yhi, uint2 *__restrict__ ylo) {
+                                                               uint2 *__restrict__ yhi, uint2 *__restrict__ ylo,
+                                                               const PartIn pin, float *__restrict__ xout) {
   __shared__ float red[LN_THREADS / 32];
   pdl_enter();
   const int64_t row = blockIdx.x;
@@ -104,6 +105,13 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__re
     const int c = threadIdx.x + LN_THREADS * i;
     if (c < d4) {
       v[i] = xr[c];
+      if (pin.splits > 0) {
+        // x is the residual input; the row normalised is residual + the pending linear output,
+        // which also becomes the new residual stream
+        const float4 t = partin_load4(pin, src_row, 4 * c);
+        v[i].x = v[i].x + t.x; v[i].y = v[i].y + t.y; v[i].z = v[i].z + t.z; v[i].w = v[i].w + t.w;
+        reinterpret_cast<float4 *>(xout)[src_row * d4 + c] = v[i];
+      }
       sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
     }
   }
@@ -147,7 +155,19 @@ int launch_layernorm_strided(caten_b200_ctx *ctx, const float *x, const float *g
   if (d % 4 || d > 4 * LN_THREADS * LN_MAXV) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: d=%lld (need d%%4==0, d<=2048)", (long long)d);
   if (rows > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: too many rows");
   launch_k(ctx, layernorm_kernel, dim3((unsigned)rows), dim3(LN_THREADS), 0, x, g, b, y, (int)(d / 4), 1.0f / (float)d, eps, src_stride,
-                                                                   (uint2 *)bf.hi, (uint2 *)bf.lo);
+                                                                   (uint2 *)bf.hi, (uint2 *)bf.lo, PartIn(), (float *)nullptr);
+  CB_LAUNCH_CHECK(ctx, "layernorm_kernel");
+  return 0;
+}
+
+int launch_layernorm_pending(caten_b200_ctx *ctx, const PartIn &pin, const float *res, float *xout, const float *g, const float *b,
+                             float *y, int64_t rows, int64_t d, float eps, int64_t src_stride, BfOut bf) {
+  if (rows <= 0) return 0;
+  if (pin.splits <= 0 || !res || !xout) return fail(ctx, CATEN_B200_EINVAL, "layernorm: no pending linear output");
+  if (d % 4 || d > 4 * LN_THREADS * LN_MAXV) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: d=%lld (need d%%4==0, d<=2048)", (long long)d);
+  if (rows > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: too many rows");
+  launch_k(ctx, layernorm_kernel, dim3((unsigned)rows), dim3(LN_THREADS), 0, res, g, b, y, (int)(d / 4), 1.0f / (float)d, eps, src_stride,
+                                                                   (uint2 *)bf.hi, (uint2 *)bf.lo, pin, xout);
   CB_LAUNCH_CHECK(ctx, "layernorm_kernel");
   return 0;
 }

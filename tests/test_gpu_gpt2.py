@@ -145,6 +145,35 @@ def test_graph_replayed_decode_is_repeatable(rt, precision, batch):
     ref.close(); m.close()
 
 
+WIDE = S.GPT2Params(n_layers=2, n_heads=8, dim=512, vocab_size=1003)  # wide enough for split-K linears
+
+
+def test_wide_bf16x3_parity_with_split_k(rt, oracle):
+    """d=512: the decode linears run split-K and their consumers (LayerNorm, attention) sum the
+    partial tiles; same bounds as every other bf16x3 case."""
+    run_parity(rt, oracle, WIDE, "q4_0", "bf16x3", B=6, prompt_len=7, steps=5, T=40, logit_tol=1e-3)
+
+
+def test_deferred_split_k_reduction_is_bit_identical(rt, monkeypatch):
+    """Summing the split-K partial tiles inside the consuming kernel gives the same bits as the
+    separate reduction kernel (same order of additions)."""
+    sd = S.synth_state_dict(WIDE, "q4_0", seed=9, max_seq_len=40, trivial_affine=False, weight_std=0.08)
+    prompt = S.synth_prompts(6, 5, WIDE.vocab_size, seed=8)
+    outs = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("CATEN_B200_DEFER_REDUCE", flag)
+        m = GPT2(rt, WIDE, sd, max_seq_len=40, batch=6, precision="bf16x3")
+        first = m.forward(prompt, 5, 0)
+        ids = m.decode_device(first, 5, 6)
+        launches = m.launch_count
+        nxt = m.forward(ids[:, -1:], 1, 11)
+        outs.append((first, ids, nxt, m.logits().copy(), launches))
+        m.close()
+    for a, b in zip(outs[0][:4], outs[1][:4]):
+        np.testing.assert_array_equal(a.view(np.uint32) if a.dtype == np.float32 else a, b.view(np.uint32) if b.dtype == np.float32 else b)
+    assert outs[0][4] < outs[1][4]  # fewer kernels per step
+
+
 def test_prefill_in_chunks_equals_one_pass(rt):
     """max_rows forces the prefill to run sequence group by sequence group."""
     sd = S.synth_state_dict(TINY, "q8_0", seed=6, max_seq_len=32, trivial_affine=False, weight_std=0.08)
