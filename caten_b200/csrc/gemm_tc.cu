@@ -8,16 +8,22 @@
 // the epilogue one thread owns one output feature, so bias is a scalar and stores of a fixed
 // activation row are coalesced across the warp.
 //
-// Pipeline per CTA (576 threads), K in chunks of 64:
-//   warps 0-15 load the packed weight chunk (128 rows x 64 k) with vector loads, dequantise in
-//              registers to bf16 and write it to shared memory in the 128-byte-swizzled K-major
-//              layout tcgen05.mma reads; after the K loop they run the epilogue
+// Pipeline per CTA, K in chunks of 64:
+//   producer warps (16, or 8 for fp32 weights) load one weight row each (64 k of packed
+//              weights), dequantise in registers to bf16 and write the result to TENSOR MEMORY
+//              (tcgen05.st): the weight tile is the MMA's A operand read from TMEM, so shared
+//              memory carries only the activations; after the K loop they run the epilogue
 //              (tcgen05.ld -> bias/activation/residual -> global)
-//   warp 16    one lane issues the TMA loads of the activation chunk (bf16 copy of x made by a
-//              small pre-pass; tiled cp.async.bulk.tensor, no multicast)
-//   warp 17    allocates TMEM; one lane issues tcgen05.mma and commits to the stage's mbarrier
-// NSPLIT = 1: plain bf16 operands.  NSPLIT = 3: x = x_hi + x_lo and w = w_hi + w_lo in bf16 and
-// three products (hi*hi + lo*hi + hi*lo) accumulate in the same fp32 TMEM tile.
+//   TMA warp   one lane issues the TMA loads of the activation chunk (bf16 copy of x written by
+//              the kernel that produced x; tiled cp.async.bulk.tensor, no multicast) into the
+//              128-byte-swizzled K-major layout tcgen05.mma reads as B
+//   MMA warp   allocates TMEM; one lane issues tcgen05.mma (A in TMEM, B in shared memory) and
+//              commits to the stage's mbarrier
+// TMEM: columns [0, 256) accumulator, [256, 512) ring of weight stages (32 columns hi [+ 32 lo]).
+// NSPLIT = 1: plain bf16 operands.  NSPLIT = 3: x = x_hi + x_lo and w = w_hi + w_lo in bf16.  With
+// 256 activation rows three products (hi*hi + lo*hi + hi*lo) accumulate in one fp32 TMEM tile;
+// with at most 128 rows B is the 2*rows-row tile [x_hi; x_lo], so two MMAs per k-step give all
+// four products in two column blocks that the epilogue adds.
 //
 // Every mbarrier wait is bounded; when one runs out the kernel records it in the context's
 // status word, stops issuing work, waits (bounded) for its own TMA copies, frees TMEM and returns.
@@ -29,9 +35,6 @@ constexpr int WT_F32_T = 100;  // fp32 operand given as [K, N] row-major (relu_m
 
 constexpr int TC_BM = 128;      // weight rows per CTA (MMA M)
 constexpr int TC_BK = 64;       // k per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int TC_WBYTES = TC_BM * TC_BK * 2;
-constexpr int TC_PRODUCERS = 512;  // 16 warps dequantise; warp 16 issues TMA, warp 17 issues MMA
-constexpr int TC_THREADS = TC_PRODUCERS + 64;
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
 
 struct TcArgs {
@@ -41,7 +44,8 @@ struct TcArgs {
   float *y;
   int *status;
   int act, M, N, K, nkb, bnx, stages;
-  uint32_t idesc, tmem_cols;
+  uint32_t idesc;
+  int concat;  // 1: B operand = [x_hi; x_lo], accumulator columns [bnx, 2 bnx) hold the x_lo products
   // split-K: grid.z CTAs share one output tile, each covering `cps` K-chunks; partial tiles go
   // to `part` and splitk_reduce_kernel adds them in split order and applies the epilogue
   int splits, cps;
@@ -85,6 +89,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   return false;
 }
+// One lane of the (converged) warp; the same lane every time for a full mask.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred)::"memory");
+  return pred != 0;
+}
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -126,191 +140,196 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *r) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// ---- operand split and swizzled stores ----------------------------------------------------------
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 
-// byte offset of 16-byte chunk `c` (0..7) of row `r` inside a [rows x 128 B] tile, Swizzle<3,4,3>
-__device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+// ---- weight rows: global memory -> registers -> bf16 in tensor memory -----------------------------
+//
+// The weight tile is the MMA's A operand and lives in tensor memory, not in shared memory: TMEM
+// lane = weight row (128 per CTA), and a 32-bit TMEM column holds two consecutive k (low half =
+// even k), so a 64-k chunk of bf16 is 32 columns.  A producer thread owns one row: it loads the
+// row's 64 k of packed weights, converts them in registers and writes them with tcgen05.st.  The
+// tensor core then reads A from TMEM and only the activations (B) from shared memory, which keeps
+// the shared-memory port for the TMA writes and the B reads.
+//
+// The producer warps form GROUPS groups of 4 (one warp per 32-lane TMEM quadrant); the groups
+// take the chunks in turn.  DEPTH chunks of a group's future loads are in flight.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t *r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+constexpr int TC_WCOL0 = 256;  // first TMEM column of the weight stages (the accumulator has columns [0, 256))
+
+// 16 consecutive k given as fp32 -> 8 columns of hi (and lo) at column offset `col` of the stage
 template <int NSPLIT>
-__device__ __forceinline__ void store8(uint8_t *whi, uint8_t *wlo, int r, int c, const float *w) {
-  *reinterpret_cast<uint4 *>(whi + swz(r, c)) =
-      make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]), pack_bf16(w[4], w[5]), pack_bf16(w[6], w[7]));
-  if (NSPLIT == 3) {
-    float l[8];
+__device__ __forceinline__ void emit16(uint32_t t_hi, int col, const float *w) {
+  uint32_t h[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) l[e] = bf16_lo(w[e]);
-    *reinterpret_cast<uint4 *>(wlo + swz(r, c)) =
-        make_uint4(pack_bf16(l[0], l[1]), pack_bf16(l[2], l[3]), pack_bf16(l[4], l[5]), pack_bf16(l[6], l[7]));
+  for (int e = 0; e < 8; ++e) h[e] = pack_bf16(w[2 * e], w[2 * e + 1]);
+  tmem_st8(t_hi + col, h);
+  if (NSPLIT == 3) {
+    uint32_t l[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) l[e] = pack_bf16(bf16_lo(w[2 * e]), bf16_lo(w[2 * e + 1]));
+    tmem_st8(t_hi + 32 + col, l);
   }
 }
 
-// One thread's share of a weight chunk (128 rows x 64 k), split into a global-load step and a
-// convert-and-store step so that the loads of later chunks are in flight while the current one
-// is dequantised (DEPTH chunks of look-ahead hide the HBM latency of the packed stream).
-//
-// The 512 producer threads form GROUPS groups that take the chunks in turn; `t` is the thread's
-// index inside its group.  With one group (all formats but Q4_0) warp w owns rows 8w..8w+7 and
-// lane l is (row 8w + (l & 7), part l >> 3): one warp-wide load reads 8 rows x one contiguous run
-// per row (whole 32-byte sectors), and the 8 lanes that store together write 8 different rows,
-// which the 128-byte swizzle spreads over all banks.
-template <int WT> struct WChunk;
+template <int WT> struct WRow;
 
-// Q4_0, converted with packed bf16 arithmetic (two weights per instruction, no fp32 detour).
-// The producers work as two groups of 256 threads that take alternate chunks; a thread owns one
-// whole block (16 code bytes = 32 weights) of one row: warp w of the group holds rows
-// 16w..16w+15, lane l is (row 16w + (l & 15), block l >> 4).
+// Q4_0, converted with packed bf16 arithmetic (two weights per instruction, no fp32 detour):
 //   A  = code - 8                      exact in bf16 (|A| <= 8)
 //   d  = dh + dl, dh = bf16(d)         exact: an fp16 scale has 11 significant bits, dl at most 3
 //   hi = bf16(A * dh)                  one rounding
 //   lo = bf16(A * dl + (A * dh - hi))  the inner difference is exact; hi + lo = A * d to 2^-17
 // NSPLIT = 1 stores bf16(A * d) (correctly rounded: A * dl is exact, then one fused rounding).
-template <> struct WChunk<CATEN_B200_Q4_0> {
-  static constexpr int DEPTH = 4, GROUPS = 2;
-  uint4 q;      // byte j: low nibble = element j, high nibble = element j + 16
-  __half sc;
-  __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int t) {
-    const int l = t & 31;
-    const int64_t row = (int64_t)n0 + 16 * (t >> 5) + (l & 15);
-    const int64_t bi = row * a.nkb + (int64_t)kc * 2 + (l >> 4);
-    if (row < a.N) {
-      q = __ldcs(reinterpret_cast<const uint4 *>(a.qs) + bi);
-      sc = a.d[bi];
+template <> struct WRow<CATEN_B200_Q4_0> {
+  static constexpr int DEPTH = 3, GROUPS = 4;
+  uint4 q[2];     // the chunk's two blocks; byte j: low nibble = element j, high nibble = element j + 16
+  uint32_t sc2;   // their two fp16 scales
+  __device__ __forceinline__ void load(const TcArgs &a, int64_t row, bool ok, int kc) {
+    if (ok) {
+      const int64_t bi = row * a.nkb + (int64_t)kc * 2;
+      q[0] = __ldcs(reinterpret_cast<const uint4 *>(a.qs) + bi);
+      q[1] = __ldcs(reinterpret_cast<const uint4 *>(a.qs) + bi + 1);
+      sc2 = *reinterpret_cast<const uint32_t *>(a.d + bi);  // bi is even: 4-byte aligned
     } else {
-      q = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-      sc = __ushort_as_half((unsigned short)0);
+      q[0] = q[1] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+      sc2 = 0u;
     }
   }
-  // the two code bytes `first`, `first + 1` of `word` (already shifted so that the wanted nibbles
-  // are the low ones) -> bf16x2 (code0 - 8, code1 - 8); 0x4300 | n is the bf16 value 128 + n
+  // code bytes FIRST, FIRST + 1 of `word` (shifted so that the wanted nibbles are the low ones)
+  // -> bf16x2 (code0 - 8, code1 - 8); 0x4300 | n is the bf16 value 128 + n
   template <int FIRST> static __device__ __forceinline__ __nv_bfloat162 codes2(uint32_t word) {
     const uint32_t two = __byte_perm(word, 0u, FIRST == 0 ? 0x4140u : 0x4342u);
     const uint32_t bits = (two & 0x000F000Fu) | 0x43004300u;
     const uint32_t off = 0x43084308u;  // bf16x2 (136, 136)
     return __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&bits), *reinterpret_cast<const __nv_bfloat162 *>(&off));
   }
-  template <int NSPLIT> __device__ __forceinline__ void store(uint8_t *whi, uint8_t *wlo, int t) const {
-    const int l = t & 31, r = 16 * (t >> 5) + (l & 15), blk = l >> 4;
-    const float d = __half2float(sc);
-    const __nv_bfloat16 dh1 = __float2bfloat16_rn(d);
-    const __nv_bfloat16 dl1 = __float2bfloat16_rn(d - __bfloat162float(dh1));
-    const __nv_bfloat162 dh = __halves2bfloat162(dh1, dh1), dl = __halves2bfloat162(dl1, dl1);
-    const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
+  template <int NSPLIT> __device__ __forceinline__ void store(uint32_t t_hi) const {
 #pragma unroll
-    for (int part = 0; part < 4; ++part) {  // elements 8 * part .. 8 * part + 7 of the block
-      uint32_t h[4], lo[4];
+    for (int b = 0; b < 2; ++b) {
+      const float d = __half2float(__ushort_as_half((unsigned short)(b ? sc2 >> 16 : sc2 & 0xFFFFu)));
+      const __nv_bfloat16 dh1 = __float2bfloat16_rn(d);
+      const __nv_bfloat16 dl1 = __float2bfloat16_rn(d - __bfloat162float(dh1));
+      const __nv_bfloat162 dh = __halves2bfloat162(dh1, dh1), dl = __halves2bfloat162(dl1, dl1);
+      const uint32_t wd[4] = {q[b].x, q[b].y, q[b].z, q[b].w};
+      uint32_t h[16], l[16];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t word = wd[(part & 1) * 2 + (j >> 1)] >> (part >= 2 ? 4 : 0);
-        const __nv_bfloat162 A = (j & 1) ? codes2<2>(word) : codes2<0>(word);
+      for (int p = 0; p < 16; ++p) {  // pair p = elements 2p, 2p + 1 of the block
+        const uint32_t word = wd[(p & 7) >> 1] >> (p >= 8 ? 4 : 0);
+        const __nv_bfloat162 A = (p & 1) ? codes2<2>(word) : codes2<0>(word);
         if (NSPLIT == 3) {
           const __nv_bfloat162 hv = __hmul2(A, dh);
           const __nv_bfloat162 lv = __hfma2(A, dl, __hfma2(A, dh, __hneg2(hv)));
-          h[j] = *reinterpret_cast<const uint32_t *>(&hv);
-          lo[j] = *reinterpret_cast<const uint32_t *>(&lv);
+          h[p] = *reinterpret_cast<const uint32_t *>(&hv);
+          l[p] = *reinterpret_cast<const uint32_t *>(&lv);
         } else {
           const __nv_bfloat162 hv = __hfma2(A, dh, __hmul2(A, dl));
-          h[j] = *reinterpret_cast<const uint32_t *>(&hv);
+          h[p] = *reinterpret_cast<const uint32_t *>(&hv);
         }
       }
-      *reinterpret_cast<uint4 *>(whi + swz(r, blk * 4 + part)) = make_uint4(h[0], h[1], h[2], h[3]);
-      if (NSPLIT == 3) *reinterpret_cast<uint4 *>(wlo + swz(r, blk * 4 + part)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      tmem_st16(t_hi + 16 * b, h);
+      if (NSPLIT == 3) tmem_st16(t_hi + 32 + 16 * b, l);
     }
   }
 };
 
-template <> struct WChunk<CATEN_B200_Q8_0> {
-  static constexpr int DEPTH = 3, GROUPS = 1;
-  uint4 q;   // 16 of the block's 32 codes
-  float sc;
-  __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int tid) {
-    const int l = tid & 31, part = l >> 3;
-    const int64_t row = (int64_t)n0 + 8 * (tid >> 5) + (l & 7);
-    const int64_t bi = row * a.nkb + (int64_t)kc * 2 + (part >> 1);
-    if (row < a.N) {
-      q = __ldcs(reinterpret_cast<const uint4 *>(a.qs) + bi * 2 + (part & 1));
-      sc = __half2float(a.d[bi]);
+template <> struct WRow<CATEN_B200_Q8_0> {
+  static constexpr int DEPTH = 2, GROUPS = 4;
+  uint4 q[4];   // 2 blocks x 32 codes
+  uint32_t sc2;
+  __device__ __forceinline__ void load(const TcArgs &a, int64_t row, bool ok, int kc) {
+    if (ok) {
+      const int64_t bi = row * a.nkb + (int64_t)kc * 2;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) q[j] = __ldcs(reinterpret_cast<const uint4 *>(a.qs) + bi * 2 + j);
+      sc2 = *reinterpret_cast<const uint32_t *>(a.d + bi);
     } else {
-      q = make_uint4(0, 0, 0, 0);
-      sc = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) q[j] = make_uint4(0, 0, 0, 0);
+      sc2 = 0u;
     }
   }
-  template <int NSPLIT> __device__ __forceinline__ void store(uint8_t *whi, uint8_t *wlo, int tid) const {
-    const int l = tid & 31, part = l >> 3, r = 8 * (tid >> 5) + (l & 7), blk = part >> 1, h = part & 1;
-    const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
+  template <int NSPLIT> __device__ __forceinline__ void store(uint32_t t_hi) const {
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      float w[8];
+    for (int j = 0; j < 4; ++j) {  // 16 codes each
+      const float d = __half2float(__ushort_as_half((unsigned short)(j >= 2 ? sc2 >> 16 : sc2 & 0xFFFFu)));
+      const uint32_t wd[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+      float w[16];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) w[e] = (float)(int8_t)(wd[2 * c + (e >> 2)] >> (8 * (e & 3))) * sc;
-      store8<NSPLIT>(whi, wlo, r, blk * 4 + h * 2 + c, w);
+      for (int e = 0; e < 16; ++e) w[e] = (float)(int8_t)(wd[e >> 2] >> (8 * (e & 3))) * d;
+      emit16<NSPLIT>(t_hi, 8 * j, w);
     }
   }
 };
 
-template <> struct WChunk<CATEN_B200_F32> {
-  static constexpr int DEPTH = 2, GROUPS = 1;
-  float4 v[4];
-  __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int tid) {
-    const int l = tid & 31;
-    const int64_t row = (int64_t)n0 + 8 * (tid >> 5) + (l & 7);
+template <> struct WRow<CATEN_B200_F16> {
+  static constexpr int DEPTH = 1, GROUPS = 4;
+  uint4 v[8];
+  __device__ __forceinline__ void load(const TcArgs &a, int64_t row, bool ok, int kc) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      v[j] = row < a.N ? __ldcs(reinterpret_cast<const float4 *>((const float *)a.qs + row * a.K + (int64_t)kc * 64) + (l >> 3) + 4 * j)
-                       : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < 8; ++j)
+      v[j] = ok ? __ldcs(reinterpret_cast<const uint4 *>((const __half *)a.qs + row * a.K + (int64_t)kc * 64) + j) : make_uint4(0, 0, 0, 0);
   }
-  template <int NSPLIT> __device__ __forceinline__ void store(uint8_t *whi, uint8_t *wlo, int tid) const {
-    const int l = tid & 31, r = 8 * (tid >> 5) + (l & 7);
+  template <int NSPLIT> __device__ __forceinline__ void store(uint32_t t_hi) const {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int c4 = (l >> 3) + 4 * j;
-      const uint32_t off = swz(r, c4 >> 1) + (c4 & 1) * 8;
-      *reinterpret_cast<uint2 *>(whi + off) = make_uint2(pack_bf16(v[j].x, v[j].y), pack_bf16(v[j].z, v[j].w));
-      if (NSPLIT == 3)
-        *reinterpret_cast<uint2 *>(wlo + off) =
-            make_uint2(pack_bf16(bf16_lo(v[j].x), bf16_lo(v[j].y)), pack_bf16(bf16_lo(v[j].z), bf16_lo(v[j].w)));
+      const __half *h = reinterpret_cast<const __half *>(&v[2 * j]);
+      float w[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) w[e] = __half2float(h[e]);
+      emit16<NSPLIT>(t_hi, 8 * j, w);
     }
   }
 };
 
-template <> struct WChunk<CATEN_B200_F16> {
-  static constexpr int DEPTH = 3, GROUPS = 1;
-  uint4 v[2];
-  __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int tid) {
-    const int l = tid & 31;
-    const int64_t row = (int64_t)n0 + 8 * (tid >> 5) + (l & 7);
+// fp32 rows: 64 floats per thread and chunk; two groups of four warps so that the registers fit
+template <> struct WRow<CATEN_B200_F32> {
+  static constexpr int DEPTH = 1, GROUPS = 2;
+  float4 v[16];
+  __device__ __forceinline__ void load(const TcArgs &a, int64_t row, bool ok, int kc) {
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
-      v[j] = row < a.N ? __ldcs(reinterpret_cast<const uint4 *>((const __half *)a.qs + row * a.K + (int64_t)kc * 64) + (l >> 3) + 4 * j)
-                       : make_uint4(0, 0, 0, 0);
+    for (int j = 0; j < 16; ++j)
+      v[j] = ok ? __ldcs(reinterpret_cast<const float4 *>((const float *)a.qs + row * a.K + (int64_t)kc * 64) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  template <int NSPLIT> __device__ __forceinline__ void store(uint8_t *whi, uint8_t *wlo, int tid) const {
-    const int l = tid & 31, r = 8 * (tid >> 5) + (l & 7);
+  template <int NSPLIT> __device__ __forceinline__ void store(uint32_t t_hi) const {
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const __half *h = reinterpret_cast<const __half *>(&v[j]);
-      float w[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) w[e] = __half2float(h[e]);
-      store8<NSPLIT>(whi, wlo, r, (l >> 3) + 4 * j, w);
-    }
+    for (int j = 0; j < 4; ++j) emit16<NSPLIT>(t_hi, 8 * j, reinterpret_cast<const float *>(&v[4 * j]));
   }
 };
 
-// b[k, n] (relu_matmul): thread = (n, quarter of the 64 k); loads coalesced across n
-template <> struct WChunk<WT_F32_T> {
-  static constexpr int DEPTH = 2, GROUPS = 1;
-  float v[16];
-  __device__ __forceinline__ void load(const TcArgs &a, int n0, int kc, int tid) {
-    const int64_t col = (int64_t)n0 + (tid & 127);
-    const float *b = (const float *)a.qs + ((int64_t)kc * 64 + (tid >> 7) * 16) * a.N + col;
+// b[k, n] (relu_matmul): the "row" is column n of b; loads are coalesced across the warp's lanes
+template <> struct WRow<WT_F32_T> {
+  static constexpr int DEPTH = 1, GROUPS = 2;
+  float v[64];
+  __device__ __forceinline__ void load(const TcArgs &a, int64_t row, bool ok, int kc) {
+    const float *b = (const float *)a.qs + (int64_t)kc * 64 * a.N + row;
 #pragma unroll
-    for (int e = 0; e < 16; ++e) v[e] = col < a.N ? __ldcs(b + (int64_t)e * a.N) : 0.0f;
+    for (int e = 0; e < 64; ++e) v[e] = ok ? __ldcs(b + (int64_t)e * a.N) : 0.0f;
   }
-  template <int NSPLIT> __device__ __forceinline__ void store(uint8_t *whi, uint8_t *wlo, int tid) const {
+  template <int NSPLIT> __device__ __forceinline__ void store(uint32_t t_hi) const {
 #pragma unroll
-    for (int c = 0; c < 2; ++c) store8<NSPLIT>(whi, wlo, tid & 127, (tid >> 7) * 2 + c, v + 8 * c);
+    for (int j = 0; j < 4; ++j) emit16<NSPLIT>(t_hi, 8 * j, v + 16 * j);
   }
 };
+
+template <int WT> constexpr int tc_threads() { return (WRow<WT>::GROUPS * 4 + 2) * 32; }
 
 // Epilogue of one 16-column group held in registers: y[m, o] = act(acc + bias) + res.
 template <int ACT>
@@ -338,14 +357,18 @@ __device__ __forceinline__ void epi_store16(const TcArgs &a, const uint32_t *r, 
 }
 
 template <int WT, int NSPLIT>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(tc_threads<WT>(), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo, const TcArgs a) {
+  constexpr int GROUPS = WRow<WT>::GROUPS, DEPTH = WRow<WT>::DEPTH;
+  constexpr int NPROD = GROUPS * 128;           // producer threads
+  constexpr int TMA_WARP = GROUPS * 4, MMA_WARP = GROUPS * 4 + 1;
+  constexpr uint32_t WCOLS = NSPLIT == 3 ? 64u : 32u;  // TMEM columns of one weight stage (hi [, lo])
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int S = a.stages, bnx = a.bnx;
   const uint32_t xbytes = (uint32_t)bnx * 128u;
-  const uint32_t stage_bytes = (TC_WBYTES + xbytes) * (NSPLIT == 3 ? 2u : 1u);
-  // first 1 KB: barriers + bookkeeping; then the stage buffers (reused as the split-K staging tile)
+  const uint32_t stage_bytes = xbytes * (NSPLIT == 3 ? 2u : 1u);
+  // first 1 KB: barriers + bookkeeping; then the activation stages (reused as the split-K staging tile)
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
   smem += 1024;
   const uint32_t bar0 = smem_u32(bars);
@@ -357,10 +380,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
   // [0] some role gave up a wait; [1] never set (for waits that must not be cut short);
   // [3] thread 0's verdict for the producer warps: accumulator ready
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-  auto stage_whi = [&](int s) { return smem + (size_t)s * stage_bytes; };
-  auto stage_wlo = [&](int s) { return smem + (size_t)s * stage_bytes + TC_WBYTES; };
-  auto stage_xhi = [&](int s) { return smem + (size_t)s * stage_bytes + (NSPLIT == 3 ? 2 : 1) * TC_WBYTES; };
-  auto stage_xlo = [&](int s) { return stage_xhi(s) + xbytes; };
+  auto stage_xhi = [&](int s) { return smem + (size_t)s * stage_bytes; };
+  auto stage_xlo = [&](int s) { return smem + (size_t)s * stage_bytes + xbytes; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * TC_BM, m0 = blockIdx.y * bnx;
@@ -369,7 +390,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(full_w(s), TC_PRODUCERS / 32 / WChunk<WT>::GROUPS);  // one arrival per warp of a producer group
+      mbar_init(full_w(s), 4);  // one arrival per warp of the producer group that filled the stage
       mbar_init(full_x(s), 1);
       mbar_init(empty(s), 1);
     }
@@ -380,8 +401,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
     abort_flag[3] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 17) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(a.tmem_cols) : "memory");
+  if (warp == MMA_WARP) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -393,27 +414,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
   // writes) wait for it.
   pdl_launch_dependents();
 
-  if (warp < 16) {
+  if (warp < GROUPS * 4) {
     // ---------------- weight producers ----------------
-    // The producer warps run independently of one another.  They form GROUPS groups that take the
-    // chunks in turn; for its chunk a warp's lane 0 polls the stage's `empty` mbarrier, the warp
-    // converts and stores its rows, and lane 0 arrives on `full_w` (which counts one arrival per
-    // warp of a group).  A warp that is ahead starts on its next stage while others are still
-    // storing, so conversion, barrier latency and the MMAs overlap.
-    constexpr int DEPTH = WChunk<WT>::DEPTH, GROUPS = WChunk<WT>::GROUPS, GSIZE = TC_PRODUCERS / GROUPS;
-    const int g = tid / GSIZE, t = tid % GSIZE;
-    WChunk<WT> ring[DEPTH];
+    // Warps run independently.  For its chunk a warp's lane 0 polls the stage's `empty` mbarrier,
+    // the warp converts its 32 rows and writes them to the stage's TMEM columns, and lane 0
+    // arrives on `full_w`.  A group that is ahead starts on its next stage while the MMAs of
+    // earlier chunks run, so conversion, barrier latency and the MMAs overlap.
+    const int g = warp >> 2, quad = warp & 3;
+    const int64_t row = (int64_t)n0 + quad * 32 + lane;
+    const bool row_ok = row < a.N;
+    const uint32_t t_quad = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)TC_WCOL0;
+    // An mbarrier wait tells two consecutive phases apart and no more, so a group must not skip
+    // a phase of a stage's `empty` barrier: with S stages at most S groups take chunks (then a
+    // group's previous wait guarantees that its stage is at most one phase behind).
+    const int ga = S < GROUPS ? S : GROUPS;
+    WRow<WT> ring[DEPTH];
 #pragma unroll
     for (int j = 0; j < DEPTH; ++j)
-      if (j * GROUPS + g < num_k) ring[j].load(a, n0, kc0 + j * GROUPS + g, t);
+      if (g < ga && j * ga + g < num_k) ring[j].load(a, row, row_ok, kc0 + j * ga + g);
     int s = g;
     uint32_t ph = 0;
-    while (s >= S) { s -= S; ph ^= 1u; }
-    bool alive = true;
-    for (int kb = 0; kb * GROUPS + g < num_k && alive; kb += DEPTH) {
+    bool alive = g < ga;
+    for (int kb = 0; kb * ga + g < num_k && alive; kb += DEPTH) {
 #pragma unroll
       for (int j = 0; j < DEPTH; ++j) {
-        const int kc = (kb + j) * GROUPS + g;
+        const int kc = (kb + j) * ga + g;
         if (kc < num_k && alive) {
           int got = 0;
           if (lane == 0) {
@@ -424,12 +449,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
           if (!got) {
             alive = false;
           } else {
-            ring[j].template store<NSPLIT>(stage_whi(s), stage_wlo(s), t);
-            fence_proxy_async();  // this thread's stores -> visible to the tensor core's (async proxy) reads
+            tc_fence_after();  // the MMAs that read this stage are complete (their commit fired `empty`)
+            ring[j].template store<NSPLIT>(t_quad + (uint32_t)s * WCOLS);
+            tmem_st_wait();
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(full_w(s));
-            if (kc + DEPTH * GROUPS < num_k) ring[j].load(a, n0, kc0 + kc + DEPTH * GROUPS, t);
-            s += GROUPS;
+            if (kc + DEPTH * ga < num_k) ring[j].load(a, row, row_ok, kc0 + kc + DEPTH * ga);
+            s += ga;
             while (s >= S) { s -= S; ph ^= 1u; }
           }
         }
@@ -442,55 +469,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
       if (!got && !*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 2; }
       abort_flag[3] = got ? 1 : 0;
     }
-    asm volatile("bar.sync 1, 512;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");
     if (abort_flag[3]) {
       tc_fence_after();
-      const int quad = warp & 3;
-      const int64_t o = (int64_t)n0 + quad * 32 + lane;  // output feature of this thread
-      const bool o_ok = o < a.N;
+      const int64_t o = row;  // output feature of this thread
+      const bool o_ok = row_ok;
       const float bias = (a.bias && o_ok) ? a.bias[o] : 0.0f;
-      // four warps per TMEM lane quadrant share the columns in groups of at least 16
-      const int ngroups = bnx >= 64 ? 4 : bnx / 16, per_group = bnx / ngroups, cgroup = warp >> 2;
+      // the warps of a TMEM lane quadrant share the columns in groups of at least 16
+      const int ngroups = bnx / 16 < GROUPS ? bnx / 16 : GROUPS, per_group = bnx / ngroups, cgroup = g;
       const int c_begin = cgroup * per_group, c_end = cgroup < ngroups ? c_begin + per_group : c_begin;
       const uint32_t trow = tmem_base + ((uint32_t)(quad * 32) << 16);
-      if (a.splits == 1) {
-        for (int c = c_begin; c < c_end; c += 16) {
-          uint32_t r[16];
-          tmem_ld16(trow + (uint32_t)c, r);
+      for (int c = c_begin; c < c_end; c += 16) {
+        uint32_t r[16];
+        tmem_ld16(trow + (uint32_t)c, r);
+        if (a.concat) {
+          // columns [bnx, 2 bnx) hold the products with the low part of x
+          uint32_t r2[16];
+          tmem_ld16(trow + (uint32_t)(bnx + c), r2);
           tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
+        } else {
+          tmem_ld_wait();
+        }
+        if (a.splits == 1) {
           if (o_ok && m0 + c < a.M) {
             if (a.act == CATEN_B200_ACT_GELU) epi_store16<CATEN_B200_ACT_GELU>(a, r, bias, o, m0 + c);
             else if (a.act == CATEN_B200_ACT_RELU) epi_store16<CATEN_B200_ACT_RELU>(a, r, bias, o, m0 + c);
             else epi_store16<CATEN_B200_ACT_NONE>(a, r, bias, o, m0 + c);
           }
-        }
-      } else if (a.cluster) {
-        // partial tile -> this CTA's shared memory, [column][row]; the stage buffers are free now
-        // (the accumulator barrier fired: every MMA has read them and every TMA copy has landed)
-        float *stg = reinterpret_cast<float *>(smem) + quad * 32 + lane;
-        for (int c = c_begin; c < c_end; c += 16) {
-          uint32_t r[16];
-          tmem_ld16(trow + (uint32_t)c, r);
-          tmem_ld_wait();
+        } else if (a.cluster) {
+          // partial tile -> this CTA's shared memory, [column][row]; the stage buffers are free now
+          // (the accumulator barrier fired: every MMA has read them and every TMA copy has landed)
+          float *stg = reinterpret_cast<float *>(smem) + quad * 32 + lane;
 #pragma unroll
           for (int i = 0; i < 16; ++i) stg[(c + i) * TC_BM] = __uint_as_float(r[i]);
-        }
-      } else {
-        // partial tile -> part[split][tile][column][row]: a warp stores 128 contiguous bytes
-        const int tiles = gridDim.x * gridDim.y, tile = blockIdx.y * gridDim.x + blockIdx.x;
-        const int rrow = quad * 32 + lane;
-        float *mine = a.part + ((size_t)blockIdx.z * tiles + tile) * bnx * TC_BM + rrow;
-        for (int c = c_begin; c < c_end; c += 16) {
-          uint32_t r[16];
-          tmem_ld16(trow + (uint32_t)c, r);
-          tmem_ld_wait();
+        } else {
+          // partial tile -> part[split][tile][column][row]: a warp stores 128 contiguous bytes
+          const int tiles = gridDim.x * gridDim.y, tile = blockIdx.y * gridDim.x + blockIdx.x;
+          float *mine = a.part + ((size_t)blockIdx.z * tiles + tile) * bnx * TC_BM + quad * 32 + lane;
 #pragma unroll
           for (int i = 0; i < 16; ++i) mine[(c + i) * TC_BM] = __uint_as_float(r[i]);
         }
       }
     }
     tc_fence_before();
-  } else if (warp == 16) {
+  } else if (warp == TMA_WARP) {
     // ---------------- activation TMA producer ----------------
     if (lane == 0) {
       pdl_wait();  // x is written by the preceding kernel
@@ -501,7 +525,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
           if (!*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 3; a.status[2] = kc; }
           break;
         }
-        mbar_expect_tx(full_x(s), xbytes * (NSPLIT == 3 ? 2u : 1u));
+        mbar_expect_tx(full_x(s), stage_bytes);
         tma_load_2d(smem_u32(stage_xhi(s)), &tm_hi, full_x(s), (kc0 + kc) * TC_BK, m0);
         if (NSPLIT == 3) tma_load_2d(smem_u32(stage_xlo(s)), &tm_lo, full_x(s), (kc0 + kc) * TC_BK, m0);
         issued = kc + 1;
@@ -515,33 +539,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
     }
   } else {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      bool ok = true;
-      int s = 0;
-      uint32_t ph = 0;
-      for (int kc = 0; kc < num_k; ++kc) {
-        ok = mbar_wait(full_w(s), ph, abort_flag) && mbar_wait(full_x(s), ph, abort_flag);
-        if (!ok) {
-          if (!*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 4; a.status[2] = kc; }
-          break;
-        }
-        tc_fence_after();
-        const uint64_t dwh = umma_desc(smem_u32(stage_whi(s))), dxh = umma_desc(smem_u32(stage_xhi(s)));
-        const uint64_t dwl = umma_desc(smem_u32(stage_wlo(s))), dxl = umma_desc(smem_u32(stage_xlo(s)));
+    // The whole warp runs the loop (waits, descriptor arithmetic) in uniform control flow, so the
+    // operands of tcgen05.mma can be computed once per warp; one elected lane issues the MMAs and
+    // the commits.
+    bool ok = true;
+    int s = 0;
+    uint32_t ph = 0;
+    const uint32_t t_w0 = tmem_base + (uint32_t)TC_WCOL0;
+    const uint64_t dx0 = umma_desc(smem_u32(smem));  // descriptor of stage 0's x_hi tile
+    const uint32_t stage16 = stage_bytes >> 4, xlo16 = xbytes >> 4;  // in descriptor address units
+    for (int kc = 0; kc < num_k; ++kc) {
+      ok = mbar_wait(full_w(s), ph, abort_flag) && mbar_wait(full_x(s), ph, abort_flag);
+      if (!ok) {
+        if (lane == 0 && !*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 4; a.status[2] = kc; }
+        break;
+      }
+      tc_fence_after();
+      const uint32_t a_hi = t_w0 + (uint32_t)s * WCOLS, a_lo = a_hi + 32u;
+      const uint64_t dxh = dx0 + (uint64_t)((uint32_t)s * stage16), dxl = dxh + (uint64_t)xlo16;
+      if (elect_one()) {
 #pragma unroll
         for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
           const uint64_t adv = (uint64_t)(k4 * 2);  // 16 bf16 = 32 bytes = 2 descriptor units
-          umma_bf16(tmem_base, dwh + adv, dxh + adv, a.idesc, (kc > 0 || k4 > 0) ? 1u : 0u);
-          if (NSPLIT == 3) {
-            umma_bf16(tmem_base, dwl + adv, dxh + adv, a.idesc, 1u);
-            umma_bf16(tmem_base, dwh + adv, dxl + adv, a.idesc, 1u);
+          const uint32_t first = (kc > 0 || k4 > 0) ? 1u : 0u;
+          if (NSPLIT == 3 && a.concat) {
+            // B = [x_hi; x_lo] (2 bnx rows, adjacent in the stage): one MMA per weight part
+            umma_bf16_ts(tmem_base, a_hi + 8u * k4, dxh + adv, a.idesc, first);
+            umma_bf16_ts(tmem_base, a_lo + 8u * k4, dxh + adv, a.idesc, 1u);
+          } else {
+            umma_bf16_ts(tmem_base, a_hi + 8u * k4, dxh + adv, a.idesc, first);
+            if (NSPLIT == 3) {
+              umma_bf16_ts(tmem_base, a_lo + 8u * k4, dxh + adv, a.idesc, 1u);
+              umma_bf16_ts(tmem_base, a_hi + 8u * k4, dxl + adv, a.idesc, 1u);
+            }
           }
         }
         umma_commit(empty(s));  // frees the stage when these MMAs have read it
-        if (++s == S) { s = 0; ph ^= 1u; }
       }
-      if (ok) umma_commit(accum_bar);
+      __syncwarp();
+      if (++s == S) { s = 0; ph ^= 1u; }
     }
+    if (ok && elect_one()) umma_commit(accum_bar);
     __syncwarp();
   }
   __syncthreads();
@@ -549,11 +587,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
     // Split-K reduction inside the cluster.  Both cluster barriers are executed by every thread
     // of every CTA unconditionally (also after a timed-out wait), so no CTA can be left waiting.
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    if (tid < TC_PRODUCERS && abort_flag[3]) {
+    if (tid < NPROD && abort_flag[3]) {
       const int rank = blockIdx.z, nsp = a.splits;
       const uint32_t stg0 = smem_u32(smem);
       const int mine = (bnx - rank + nsp - 1) / nsp;  // columns rank, rank + nsp, ... of the tile
-      for (int item = tid; item < mine * 32; item += TC_PRODUCERS) {
+      for (int item = tid; item < mine * 32; item += NPROD) {
         const int col = rank + (item >> 5) * nsp, r4 = (item & 31) * 4;
         const int64_t m = (int64_t)m0 + col;
         if (m >= a.M) continue;
@@ -589,9 +627,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
     // peers may still be reading this CTA's shared memory
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
-  if (warp == 17) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
 
@@ -678,7 +716,7 @@ static int launch_tc_t(caten_b200_ctx *ctx, const CUtensorMap &mh, const CUtenso
   CB_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<WT, NSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(TC_THREADS);
+  cfg.blockDim = dim3(tc_threads<WT>());
   cfg.dynamicSmemBytes = smem;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute at[2];
@@ -702,16 +740,73 @@ static int launch_tc_t(caten_b200_ctx *ctx, const CUtensorMap &mh, const CUtenso
   return 0;
 }
 
+static int launch_tc(caten_b200_ctx *ctx, int wt, int nsplit, const CUtensorMap &mh, const CUtensorMap &ml, const TcArgs &a, dim3 grid,
+                     size_t smem) {
+#define TC_CASE(WT) \
+  case WT: return nsplit == 3 ? launch_tc_t<WT, 3>(ctx, mh, ml, a, grid, smem) : launch_tc_t<WT, 1>(ctx, mh, ml, a, grid, smem)
+  switch (wt) {
+    TC_CASE(CATEN_B200_F32);
+    TC_CASE(CATEN_B200_F16);
+    TC_CASE(CATEN_B200_Q4_0);
+    TC_CASE(CATEN_B200_Q8_0);
+    TC_CASE(WT_F32_T);
+    default: return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_tc: weight type %d", wt);
+  }
+#undef TC_CASE
+}
+
+// Tile shape, pipeline depth and split-K factor of one launch.
+struct TcPlan {
+  int bnx, stages, splits, cps, concat;
+  uint32_t idesc;
+  int64_t gx, gy, tiles;
+  size_t stage_bytes;
+};
+
+static int tc_plan(caten_b200_ctx *ctx, const char *who, int64_t M, int64_t N, int64_t K, int nsplit, int split_cap, TcPlan *p) {
+  if (!ctx->encode_tiled) return fail(ctx, CATEN_B200_ECUDA, "%s: cuTensorMapEncodeTiled is not available", who);
+  if (K % TC_BK) return fail(ctx, CATEN_B200_EUNSUPPORTED, "%s: inner dimension %lld is not a multiple of 64", who, (long long)K);
+  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "%s: dimension too large", who);
+  if (nsplit != 1 && nsplit != 3) return fail(ctx, CATEN_B200_EINVAL, "%s: nsplit must be 1 or 3", who);
+  int bnx = 16;
+  while (bnx < 256 && bnx < M) bnx *= 2;
+  p->bnx = bnx;
+  p->concat = (nsplit == 3 && bnx <= 128) ? 1 : 0;
+  const int mma_n = p->concat ? 2 * bnx : bnx;
+  p->idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(mma_n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+  p->stage_bytes = (size_t)bnx * 128 * (nsplit == 3 ? 2 : 1);
+  p->gy = (M + bnx - 1) / bnx;
+  if (p->gy > 65535) return fail(ctx, CATEN_B200_EUNSUPPORTED, "%s: too many rows for one launch (%lld)", who, (long long)M);
+  p->gx = (N + TC_BM - 1) / TC_BM;
+  p->tiles = p->gx * p->gy;
+  // split-K when the output tiles alone cannot occupy the GPU (decode: few activation rows)
+  const int num_k = (int)(K / TC_BK);
+  int splits = 1;
+  if (p->tiles < ctx->sm_count) {
+    const int by_work = num_k / 4 > 0 ? num_k / 4 : 1;        // at least 4 chunks per CTA
+    const int by_fill = (int)(ctx->sm_count / p->tiles);      // one wave: every CTA resident at once
+    splits = by_work < by_fill ? by_work : by_fill;
+    if (splits > split_cap) splits = split_cap;
+  }
+  p->cps = (num_k + splits - 1) / splits;
+  p->splits = (num_k + p->cps - 1) / p->cps;
+  // ring depth: weight stages in TMEM (256 columns), activation stages in shared memory
+  int stages = nsplit == 3 ? 4 : 8;
+  if ((size_t)stages * p->stage_bytes > 200 * 1024) stages = (int)((200 * 1024) / p->stage_bytes);
+  if (stages > p->cps) stages = p->cps;
+  if (stages < 1) stages = 1;
+  p->stages = stages;
+  return 0;
+}
+
 static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, int64_t nkb, const float *x,
                   const float *bias, const float *res, int act, float *y, int64_t M, int64_t N, int64_t K, int nsplit,
                   const __nv_bfloat16 *xhi_pre = nullptr, const __nv_bfloat16 *xlo_pre = nullptr, BfOut ybf = BfOut(),
                   PartIn *defer = nullptr) {
   if (defer) *defer = PartIn();
   if (M <= 0 || N <= 0) return 0;
-  if (!ctx->encode_tiled) return fail(ctx, CATEN_B200_ECUDA, "gemm_tc: cuTensorMapEncodeTiled is not available");
-  if (K % TC_BK) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_tc: inner dimension %lld is not a multiple of 64", (long long)K);
-  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_tc: dimension too large");
-  if (nsplit != 1 && nsplit != 3) return fail(ctx, CATEN_B200_EINVAL, "gemm_tc: nsplit must be 1 or 3");
+  TcPlan p;
+  if (int rc = tc_plan(ctx, "gemm_tc", M, N, K, nsplit, ctx->splitk_cluster ? 8 : 32, &p)) return rc;  // 8 = portable cluster size
   uint8_t *xhi, *xlo;
   if (xhi_pre) {
     // the producer of x already wrote the split bf16 operand
@@ -730,78 +825,37 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
     launch_k(ctx, split_bf16_kernel, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, (const float4 *)x, (uint2 *)xhi, (uint2 *)xlo, n4);
     CB_LAUNCH_CHECK(ctx, "split_bf16_kernel");
   }
-
-  const int max_bnx = 256;
-  int bnx = 16;
-  while (bnx < max_bnx && bnx < M) bnx *= 2;
   CUtensorMap mh, ml;
-  if (int rc = make_x_map(ctx, &mh, xhi, M, K, bnx)) return rc;
-  if (int rc = make_x_map(ctx, &ml, nsplit == 3 ? xlo : xhi, M, K, bnx)) return rc;
+  if (int rc = make_x_map(ctx, &mh, xhi, M, K, p.bnx)) return rc;
+  if (int rc = make_x_map(ctx, &ml, nsplit == 3 ? xlo : xhi, M, K, p.bnx)) return rc;
 
   TcArgs a;
   a.qs = qs; a.d = d; a.bias = bias; a.res = res; a.y = y; a.status = ctx->d_status; a.act = act;
   a.yhi = ybf.hi; a.ylo = ybf.lo;
-  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.nkb = (int)nkb; a.bnx = bnx;
-  const size_t stage = (size_t)(TC_WBYTES + bnx * 128) * (nsplit == 3 ? 2 : 1);
-  int stages = (int)((200 * 1024) / stage);
-  if (stages > 8) stages = 8;
-  if (stages > K / TC_BK) stages = (int)(K / TC_BK);
-  if (stages < 1) stages = 1;
-  a.stages = stages;
-  a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bnx >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-  a.tmem_cols = bnx < 32 ? 32u : (uint32_t)bnx;
-  const int64_t gy = (M + bnx - 1) / bnx;
-  if (gy > 65535) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_tc: too many rows for one launch (%lld)", (long long)M);
-  const int64_t gx = (N + TC_BM - 1) / TC_BM, tiles = gx * gy;
-  // split-K when the output tiles alone cannot occupy the GPU (decode: few activation rows)
-  const int num_k = (int)(K / TC_BK);
-  int splits = 1;
-  if (tiles < ctx->sm_count) {
-    const int by_work = num_k / 4 > 0 ? num_k / 4 : 1;                       // at least 4 chunks per CTA
-    const int by_fill = (int)(ctx->sm_count / tiles);                         // one wave: every CTA resident at once
-    splits = by_work < by_fill ? by_work : by_fill;
-    const int cap = ctx->splitk_cluster ? 8 : 32;                             // 8 = portable cluster size
-    if (splits > cap) splits = cap;
-  }
-  int cps = (num_k + splits - 1) / splits;
-  splits = (num_k + cps - 1) / cps;
-  a.splits = splits; a.cps = cps; a.part = nullptr;
-  a.cluster = (splits > 1 && ctx->splitk_cluster) ? 1 : 0;
-  if (splits > 1 && !a.cluster) {
-    if (int rc = scratch_reserve(ctx, &ctx->wtmp, (size_t)splits * tiles * bnx * TC_BM * sizeof(float))) return rc;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.nkb = (int)nkb; a.bnx = p.bnx;
+  a.stages = p.stages; a.idesc = p.idesc; a.concat = p.concat;
+  a.splits = p.splits; a.cps = p.cps; a.part = nullptr;
+  a.cluster = (p.splits > 1 && ctx->splitk_cluster) ? 1 : 0;
+  if (p.splits > 1 && !a.cluster) {
+    if (int rc = scratch_reserve(ctx, &ctx->wtmp, (size_t)p.splits * p.tiles * p.bnx * TC_BM * sizeof(float))) return rc;
     a.part = (float *)ctx->wtmp.ptr;
   }
-  if (a.stages > cps) a.stages = cps;
-  // 1 KB alignment slack + 1 KB bookkeeping + the stage ring (which the split-K staging tile reuses)
-  size_t ring = stage * (size_t)a.stages;
-  if (a.cluster && ring < (size_t)bnx * TC_BM * sizeof(float)) ring = (size_t)bnx * TC_BM * sizeof(float);
+  // 1 KB alignment slack + 1 KB bookkeeping + the activation ring (which the split-K staging tile reuses)
+  size_t ring = p.stage_bytes * (size_t)p.stages;
+  if (a.cluster && ring < (size_t)p.bnx * TC_BM * sizeof(float)) ring = (size_t)p.bnx * TC_BM * sizeof(float);
   const size_t smem = 2048 + ring;
-  const dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)splits);
-
-  int rc = CATEN_B200_EUNSUPPORTED;
-#define TC_CASE(WT)                                                              \
-  case WT:                                                                       \
-    rc = nsplit == 3 ? launch_tc_t<WT, 3>(ctx, mh, ml, a, grid, smem) : launch_tc_t<WT, 1>(ctx, mh, ml, a, grid, smem); \
-    break
-  switch (wt) {
-    TC_CASE(CATEN_B200_F32);
-    TC_CASE(CATEN_B200_F16);
-    TC_CASE(CATEN_B200_Q4_0);
-    TC_CASE(CATEN_B200_Q8_0);
-    TC_CASE(WT_F32_T);
-    default: return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_tc: weight type %d", wt);
-  }
-#undef TC_CASE
-  if (rc || splits == 1 || a.cluster) return rc;
+  const dim3 grid((unsigned)p.gx, (unsigned)p.gy, (unsigned)p.splits);
+  const int rc = launch_tc(ctx, wt, nsplit, mh, ml, a, grid, smem);
+  if (rc || p.splits == 1 || a.cluster) return rc;
   if (defer && act == CATEN_B200_ACT_NONE && !a.yhi && N % 4 == 0) {
     // the consumer of this linear sums the partial tiles itself (and adds bias / residual)
-    defer->part = a.part; defer->bias = bias; defer->splits = splits; defer->tiles_x = (int)gx; defer->bnx = bnx;
-    defer->zstride = (long long)tiles * bnx * TC_BM;
+    defer->part = a.part; defer->bias = bias; defer->splits = p.splits; defer->tiles_x = (int)p.gx; defer->bnx = p.bnx;
+    defer->zstride = (long long)p.tiles * p.bnx * TC_BM;
     return 0;
   }
-  const int64_t total = tiles * bnx * (TC_BM / 4);
-  launch_k(ctx, splitk_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, a.part, splits, (int)gx, (int)tiles, bnx, bias, res, y,
-                                                                              a.yhi, a.ylo, act, (int)M, (int)N);
+  const int64_t total = p.tiles * p.bnx * (TC_BM / 4);
+  launch_k(ctx, splitk_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, a.part, p.splits, (int)p.gx, (int)p.tiles, p.bnx, bias,
+                                                                              res, y, a.yhi, a.ylo, act, (int)M, (int)N);
   CB_LAUNCH_CHECK(ctx, "splitk_reduce_kernel");
   return 0;
 }
@@ -834,36 +888,15 @@ int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, cons
                            const float *res, int act, float *y, int64_t M, int nsplit) {
   const int64_t N = w->rows, K = w->cols;
   if (M <= 0 || N <= 0) return 0;
-  if (!ctx->encode_tiled) return fail(ctx, CATEN_B200_ECUDA, "linear_noalloc: cuTensorMapEncodeTiled is not available");
-  if (K % TC_BK) return fail(ctx, CATEN_B200_EUNSUPPORTED, "linear_noalloc: inner dimension %lld is not a multiple of 64", (long long)K);
-  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "linear_noalloc: dimension too large");
-  if (nsplit != 1 && nsplit != 3) return fail(ctx, CATEN_B200_EINVAL, "linear_noalloc: nsplit must be 1 or 3");
+  TcPlan p;
+  if (int rc = tc_plan(ctx, "linear_noalloc", M, N, K, nsplit, 32, &p)) return rc;
   uint8_t *base = nullptr;
   if (int rc = fixed_scratch_ptr(ctx, &base)) return rc;
-
-  int bnx = 16;
-  while (bnx < 256 && bnx < M) bnx *= 2;
-  const size_t stage = (size_t)(TC_WBYTES + bnx * 128) * (nsplit == 3 ? 2 : 1);
-  int stages = (int)((200 * 1024) / stage);
-  if (stages > 8) stages = 8;
-  if (stages > K / TC_BK) stages = (int)(K / TC_BK);
-  if (stages < 1) stages = 1;
-  const int64_t gy = (M + bnx - 1) / bnx, gx = (N + TC_BM - 1) / TC_BM, tiles = gx * gy;
-  if (gy > 65535) return fail(ctx, CATEN_B200_EUNSUPPORTED, "linear_noalloc: too many rows for one launch (%lld)", (long long)M);
-  const int num_k = (int)(K / TC_BK);
-  int splits = 1;
-  if (tiles < ctx->sm_count) {
-    const int by_work = num_k / 4 > 0 ? num_k / 4 : 1, by_fill = (int)(ctx->sm_count / tiles);
-    splits = by_work < by_fill ? by_work : by_fill;
-    if (splits > 32) splits = 32;
-  }
-  const int cps = (num_k + splits - 1) / splits;
-  splits = (num_k + cps - 1) / cps;
 
   // layout of the fixed buffer: [x_hi | x_lo (split-bf16 only) | split-K partial tiles]
   const size_t xb_al = ((size_t)M * K * 2 + 1023) & ~(size_t)1023;
   const size_t x_total = xb_al * (nsplit == 3 ? 2 : 1);
-  const size_t part_bytes = splits > 1 ? (size_t)splits * tiles * bnx * TC_BM * sizeof(float) : 0;
+  const size_t part_bytes = p.splits > 1 ? (size_t)p.splits * p.tiles * p.bnx * TC_BM * sizeof(float) : 0;
   if (x_total + part_bytes > FIXED_SCRATCH_BYTES)
     return fail(ctx, CATEN_B200_EUNSUPPORTED,
                 "linear_noalloc: M=%lld x %lldx%lld needs %zu bytes of scratch, the built-in buffer holds %zu; use caten_b200_linear",
@@ -875,37 +908,23 @@ int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, cons
   launch_k(ctx, split_bf16_kernel, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, (const float4 *)x, (uint2 *)xhi, (uint2 *)xlo, n4);
   CB_LAUNCH_CHECK(ctx, "split_bf16_kernel");
   CUtensorMap mh, ml;
-  if (int rc = make_x_map(ctx, &mh, xhi, M, K, bnx)) return rc;
-  if (int rc = make_x_map(ctx, &ml, nsplit == 3 ? xlo : xhi, M, K, bnx)) return rc;
+  if (int rc = make_x_map(ctx, &mh, xhi, M, K, p.bnx)) return rc;
+  if (int rc = make_x_map(ctx, &ml, nsplit == 3 ? xlo : xhi, M, K, p.bnx)) return rc;
 
   TcArgs a;
   a.qs = w->qs; a.d = w->d; a.bias = bias; a.res = res; a.y = y; a.status = ctx->d_status; a.act = act;
   a.yhi = nullptr; a.ylo = nullptr;
-  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.nkb = (int)w->nkb; a.bnx = bnx;
-  a.stages = stages > cps ? cps : stages;
-  a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bnx >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-  a.tmem_cols = bnx < 32 ? 32u : (uint32_t)bnx;
-  a.splits = splits; a.cps = cps; a.cluster = 0;  // partial tiles go through the fixed buffer
-  a.part = splits > 1 ? (float *)(base + x_total) : nullptr;
-  const size_t smem = 2048 + stage * (size_t)stages;
-  const dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)splits);
-  int rc = CATEN_B200_EUNSUPPORTED;
-#define TC_CASE(WT)                                                              \
-  case WT:                                                                       \
-    rc = nsplit == 3 ? launch_tc_t<WT, 3>(ctx, mh, ml, a, grid, smem) : launch_tc_t<WT, 1>(ctx, mh, ml, a, grid, smem); \
-    break
-  switch (w->type) {
-    TC_CASE(CATEN_B200_F32);
-    TC_CASE(CATEN_B200_F16);
-    TC_CASE(CATEN_B200_Q4_0);
-    TC_CASE(CATEN_B200_Q8_0);
-    default: return fail(ctx, CATEN_B200_EUNSUPPORTED, "linear_noalloc: weight type %d", w->type);
-  }
-#undef TC_CASE
-  if (rc || splits == 1) return rc;
-  const int64_t total = tiles * bnx * (TC_BM / 4);
-  launch_k(ctx, splitk_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, a.part, splits, (int)gx, (int)tiles, bnx, bias, res, y,
-                                                                              a.yhi, a.ylo, act, (int)M, (int)N);
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.nkb = (int)w->nkb; a.bnx = p.bnx;
+  a.stages = p.stages; a.idesc = p.idesc; a.concat = p.concat;
+  a.splits = p.splits; a.cps = p.cps; a.cluster = 0;  // partial tiles go through the fixed buffer
+  a.part = p.splits > 1 ? (float *)(base + x_total) : nullptr;
+  const size_t smem = 2048 + p.stage_bytes * (size_t)p.stages;
+  const dim3 grid((unsigned)p.gx, (unsigned)p.gy, (unsigned)p.splits);
+  const int rc = launch_tc(ctx, w->type, nsplit, mh, ml, a, grid, smem);
+  if (rc || p.splits == 1) return rc;
+  const int64_t total = p.tiles * p.bnx * (TC_BM / 4);
+  launch_k(ctx, splitk_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, a.part, p.splits, (int)p.gx, (int)p.tiles, p.bnx, bias,
+                                                                              res, y, a.yhi, a.ylo, act, (int)M, (int)N);
   CB_LAUNCH_CHECK(ctx, "splitk_reduce_kernel");
   return 0;
 }
