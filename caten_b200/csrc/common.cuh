@@ -40,7 +40,15 @@ __device__ __forceinline__ float4 partin_load4(const PartIn &p, long long m, int
   const long long tile = (m / p.bnx) * p.tiles_x + (o >> 7);
   const float *src = p.part + (tile * p.bnx + (m % p.bnx)) * 128 + (o & 127);
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int z = 0; z < p.splits; ++z) {
+  int z = 0;
+  for (; z + 4 <= p.splits; z += 4) {  // four loads in flight, added in split order
+    float4 a[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) a[u] = __ldcs(reinterpret_cast<const float4 *>(src + (long long)(z + u) * p.zstride));
+#pragma unroll
+    for (int u = 0; u < 4; ++u) { v.x += a[u].x; v.y += a[u].y; v.z += a[u].z; v.w += a[u].w; }
+  }
+  for (; z < p.splits; ++z) {
     const float4 a = __ldcs(reinterpret_cast<const float4 *>(src + (long long)z * p.zstride));
     v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
   }
