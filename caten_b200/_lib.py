@@ -45,8 +45,24 @@ class GPT2Desc(C.Structure):
     ]
 
 
+EXPR_MAX_DIMS, EXPR_MAX_OPERANDS, EXPR_MAX_CODE, EXPR_MAX_CONSTS = 6, 8, 96, 16
+
+
+class ExprDesc(C.Structure):
+    """Mirror of ``caten_b200_expr``."""
+    _fields_ = [
+        ("ndim", C.c_int32), ("shape", _i64 * EXPR_MAX_DIMS), ("n_reduce", C.c_int32), ("reduce_op", C.c_int32),
+        ("accumulate", C.c_int32), ("n_operands", C.c_int32),
+        ("operand", _vp * EXPR_MAX_OPERANDS), ("operand_dtype", C.c_int32 * EXPR_MAX_OPERANDS),
+        ("operand_offset", _i64 * EXPR_MAX_OPERANDS), ("operand_stride", (_i64 * EXPR_MAX_DIMS) * EXPR_MAX_OPERANDS),
+        ("out", _vp), ("out_dtype", C.c_int32), ("out_offset", _i64), ("out_stride", _i64 * EXPR_MAX_DIMS),
+        ("n_code", C.c_int32), ("code", C.c_uint32 * EXPR_MAX_CODE), ("consts", C.c_uint32 * EXPR_MAX_CONSTS),
+    ]
+
+
 # name -> (restype, argtypes); every name here must be declared in include/caten_b200.h
 SIGNATURES = {
+    "caten_b200_eval_expr": (C.c_int, [_vp, C.POINTER(ExprDesc)]),
     "caten_b200_init": (C.c_int, [C.c_int, _PFP]),
     "caten_b200_destroy": (C.c_int, [_vp]),
     "caten_b200_last_error": (C.c_char_p, [_vp]),

@@ -390,6 +390,12 @@ int caten_b200_argmax(caten_b200_ctx *ctx, const float *d_x, int64_t rows, int64
   return launch_argmax(ctx, d_x, rows, V, d_out);
 }
 
+int caten_b200_eval_expr(caten_b200_ctx *ctx, const caten_b200_expr *e) {
+  NEED_CTX(ctx);
+  if (!e) return fail(ctx, CATEN_B200_EINVAL, "eval_expr: NULL argument");
+  return launch_expr(ctx, e);
+}
+
 }  // extern "C"
 
 // ------------------------------------------------------------------------------------------------

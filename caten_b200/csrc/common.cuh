@@ -144,6 +144,7 @@ int launch_begin_steps(caten_b200_ctx *ctx, const float *ids_f32, const int64_t 
                        int64_t n, int64_t B);
 int launch_finish_step(caten_b200_ctx *ctx, const int64_t *out_ids, int64_t *ids_io, int64_t *hist, int *d_pos, int64_t B);
 int launch_argmax(caten_b200_ctx *ctx, const float *x, int64_t rows, int64_t V, int64_t *out);
+int launch_expr(caten_b200_ctx *ctx, const caten_b200_expr *e);
 int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc, float *out, int64_t B,
                      int64_t s, int64_t n, int64_t H, int64_t T, const int *d_n = nullptr, cb::BfOut bf = cb::BfOut(),
                      const cb::PartIn *pending_qkv = nullptr);

@@ -234,6 +234,62 @@ int caten_b200_gpt2_kv(caten_b200_gpt2 *m, int layer, float **d_k, float **d_v);
 /* Number of kernel launches issued by this model's steps since creation. */
 int64_t caten_b200_gpt2_launch_count(caten_b200_gpt2 *m);
 
+/* ---- generic schedule item ------------------------------------------------------------------------
+ * One fused element-wise (optionally reducing) kernel of the scheduler, i.e. what
+ * source/byoc/clang.lisp:163-205 renders as one C function from a Schedule-Item's :EXPR nodes
+ * (source/codegen/renderer.lisp:331-410): a loop nest over an iteration space, strided views of the
+ * operands (source/aasm/attrs.lisp:265-283), an expression over the aIR ops of
+ * source/aasm/attrs.lisp:42-216, and one store.  Instead of rendering and compiling C at run time
+ * the expression is handed over as a short postfix program that one CUDA kernel interprets per
+ * element, so any such item runs under BACKEND=B200 without a compiler on the host.
+ *
+ * Value classes: F32 (fp32), I32 (int32; int64 buffers are read/written through int32), BOOL (0/1).
+ * A program word is  opcode | arg << 8 | class << 16.  The classes of the operands must already
+ * agree (insert CAST as the reference's graph does).  Float arithmetic is fp32; SIN / EXP2 / LOG2 /
+ * SQRT go through double and are rounded once, which is what the C the reference renders computes
+ * (double libm functions applied to a float). */
+enum {
+  CATEN_B200_OP_LOAD = 1,   /* arg = operand index: push the operand's element at the current index */
+  CATEN_B200_OP_CONST = 2,  /* arg = index into consts[] (bit pattern of a float or an int32) */
+  CATEN_B200_OP_INDEX = 3,  /* arg = axis: push the loop index of that axis as I32 (:INDEX-COMPONENTS of one axis) */
+  CATEN_B200_OP_NEG = 10, CATEN_B200_OP_RECIP, CATEN_B200_OP_SIN, CATEN_B200_OP_EXP2, CATEN_B200_OP_LOG2,
+  CATEN_B200_OP_SQRT, CATEN_B200_OP_NOT,
+  CATEN_B200_OP_CAST,       /* arg = class of the operand; class field = class of the result */
+  CATEN_B200_OP_ADD = 30, CATEN_B200_OP_MUL, CATEN_B200_OP_MOD, CATEN_B200_OP_IDIV, CATEN_B200_OP_AND,
+  CATEN_B200_OP_OR, CATEN_B200_OP_XOR, CATEN_B200_OP_MAX,
+  CATEN_B200_OP_NE, CATEN_B200_OP_LT,   /* (a b -- bool); class field = class of a and b */
+  CATEN_B200_OP_WHERE = 50  /* (cond a b -- cond ? a : b) */
+};
+enum { CATEN_B200_CLS_F32 = 0, CATEN_B200_CLS_I32 = 1, CATEN_B200_CLS_BOOL = 2 };
+/* element types of operand and output buffers */
+enum { CATEN_B200_DT_F32 = 0, CATEN_B200_DT_I32 = 1, CATEN_B200_DT_I64 = 2, CATEN_B200_DT_U8 = 3 };
+enum { CATEN_B200_RED_NONE = 0, CATEN_B200_RED_SUM = 1, CATEN_B200_RED_MAX = 2 };
+#define CATEN_B200_EXPR_MAX_DIMS 6
+#define CATEN_B200_EXPR_MAX_OPERANDS 8
+#define CATEN_B200_EXPR_MAX_CODE 96
+#define CATEN_B200_EXPR_MAX_CONSTS 16
+typedef struct {
+  int32_t ndim;                                   /* loops, outermost first */
+  int64_t shape[CATEN_B200_EXPR_MAX_DIMS];
+  int32_t n_reduce;                               /* the innermost n_reduce loops are reduced into the output */
+  int32_t reduce_op;                              /* CATEN_B200_RED_*; reduction runs in loop order (as the rendered C does) */
+  int32_t accumulate;                             /* 1: the output's old value is the first term (the :reduction store) */
+  int32_t n_operands;
+  const void *operand[CATEN_B200_EXPR_MAX_OPERANDS];           /* device pointers */
+  int32_t operand_dtype[CATEN_B200_EXPR_MAX_OPERANDS];
+  int64_t operand_offset[CATEN_B200_EXPR_MAX_OPERANDS];        /* in elements */
+  int64_t operand_stride[CATEN_B200_EXPR_MAX_OPERANDS][CATEN_B200_EXPR_MAX_DIMS]; /* in elements; 0 = broadcast */
+  void *out;
+  int32_t out_dtype;
+  int64_t out_offset;
+  int64_t out_stride[CATEN_B200_EXPR_MAX_DIMS];   /* strides of the reduced loops are ignored */
+  int32_t n_code;
+  uint32_t code[CATEN_B200_EXPR_MAX_CODE];
+  uint32_t consts[CATEN_B200_EXPR_MAX_CONSTS];
+} caten_b200_expr;
+/* Runs the item.  The program must leave exactly one value; its class is converted to out_dtype. */
+int caten_b200_eval_expr(caten_b200_ctx *ctx, const caten_b200_expr *e);
+
 /* ---- per-kernel timing ----------------------------------------------------------------------------
  * Counterpart of PROFILE=1 (source/runtime/profile.lisp:15-39, source/codegen/runner.lisp:28-31),
  * which wall-clocks every node of the VM: here launches of the selected kernel classes are
