@@ -4,6 +4,7 @@
     python -m caten_b200.microbench gemv --model gpt2-xl --wtype q4_0
     python -m caten_b200.microbench gemm --rows 256 --n 1600 --k 6400 --wtype q4_0 --precision bf16x3
     python -m caten_b200.microbench relu_matmul --precision bf16x3
+    python -m caten_b200.microbench expr --elements 67108864
 
 Each prints one JSON line.  Operands are rotated over several copies larger in total than the
 126 MB L2, so every launch streams from HBM.  Events bracket each launch (the profile API of the
@@ -117,9 +118,47 @@ def relu_matmul(rt, a):
             "frac_of_measured_bf16": flops / per / 1e12 / tf}
 
 
+def expr(rt, a):
+    """Generic schedule items (`caten_b200_eval_expr`): algorithmic bytes = operand + output elements x 4."""
+    import torch
+    from . import expr as E
+    n = a.elements
+    rng = np.random.Generator(np.random.PCG64(0))
+    host = rng.standard_normal(n, dtype=np.float32)
+    x, y, z = rt.transfer_from_array(host), rt.transfer_from_array(host[::-1].copy()), rt.open_buffer((n,))
+    rows = n // 1024
+    m2 = rt.open_buffer((rows,))
+    x2 = E.View(x, strides=(1024, 1))
+    cases = {
+        "a*x+b (1 load, 1 store)": (E.load(E.View.of(x)) * 1.5 + 0.25, E.View.of(z), (n,), 0, None, 8.0 * n),
+        "x*y+x (2 loads, 1 store)": (E.load(E.View.of(x)) * E.load(E.View.of(y)) + E.load(E.View.of(x)), E.View.of(z), (n,), 0, None, 12.0 * n),
+        "relu(x)*y (where)": (E.where(E.load(E.View.of(x)) < 0.0, E.const(0.0), E.load(E.View.of(x))) * E.load(E.View.of(y)), E.View.of(z), (n,), 0, None, 12.0 * n),
+        "row sum [n/1024, 1024]": (E.load(x2), E.View(m2, strides=(1, 0)), (rows, 1024), 1, "sum", 4.0 * n),
+        "column sum [1024, n/1024] -> [n/1024]": (E.load(E.View(x, strides=(1, rows))), E.View(m2, strides=(1, 0)), (rows, 1024), 1, "sum", 4.0 * n),
+    }
+    hbm, _ = _peak()
+    out = {}
+    stream = torch.cuda.ExternalStream(rt.stream, device=f"cuda:{rt.device}")
+    for name, (root, ov, shape, nr, op, nbytes) in cases.items():
+        prog = E.Program(root)
+        for _ in range(a.warmup):
+            E.run(rt, prog, ov, shape, nr, op)
+        with torch.cuda.stream(stream):
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(stream)
+            for _ in range(a.iters):
+                E.run(rt, prog, ov, shape, nr, op)
+            t1.record(stream)
+        rt.sync()
+        per = t0.elapsed_time(t1) / a.iters / 1e3
+        out[name] = {"us": per * 1e6, "GB/s": nbytes / per / 1e9, "frac_of_measured_hbm": nbytes / per / 1e9 / hbm, "program_words": len(prog.code)}
+    return {"kernel": "expr_kernel", "elements": n, "cases": out}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn_decode", "gemv", "gemm", "relu_matmul"])
+    ap.add_argument("what", choices=["attn_decode", "gemv", "gemm", "relu_matmul", "expr"])
+    ap.add_argument("--elements", type=int, default=1 << 26)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--heads", type=int, default=25)
     ap.add_argument("--context", type=int, default=700)
@@ -133,7 +172,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
     with B200Runtime(0) as rt:
-        print(json.dumps({"attn_decode": attn_decode, "gemv": gemv, "gemm": gemm, "relu_matmul": relu_matmul}[a.what](rt, a)))
+        print(json.dumps({"attn_decode": attn_decode, "gemv": gemv, "gemm": gemm, "relu_matmul": relu_matmul, "expr": expr}[a.what](rt, a)))
 
 
 if __name__ == "__main__":
