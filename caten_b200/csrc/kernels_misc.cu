@@ -100,19 +100,57 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__re
   const float4 *xr = reinterpret_cast<const float4 *>(x) + src_row * d4;
   float4 v[LN_MAXV];
   float sum = 0.0f;
+  if (pin.splits > 0) {
+    // x is the residual input; the row normalised is residual + the pending linear output, which
+    // also becomes the new residual stream.  The partial tiles of all the thread's columns are
+    // fetched together, eight splits at a time (the kernel is latency-bound: 256 CTAs, a few
+    // loads each), and added in split order.
+    const float *src[LN_MAXV];
+    float4 t[LN_MAXV];
+    bool on[LN_MAXV];
 #pragma unroll
-  for (int i = 0; i < LN_MAXV; ++i) {
-    const int c = threadIdx.x + LN_THREADS * i;
-    if (c < d4) {
-      v[i] = xr[c];
-      if (pin.splits > 0) {
-        // x is the residual input; the row normalised is residual + the pending linear output,
-        // which also becomes the new residual stream
-        const float4 t = partin_load4(pin, src_row, 4 * c);
-        v[i].x = v[i].x + t.x; v[i].y = v[i].y + t.y; v[i].z = v[i].z + t.z; v[i].w = v[i].w + t.w;
+    for (int i = 0; i < LN_MAXV; ++i) {
+      const int c = threadIdx.x + LN_THREADS * i, o = 4 * c;
+      on[i] = c < d4;
+      const long long tile = (src_row / pin.bnx) * pin.tiles_x + (o >> 7);
+      src[i] = pin.part + (tile * pin.bnx + (src_row % pin.bnx)) * 128 + (o & 127);
+      t[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (on[i]) v[i] = xr[c];
+    }
+    for (int z0 = 0; z0 < pin.splits; z0 += 8) {
+      float4 a[LN_MAXV][8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+#pragma unroll
+        for (int i = 0; i < LN_MAXV; ++i)
+          if (on[i] && z0 + u < pin.splits) a[i][u] = __ldcs(reinterpret_cast<const float4 *>(src[i] + (long long)(z0 + u) * pin.zstride));
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+#pragma unroll
+        for (int i = 0; i < LN_MAXV; ++i)
+          if (on[i] && z0 + u < pin.splits) { t[i].x += a[i][u].x; t[i].y += a[i][u].y; t[i].z += a[i][u].z; t[i].w += a[i][u].w; }
+    }
+#pragma unroll
+    for (int i = 0; i < LN_MAXV; ++i) {
+      const int c = threadIdx.x + LN_THREADS * i;
+      if (on[i]) {
+        if (pin.bias) {
+          const float4 bb = *reinterpret_cast<const float4 *>(pin.bias + 4 * c);
+          t[i].x = t[i].x + bb.x; t[i].y = t[i].y + bb.y; t[i].z = t[i].z + bb.z; t[i].w = t[i].w + bb.w;
+        }
+        v[i].x = v[i].x + t[i].x; v[i].y = v[i].y + t[i].y; v[i].z = v[i].z + t[i].z; v[i].w = v[i].w + t[i].w;
         reinterpret_cast<float4 *>(xout)[src_row * d4 + c] = v[i];
+        sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
       }
-      sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < LN_MAXV; ++i) {
+      const int c = threadIdx.x + LN_THREADS * i;
+      if (c < d4) {
+        v[i] = xr[c];
+        sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+      }
     }
   }
   const float u = ln_block_sum(sum, red) * invd;
