@@ -17,6 +17,9 @@ constexpr float kInvLn2 = 1.0f / 0.6931472f;  // (/ (log 2)) in single float, ap
 // Scores are kept in shared memory (t <= T floats) and the softmax is the reference's two-pass
 // form (max, then exp and sum), not an online rescaling.
 // ---------------------------------------------------------------------------------------------
+#ifndef ATT_U
+#define ATT_U 4  // rows in flight per half-warp
+#endif
 __global__ void __launch_bounds__(256) attn_decode_kernel(const float *__restrict__ qkv, float *__restrict__ kc,
                                                           float *__restrict__ vc, float *__restrict__ out, int H,
                                                           int T, int n, const int *__restrict__ d_n,
@@ -51,15 +54,15 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float *__restric
   __syncthreads();
   const int hw = tid >> 4, l16 = tid & 15;
   const float4 q4 = reinterpret_cast<const float4 *>(q)[l16];
-  for (int j0 = 0; j0 < t; j0 += 64) {
-    float4 k4[4];
+  for (int j0 = 0; j0 < t; j0 += 16 * ATT_U) {
+    float4 k4[ATT_U];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < ATT_U; ++u) {
       const int j = j0 + u * 16 + hw;
       k4[u] = j < t ? __ldcs(reinterpret_cast<const float4 *>(kb + (int64_t)j * 64) + l16) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < ATT_U; ++u) {
       float p = fmaf(q4.x, k4[u].x, fmaf(q4.y, k4[u].y, fmaf(q4.z, k4[u].z, q4.w * k4[u].w)));
       p += __shfl_xor_sync(0xffffffffu, p, 8);
       p += __shfl_xor_sync(0xffffffffu, p, 4);
@@ -96,18 +99,18 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float *__restric
   const float inv = 1.0f / ss;
   // O = P.V
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int j0 = 0; j0 < t; j0 += 64) {
-    float4 v4[4];
-    float p[4];
+  for (int j0 = 0; j0 < t; j0 += 16 * ATT_U) {
+    float4 v4[ATT_U];
+    float p[ATT_U];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < ATT_U; ++u) {
       const int j = j0 + u * 16 + hw;
       const bool ok = j < t;
       v4[u] = ok ? __ldcs(reinterpret_cast<const float4 *>(vb + (int64_t)j * 64) + l16) : make_float4(0.f, 0.f, 0.f, 0.f);
       p[u] = ok ? sc[j] * inv : 0.0f;
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < ATT_U; ++u) {
       acc.x = fmaf(p[u], v4[u].x, acc.x);
       acc.y = fmaf(p[u], v4[u].y, acc.y);
       acc.z = fmaf(p[u], v4[u].z, acc.z);

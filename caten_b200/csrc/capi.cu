@@ -107,7 +107,7 @@ int caten_b200_init(int device, caten_b200_ctx **out) {
   ctx->device = device;
   ctx->sm_count = prop.multiProcessorCount;
   if (const char *e = getenv("CATEN_B200_PDL")) ctx->use_pdl = atoi(e) != 0;
-  if (const char *e = getenv("CATEN_B200_SPLITK_CLUSTER")) ctx->splitk_cluster = atoi(e) != 0;
+  if (const char *e = getenv("CATEN_B200_SPLITK_CLUSTER")) ctx->splitk_cluster = atoi(e);
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaStreamCreate"); }
   if ((e = cudaMalloc(&ctx->d_status, 4 * sizeof(int))) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaMalloc"); }
   cudaMemset(ctx->d_status, 0, 4 * sizeof(int));
@@ -226,7 +226,7 @@ int64_t caten_b200_weight_nbytes(int type, int64_t rows, int64_t cols) {
     case CATEN_B200_Q4_0: return cols % 32 ? -1 : n / 32 * 18;
     case CATEN_B200_Q8_0: return cols % 32 ? -1 : n / 32 * 34;
   }
-  return -1;
+  return cb::extra_type_nbytes(type, n, cols);
 }
 
 int caten_b200_weight_upload_device(caten_b200_ctx *ctx, int type, const void *d_blocks, int64_t rows, int64_t cols,
@@ -237,12 +237,17 @@ int caten_b200_weight_upload_device(caten_b200_ctx *ctx, int type, const void *d
   if (!d_blocks || rows <= 0 || cols <= 0) return fail(ctx, CATEN_B200_EINVAL, "weight_upload: NULL data or empty shape %lldx%lld", (long long)rows, (long long)cols);
   const int64_t nbytes = caten_b200_weight_nbytes(type, rows, cols);
   if (nbytes < 0)
-    return fail(ctx, CATEN_B200_EUNSUPPORTED, "weight_upload: ggml type %d with cols=%lld (types: F32=0 F16=1 Q4_0=2 Q8_0=8; quantised cols %% 32 == 0)", type, (long long)cols);
+    return fail(ctx, CATEN_B200_EUNSUPPORTED, "weight_upload: ggml type %d with cols=%lld (types: F32=0 F16=1 Q4_0=2 Q4_1=3 Q5_0=6 Q5_1=7 Q8_0=8 Q4_K=12 Q5_K=13 Q6_K=14; cols a multiple of the block size)", type, (long long)cols);
   caten_b200_weight *w = new (std::nothrow) caten_b200_weight();
   if (!w) return fail(ctx, CATEN_B200_ECUDA, "out of host memory");
   w->type = type; w->rows = rows; w->cols = cols; w->ctx = ctx;
   cudaError_t e;
-  if (type == CATEN_B200_F32 || type == CATEN_B200_F16) {
+  if (cb::extra_type_nbytes(type, rows * cols, cols) >= 0) {
+    // a block format the kernels do not consume packed: expand to fp32 now, keep an fp32 weight
+    w->type = CATEN_B200_F32;
+    if ((e = cudaMalloc(&w->qs, (size_t)(rows * cols) * sizeof(float))) != cudaSuccess) { delete w; return cuda_fail(ctx, e, "cudaMalloc(weight)"); }
+    if (int rc = launch_dequant_extra(ctx, type, (const uint8_t *)d_blocks, rows * cols, (float *)w->qs)) { cudaFree(w->qs); delete w; return rc; }
+  } else if (type == CATEN_B200_F32 || type == CATEN_B200_F16) {
     if ((e = cudaMalloc(&w->qs, (size_t)nbytes)) != cudaSuccess) { delete w; return cuda_fail(ctx, e, "cudaMalloc(weight)"); }
     if ((e = cudaMemcpyAsync(w->qs, d_blocks, (size_t)nbytes, cudaMemcpyDeviceToDevice, ctx->stream)) != cudaSuccess) {
       cudaFree(w->qs); delete w; return cuda_fail(ctx, e, "cudaMemcpyAsync(weight)");
@@ -267,7 +272,7 @@ int caten_b200_weight_upload(caten_b200_ctx *ctx, int type, const void *h_blocks
   if (!h_blocks || rows <= 0 || cols <= 0) return fail(ctx, CATEN_B200_EINVAL, "weight_upload: NULL data or empty shape %lldx%lld", (long long)rows, (long long)cols);
   const int64_t nbytes = caten_b200_weight_nbytes(type, rows, cols);
   if (nbytes < 0)
-    return fail(ctx, CATEN_B200_EUNSUPPORTED, "weight_upload: ggml type %d with cols=%lld (types: F32=0 F16=1 Q4_0=2 Q8_0=8; quantised cols %% 32 == 0)", type, (long long)cols);
+    return fail(ctx, CATEN_B200_EUNSUPPORTED, "weight_upload: ggml type %d with cols=%lld (types: F32=0 F16=1 Q4_0=2 Q4_1=3 Q5_0=6 Q5_1=7 Q8_0=8 Q4_K=12 Q5_K=13 Q6_K=14; cols a multiple of the block size)", type, (long long)cols);
   void *staging = nullptr;
   CB_CUDA(ctx, cudaMalloc(&staging, (size_t)nbytes));
   cudaError_t e = cudaMemcpyAsync(staging, h_blocks, (size_t)nbytes, cudaMemcpyHostToDevice, ctx->stream);
@@ -388,6 +393,16 @@ int caten_b200_argmax(caten_b200_ctx *ctx, const float *d_x, int64_t rows, int64
   NEED_CTX(ctx);
   if (!d_x || !d_out) return fail(ctx, CATEN_B200_EINVAL, "argmax: NULL argument");
   return launch_argmax(ctx, d_x, rows, V, d_out);
+}
+
+int caten_b200_sample(caten_b200_ctx *ctx, const float *d_logits, int64_t rows, int64_t V, float temperature, int top_k,
+                      const float *d_uniform, int64_t *d_out) {
+  NEED_CTX(ctx);
+  if (!d_logits || !d_out) return fail(ctx, CATEN_B200_EINVAL, "sample: NULL argument");
+  if (V <= 0) return fail(ctx, CATEN_B200_EINVAL, "sample: V=%lld", (long long)V);
+  if (!(temperature > 0.0f)) return launch_argmax(ctx, d_logits, rows, V, d_out);
+  if (!d_uniform) return fail(ctx, CATEN_B200_EINVAL, "sample: uniform numbers are NULL");
+  return launch_sample(ctx, d_logits, rows, V, temperature, top_k, d_uniform, d_out);
 }
 
 int caten_b200_eval_expr(caten_b200_ctx *ctx, const caten_b200_expr *e) {

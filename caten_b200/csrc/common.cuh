@@ -88,8 +88,9 @@ struct caten_b200_ctx {
   int64_t launches = 0;
   // split-K partial tiles: reduced by a second kernel through global scratch (default: it overlaps
   // with its neighbours under programmatic dependent launch and measured faster), or inside a
-  // thread-block cluster through distributed shared memory (CATEN_B200_SPLITK_CLUSTER=1)
-  bool splitk_cluster = false;
+  // thread-block cluster through distributed shared memory (CATEN_B200_SPLITK_CLUSTER=1: every split-K
+  // launch; =2: only launches whose epilogue cannot be handed to the consuming kernel)
+  int splitk_cluster = 0;
   bool use_pdl = true;       // programmatic dependent launch between consecutive kernels (CATEN_B200_PDL=0 turns it off)
   // per-kernel-class event timing (caten_b200_profile_begin / _end)
   unsigned prof_mask = 0;
@@ -128,6 +129,9 @@ int scratch_reserve(caten_b200_ctx *ctx, Scratch *s, size_t bytes);
 // ---- launchers (each returns a status code; all asynchronous on ctx->stream) ----
 int launch_repack(caten_b200_ctx *ctx, int type, const uint8_t *d_blocks, int64_t nblocks, void *qs, __half *d);
 int launch_dequant(caten_b200_ctx *ctx, const caten_b200_weight *w, float *out);
+// block formats that are expanded to fp32 at upload (dequant_extra.cu)
+int64_t extra_type_nbytes(int type, int64_t n, int64_t cols);
+int launch_dequant_extra(caten_b200_ctx *ctx, int type, const uint8_t *d_blocks, int64_t n, float *out);
 int launch_layernorm(caten_b200_ctx *ctx, const float *x, const float *g, const float *b, float *y,
                      int64_t rows, int64_t d, float eps);
 // src_rows: optional gather — row r of the output reads row (r+1)*src_stride-1 of x when src_stride > 1
@@ -145,6 +149,8 @@ int launch_begin_steps(caten_b200_ctx *ctx, const float *ids_f32, const int64_t 
 int launch_finish_step(caten_b200_ctx *ctx, const int64_t *out_ids, int64_t *ids_io, int64_t *hist, int *d_pos, int64_t B);
 int launch_argmax(caten_b200_ctx *ctx, const float *x, int64_t rows, int64_t V, int64_t *out);
 int launch_expr(caten_b200_ctx *ctx, const caten_b200_expr *e);
+int launch_sample(caten_b200_ctx *ctx, const float *logits, int64_t rows, int64_t V, float temperature, int top_k,
+                  const float *uniform, int64_t *out);
 int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc, float *out, int64_t B,
                      int64_t s, int64_t n, int64_t H, int64_t T, const int *d_n = nullptr, cb::BfOut bf = cb::BfOut(),
                      const cb::PartIn *pending_qkv = nullptr);

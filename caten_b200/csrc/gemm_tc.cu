@@ -806,7 +806,10 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
   if (defer) *defer = PartIn();
   if (M <= 0 || N <= 0) return 0;
   TcPlan p;
-  if (int rc = tc_plan(ctx, "gemm_tc", M, N, K, nsplit, ctx->splitk_cluster ? 8 : 32, &p)) return rc;  // 8 = portable cluster size
+  // reduce inside a cluster: always (mode 1) or only when this launch needs its own epilogue (mode 2)
+  const bool own_epilogue = !(defer && act == CATEN_B200_ACT_NONE && !ybf.hi && N % 4 == 0);
+  const bool want_cluster = ctx->splitk_cluster == 1 || (ctx->splitk_cluster == 2 && own_epilogue);
+  if (int rc = tc_plan(ctx, "gemm_tc", M, N, K, nsplit, want_cluster ? 8 : 32, &p)) return rc;  // 8 = portable cluster size
   uint8_t *xhi, *xlo;
   if (xhi_pre) {
     // the producer of x already wrote the split bf16 operand
@@ -835,7 +838,7 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.nkb = (int)nkb; a.bnx = p.bnx;
   a.stages = p.stages; a.idesc = p.idesc; a.concat = p.concat;
   a.splits = p.splits; a.cps = p.cps; a.part = nullptr;
-  a.cluster = (p.splits > 1 && ctx->splitk_cluster) ? 1 : 0;
+  a.cluster = (p.splits > 1 && want_cluster) ? 1 : 0;
   if (p.splits > 1 && !a.cluster) {
     if (int rc = scratch_reserve(ctx, &ctx->wtmp, (size_t)p.splits * p.tiles * p.bnx * TC_BM * sizeof(float))) return rc;
     a.part = (float *)ctx->wtmp.ptr;

@@ -129,7 +129,7 @@ def load_gguf(path: str) -> GGUF:
 
 
 def gguf_to_state_dict(g: GGUF, remap=remap_key) -> dict:
-    """`gguf->state-dict` + `remap-state-dict-keys`.  2-D F16/Q8_0/Q4_0 tensors stay packed
+    """`gguf->state-dict` + `remap-state-dict-keys`.  2-D F16 and block-quantised tensors stay packed
     (:class:`Packed`, zero-copy); F32 tensors and all 1-D tensors become float32 arrays (1-D F16 is
     widened).  The arrays are views of the mapping: keep ``g`` open while they are in use."""
     sd = {}
@@ -137,7 +137,7 @@ def gguf_to_state_dict(g: GGUF, remap=remap_key) -> dict:
         t = g.tensors[name]
         raw = t.raw()
         key = remap(name) if remap else name
-        if len(t.dims) == 2 and t.ggml_type in (L.Q4_0, L.Q8_0):
+        if len(t.dims) == 2 and t.ggml_type in L.BLOCK_FORMATS:
             sd[key] = Packed(t.ggml_type, t.dims[1], t.dims[0], raw)
         elif t.ggml_type == L.F32:
             sd[key] = raw.view(np.float32).reshape(t.shape)

@@ -122,6 +122,15 @@ class GPT2:
         ptr = self.rt.lib.caten_b200_gpt2_logits(self._h)
         return B200Buffer(self.rt, ptr, (self.batch, self.params.vocab_size), np.float32, owned=False).numpy()
 
+    def sample(self, uniform, temperature: float = 1.0, top_k: int = 0) -> np.ndarray:
+        """[batch] int64 ids drawn from the last step's logits (they stay on the device)."""
+        ptr = self.rt.lib.caten_b200_gpt2_logits(self._h)
+        lg = B200Buffer(self.rt, ptr, (self.batch, self.params.vocab_size), np.float32, owned=False)
+        ids = self.rt.sample(lg, uniform, temperature, top_k)
+        out = ids.numpy()
+        ids.close()
+        return out
+
     def kv_cache(self, layer: int):
         """(k, v) of one layer as numpy arrays [batch, heads, max_seq_len, 64]."""
         k, v = C.c_void_p(), C.c_void_p()
@@ -160,15 +169,20 @@ def make_gpt2(model_type, state_dict: dict, runtime: Optional[B200Runtime] = Non
     return GPT2(rt, params, state_dict, max_seq_len=max_seq_len, batch=batch, precision=precision, **kw)
 
 
-def gpt2_generate(gpt2: GPT2, prompt_ids, max_length: int = 100) -> np.ndarray:
+def gpt2_generate(gpt2: GPT2, prompt_ids, max_length: int = 100, temperature: float = 0.0, top_k: int = 0, seed: int = 0) -> np.ndarray:
     """`gpt2-generate` (apps/gpt2/gpt2.lisp:97-113) on token ids: the first call feeds the whole
     prompt at start position 0, each later call one token; every call's argmax is appended.
-    Returns [batch, prompt_len + max_length] int64."""
+    Returns [batch, prompt_len + max_length] int64.  With ``temperature`` > 0 the next id is drawn
+    on the device from the step's logits instead (temperature / top-k sampling, seeded; beyond the
+    reference, whose loop is greedy)."""
     tokens = np.ascontiguousarray(prompt_ids, dtype=np.int64).reshape(gpt2.batch, -1)
     start_pos = 0
+    rng = np.random.Generator(np.random.PCG64(seed))
     for _ in range(max_length):
         in_tokens = tokens[:, start_pos:]
         out = gpt2.forward(in_tokens, in_tokens.shape[1], start_pos)
+        if temperature > 0.0:
+            out = gpt2.sample(rng.random(gpt2.batch, dtype=np.float32), temperature, top_k)
         start_pos = tokens.shape[1]
         tokens = np.concatenate([tokens, out.reshape(-1, 1)], axis=1)
     return tokens

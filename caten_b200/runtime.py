@@ -223,3 +223,12 @@ class B200Runtime:
         out = self.open_buffer((rows,), np.int64)
         L.check(self.ctx, self.lib.caten_b200_argmax(self.ctx, x.ptr, rows, V, out.ptr))
         return out
+
+    def sample(self, logits: B200Buffer, uniform, temperature: float = 1.0, top_k: int = 0) -> B200Buffer:
+        """One id per row by temperature / top-k sampling (`caten_b200_sample`; the reference only has the
+        greedy argmax).  ``uniform``: one number in [0, 1) per row (array or device buffer)."""
+        rows, V = logits.shape
+        u = uniform if isinstance(uniform, B200Buffer) else self.transfer_from_array(np.asarray(uniform, np.float32).reshape(rows))
+        out = self.open_buffer((rows,), np.int64)
+        L.check(self.ctx, self.lib.caten_b200_sample(self.ctx, logits.ptr, rows, V, float(temperature), int(top_k), u.ptr, out.ptr))
+        return out

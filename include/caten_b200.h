@@ -37,8 +37,16 @@ enum {
   CATEN_B200_EDEVICE = 4      /* a kernel reported a failed internal check (e.g. a bounded wait ran out) */
 };
 
-/* ggml tensor type ids as stored in GGUF (external/gguf/tensor-info.lisp:3-34). */
-enum { CATEN_B200_F32 = 0, CATEN_B200_F16 = 1, CATEN_B200_Q4_0 = 2, CATEN_B200_Q8_0 = 8 };
+/* ggml tensor type ids as stored in GGUF (external/gguf/tensor-info.lisp:3-34).  F32, F16, Q4_0
+ * and Q8_0 weights stay in their file format on the device and the kernels unpack them; the other
+ * block formats below (ids the reference lists but does not implement) are expanded to fp32 once
+ * at upload, which is what the reference's loader does for every format it knows
+ * (external/gguf/dequantize.lisp:14-53). */
+enum {
+  CATEN_B200_F32 = 0, CATEN_B200_F16 = 1, CATEN_B200_Q4_0 = 2, CATEN_B200_Q8_0 = 8,
+  CATEN_B200_Q4_1 = 3, CATEN_B200_Q5_0 = 6, CATEN_B200_Q5_1 = 7,
+  CATEN_B200_Q4_K = 12, CATEN_B200_Q5_K = 13, CATEN_B200_Q6_K = 14
+};
 
 /* epilogue applied by the Linear kernels after the bias: the scheduler fuses the activation
  * into the matmul kernel (source/test-suite/test-schedule.lisp:72-74). */
@@ -186,6 +194,14 @@ int caten_b200_attention(caten_b200_ctx *ctx, const float *d_qkv, float *d_kcach
                          float *d_out, int64_t B, int64_t s, int64_t n, int64_t H, int64_t T);
 /* argmax over the last axis, lowest index on ties (api/high-level-ops.lisp:314-343). */
 int caten_b200_argmax(caten_b200_ctx *ctx, const float *d_x, int64_t rows, int64_t V, int64_t *d_out);
+/* Temperature / top-k sampling of one id per row.  No counterpart in the reference, whose generate
+ * loop is greedy (apps/gpt2/gpt2.lisp:104-107).  Per row: keep the logits >= the top_k-th largest
+ * (top_k <= 0 or >= V: all; ties at the threshold are kept), weight them by
+ * exp((x - max) / temperature), and return the first index, in index order, whose running weight
+ * reaches d_uniform[row] * total (d_uniform: one number in [0, 1) per row, supplied by the caller,
+ * so the call is a pure function of its inputs).  temperature <= 0 is the argmax. */
+int caten_b200_sample(caten_b200_ctx *ctx, const float *d_logits, int64_t rows, int64_t V, float temperature,
+                      int top_k, const float *d_uniform, int64_t *d_out);
 
 /* ---- whole GPT-2 step ---------------------------------------------------------------------------
  * Replaces one `(forward runtime (x . tokens) (s . len) (n . start-pos))` of
