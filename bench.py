@@ -4,8 +4,11 @@
                     [--workload xl-q4_0-b256|medium-q4_0-b64|small-q8_0-b1|small-f32-b1] [--precision bf16x3|bf16|fp32]
 
 A "step" is one KV-cached greedy decode step of the whole batch (one new token per sequence).
-Default workload: GPT-2 XL, Q4_0 weights, 256 sequences, 512-token prompts, fp32 KV cache, batch
-sharded over the N GPUs with replicated weights (strong scaling).  Prints ONE JSON line on rank 0.
+Default workload: GPT-2 XL, Q4_0 weights, 256 sequences per GPU, 512-token prompts, fp32 KV cache.
+Sequences are independent, so they are sharded over the N GPUs with replicated weights and no
+collective on the data path; `--scaling weak` (default) keeps the workload's batch on every GPU
+(global batch = batch x N), `--scaling strong` splits one batch of that size over the GPUs.
+Prints ONE JSON line on rank 0.
 
 * ``value``  decode tokens/s with token ids resident in HBM (CUDA events on the library's stream,
              barrier + synchronize on both sides, max over ranks).
@@ -136,6 +139,8 @@ def main():
     ap.add_argument("--workload", default="xl-q4_0-b256", choices=sorted(WORKLOADS))
     ap.add_argument("--precision", default="bf16x3", choices=["fp32", "bf16", "bf16x3"])
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"], help="replay decode steps from a CUDA graph (auto = on; off launches kernel by kernel)")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: the workload's batch on every GPU; strong: one batch of that size split over the GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill/GEMV/kernel-breakdown side measurements")
     args = ap.parse_args()
@@ -144,6 +149,8 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     model_name, wtype, batch, prompt_len, decode_len = WORKLOADS[args.workload]
+    if args.scaling == "weak":
+        batch *= world   # global batch; every rank keeps the workload's own batch
     W = max(0, args.warmup)
     K = args.steps if args.steps is not None else max(1, min(64, decode_len - W - 1))
     if W + K > decode_len:
@@ -165,7 +172,7 @@ def main():
         ctx_len = prompt_len + decode_len // 2
         tps, done, dt = cpu_decode_sample(params, sd, ctx_len, K, threads, budget_s=150.0)
         line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": done, "warmup": 1,
-                "ms_per_step": 1000.0 * dt / done, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "ms_per_step": 1000.0 * dt / done, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
                 "data": "synthetic", "config": config,
                 "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
                                  "sample": f"{done} decode steps of 1 sequence at context {ctx_len}, KV cache pre-filled, OpenMP over output rows"},
@@ -384,10 +391,10 @@ def main():
 
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-                "ms_per_step": dec_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "ms_per_step": dec_ms / K, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
                 "dtype": "f32 (attention, LayerNorm, accumulation); linears " + {"fp32": "f32", "bf16": "bf16 operands", "bf16x3": "split-bf16 operands (3 products)"}[args.precision] + " on tcgen05",
                 "data": "synthetic",
-                "config": {**config, "parallelism": f"batch-sharded x{world}, weights replicated", "local_batch": nb, "precision": args.precision,
+                "config": {**config, "parallelism": f"batch-sharded x{world}, weights replicated", "global_batch": batch, "local_batch": nb, "precision": args.precision,
                            "context_tokens": [prompt_len + W + 1, prompt_len + W + K], "cuda_graph": use_graph,
                            "l2": "inputs larger than L2: every step re-reads the whole KV cache and all weights (>= hundreds of MB)"},
                 "roofline": roofline, "whole_step": {"algorithmic_bytes": step_bytes, "frac_of_hbm_peak": step_frac},
