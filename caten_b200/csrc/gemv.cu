@@ -98,22 +98,13 @@ struct BlkQ8 {
 template <class BLK, int RI>
 __global__ void __launch_bounds__(GEMV_MAX_THREADS) gemv_blocked_kernel(GemvArgs a) {
   extern __shared__ float red[];
-  pdl_enter();
+  // The packed weights depend on no other kernel: the first loads of this CTA's rows are issued
+  // before waiting for the kernel that produces x, so their HBM latency overlaps its tail.
+  pdl_launch_dependents();
   constexpr int W = BLK::WORDS;
   const int tid = threadIdx.x, nkb = a.nkb, G = a.G;
   const bool active = tid < G * nkb;
   const int kb = active ? tid % nkb : 0, ro = active ? tid / nkb : 0;
-  BLK blk;
-  {
-    float xv[32];
-    const float4 *xp = reinterpret_cast<const float4 *>(a.x + (int64_t)kb * 32);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float4 v = xp[i];
-      xv[4 * i] = v.x; xv[4 * i + 1] = v.y; xv[4 * i + 2] = v.z; xv[4 * i + 3] = v.w;
-    }
-    blk.prep(xv);
-  }
   const uint4 *qs = reinterpret_cast<const uint4 *>(a.qs);
   const int rows_per_iter = G * RI;
   const int warp = tid >> 5, lane = tid & 31, nwarps = (blockDim.x + 31) >> 5;
@@ -140,6 +131,18 @@ __global__ void __launch_bounds__(GEMV_MAX_THREADS) gemv_blocked_kernel(GemvArgs
   };
   int64_t base = (int64_t)blockIdx.x * rows_per_iter;
   if (base < a.N) load(base);
+  pdl_wait();
+  BLK blk;
+  {
+    float xv[32];
+    const float4 *xp = reinterpret_cast<const float4 *>(a.x + (int64_t)kb * 32);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 v = xp[i];
+      xv[4 * i] = v.x; xv[4 * i + 1] = v.y; xv[4 * i + 2] = v.z; xv[4 * i + 3] = v.w;
+    }
+    blk.prep(xv);
+  }
   int buf = 0;
   for (; base < a.N; base += stride) {
     uint32_t q[RI][W];
@@ -201,31 +204,64 @@ __global__ void __launch_bounds__(256) gemv_dense_kernel(const T *__restrict__ W
                                                          const float *__restrict__ bias, const float *__restrict__ res,
                                                          float *__restrict__ y, int act, int N, int K) {
   extern __shared__ float xs[];
-  pdl_enter();
+  // weights depend on no other kernel: the first tile of this warp's rows is loaded before the
+  // wait for the producer of x
+  pdl_launch_dependents();
   constexpr int VEC = DenseLoad<T>::VEC;
-  for (int i = threadIdx.x; i < K; i += blockDim.x) xs[i] = x[i];
-  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = K / VEC;
-  for (int64_t base = ((int64_t)blockIdx.x * 8 + warp) * RI; base < N; base += (int64_t)gridDim.x * 8 * RI) {
+  const int64_t first = ((int64_t)blockIdx.x * 8 + warp) * RI;
+  float w0[RI][VEC];
+#pragma unroll
+  for (int i = 0; i < RI; ++i) {
+    if (first + i < N && lane < nvec) DenseLoad<T>::load(W + (first + i) * K + (int64_t)lane * VEC, w0[i]);
+    else {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) w0[i][j] = 0.0f;
+    }
+  }
+  pdl_wait();
+  for (int i = threadIdx.x; i < K; i += blockDim.x) xs[i] = x[i];
+  __syncthreads();
+  for (int64_t base = first; base < N; base += (int64_t)gridDim.x * 8 * RI) {
     float acc[RI];
 #pragma unroll
     for (int i = 0; i < RI; ++i) acc[i] = 0.0f;
-    for (int c = lane; c < nvec; c += 32) {
-      float wv[RI][VEC];
-#pragma unroll
-      for (int i = 0; i < RI; ++i) {
-        if (base + i < N) DenseLoad<T>::load(W + (base + i) * K + (int64_t)c * VEC, wv[i]);
-        else {
-#pragma unroll
-          for (int j = 0; j < VEC; ++j) wv[i][j] = 0.0f;
-        }
-      }
+    int c = lane;
+    if (base == first && c < nvec) {  // the tile fetched before the wait
 #pragma unroll
       for (int j = 0; j < VEC; ++j) {
         const float xv = xs[c * VEC + j];
 #pragma unroll
-        for (int i = 0; i < RI; ++i) acc[i] = fmaf(xv, wv[i][j], acc[i]);
+        for (int i = 0; i < RI; ++i) acc[i] = fmaf(xv, w0[i][j], acc[i]);
+      }
+      c += 32;
+    }
+    // four tiles per lane in flight; the products are still added in increasing k
+    for (; c < nvec; c += 32 * 4) {
+      float wv[4][RI][VEC];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+#pragma unroll
+        for (int i = 0; i < RI; ++i) {
+          if (c + 32 * u < nvec && base + i < N) {
+            DenseLoad<T>::load(W + (base + i) * K + (int64_t)(c + 32 * u) * VEC, wv[u][i]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) wv[u][i][j] = 0.0f;
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (c + 32 * u < nvec) {
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) {
+            const float xv = xs[(c + 32 * u) * VEC + j];
+#pragma unroll
+            for (int i = 0; i < RI; ++i) acc[i] = fmaf(xv, wv[u][i][j], acc[i]);
+          }
+        }
       }
     }
 #pragma unroll
@@ -274,17 +310,27 @@ int launch_gemv(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x,
   }
   const size_t smem = (size_t)K * sizeof(float);
   if (smem > 160 * 1024) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv: cols=%d too wide", K);
-  const int64_t groups = ((int64_t)N + 8 * 2 - 1) / (8 * 2);
+  // two rows per warp when that still gives every SM a CTA, else one row per warp (more CTAs)
+  const bool two = ((int64_t)N + 15) / 16 >= ctx->sm_count;
+  const int64_t groups = two ? ((int64_t)N + 15) / 16 : ((int64_t)N + 7) / 8;
   int64_t grid = (int64_t)ctx->sm_count * 4;
   if (grid > groups) grid = groups;
   if (w->type == CATEN_B200_F32) {
     if (K % 4) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv f32: cols %% 4 != 0");
-    if (smem > 48 * 1024) cudaFuncSetAttribute(gemv_dense_kernel<float, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_k(ctx, gemv_dense_kernel<float, 2>, dim3((unsigned)grid), dim3(256), smem, (const float *)w->qs, x, bias, res, y, act, N, K);
+    if (smem > 48 * 1024) {
+      cudaFuncSetAttribute(gemv_dense_kernel<float, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaFuncSetAttribute(gemv_dense_kernel<float, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    if (two) launch_k(ctx, gemv_dense_kernel<float, 2>, dim3((unsigned)grid), dim3(256), smem, (const float *)w->qs, x, bias, res, y, act, N, K);
+    else launch_k(ctx, gemv_dense_kernel<float, 1>, dim3((unsigned)grid), dim3(256), smem, (const float *)w->qs, x, bias, res, y, act, N, K);
   } else if (w->type == CATEN_B200_F16) {
     if (K % 8) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv f16: cols %% 8 != 0");
-    if (smem > 48 * 1024) cudaFuncSetAttribute(gemv_dense_kernel<__half, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_k(ctx, gemv_dense_kernel<__half, 2>, dim3((unsigned)grid), dim3(256), smem, (const __half *)w->qs, x, bias, res, y, act, N, K);
+    if (smem > 48 * 1024) {
+      cudaFuncSetAttribute(gemv_dense_kernel<__half, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaFuncSetAttribute(gemv_dense_kernel<__half, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    if (two) launch_k(ctx, gemv_dense_kernel<__half, 2>, dim3((unsigned)grid), dim3(256), smem, (const __half *)w->qs, x, bias, res, y, act, N, K);
+    else launch_k(ctx, gemv_dense_kernel<__half, 1>, dim3((unsigned)grid), dim3(256), smem, (const __half *)w->qs, x, bias, res, y, act, N, K);
   } else {
     return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv: weight type %d", w->type);
   }
