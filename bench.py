@@ -384,7 +384,7 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         ctx_len = prompt_len + decode_len // 2
-        tps, done, dt = cpu_decode_sample(params, sd, ctx_len, 6, 1, budget_s=30.0)
+        tps, done, dt = cpu_decode_sample(params, sd, ctx_len, 24, 1, budget_s=15.0)   # about 10-15 s of CPU work
         cpu = {"value": tps, "unit": "tokens/s", "cores": 1, "kind": "port",
                "sample": f"{done} decode steps of 1 sequence at context {ctx_len} (KV cache pre-filled), {dt:.1f} s; "
                          "BACKEND=CLANG executes its kernels on one thread"}
