@@ -435,31 +435,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
     int s = g;
     uint32_t ph = 0;
     bool alive = g < ga;
-    for (int kb = 0; kb * ga + g < num_k && alive; kb += DEPTH) {
+    // ring[0] is always the chunk being converted: after each chunk the ring shifts down by one
+    // (a few register moves) and the new load goes to the last slot, so the conversion code
+    // exists once in the kernel instead of once per slot (a launch starts with a cold
+    // instruction cache, and this loop is most of the kernel's code).
+    for (int kc = g; kc < num_k && alive; kc += ga) {
+      int got = 0;
+      if (lane == 0) {
+        got = mbar_wait(empty(s), ph ^ 1u, abort_flag) ? 1 : 0;
+        if (!got && !*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 1; a.status[2] = kc; }
+      }
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) {
+        alive = false;
+      } else {
+        tc_fence_after();  // the MMAs that read this stage are complete (their commit fired `empty`)
+        ring[0].template store<NSPLIT>(t_quad + (uint32_t)s * WCOLS);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_w(s));
 #pragma unroll
-      for (int j = 0; j < DEPTH; ++j) {
-        const int kc = (kb + j) * ga + g;
-        if (kc < num_k && alive) {
-          int got = 0;
-          if (lane == 0) {
-            got = mbar_wait(empty(s), ph ^ 1u, abort_flag) ? 1 : 0;
-            if (!got && !*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 1; a.status[2] = kc; }
-          }
-          got = __shfl_sync(0xffffffffu, got, 0);
-          if (!got) {
-            alive = false;
-          } else {
-            tc_fence_after();  // the MMAs that read this stage are complete (their commit fired `empty`)
-            ring[j].template store<NSPLIT>(t_quad + (uint32_t)s * WCOLS);
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(full_w(s));
-            if (kc + DEPTH * ga < num_k) ring[j].load(a, row, row_ok, kc0 + kc + DEPTH * ga);
-            s += ga;
-            while (s >= S) { s -= S; ph ^= 1u; }
-          }
-        }
+        for (int j = 0; j + 1 < DEPTH; ++j) ring[j] = ring[j + 1];
+        if (kc + DEPTH * ga < num_k) ring[DEPTH - 1].load(a, row, row_ok, kc0 + kc + DEPTH * ga);
+        s += ga;
+        while (s >= S) { s -= S; ph ^= 1u; }
       }
     }
     // ---------------- epilogue ----------------
