@@ -77,3 +77,43 @@ def test_gpt2_from_gguf_file(rt, oracle, tmp_path, wtype):
     h = g.upload("blk.1.ffn_up.weight", rt)
     np.testing.assert_array_equal(h.dequantize().view(np.uint32), fsd["h.1.mlp.c_fc.weight"].view(np.uint32))
     h.close(); g.close(); m.close(); ref.close()
+
+
+def test_text_in_text_out_from_one_gguf_file(rt, tmp_path):
+    """The whole caller-side flow of apps/gpt2/gpt2.lisp:97-113 from one file: tokenizer metadata ->
+    ids -> greedy loop on the GPU -> text.  The weights are random, so only the plumbing is checked:
+    the prompt survives the round trip and every generated id decodes."""
+    from gguf import GGMLQuantizationType as GT
+    from gguf import GGUFWriter
+    from caten_b200.bpe import BYTE2UNICODE, gguf_to_bpe_tokenizer
+    tokens = [BYTE2UNICODE[b] for b in range(256)] + ["th", "the", "Ġthe", "he", "ll", "hell", "hello"]
+    merges = ["t h", "th e", "Ġ the", "h e", "l l", "he ll", "hell o"]
+    p = S.GPT2Params(n_layers=1, n_heads=2, dim=128, vocab_size=len(tokens))
+    T = 48
+    sd = S.synth_state_dict(p, "q8_0", seed=3, max_seq_len=T, trivial_affine=False, weight_std=0.08)
+    path = tmp_path / "tiny-text.gguf"
+    w = GGUFWriter(str(path), "gpt2")
+    w.add_uint32("gpt2.block_count", p.n_layers)
+    w.add_uint32("gpt2.embedding_length", p.dim)
+    w.add_uint32("gpt2.attention.head_count", p.n_heads)
+    w.add_uint32("gpt2.context_length", T)
+    w.add_array("tokenizer.ggml.tokens", tokens)
+    w.add_array("tokenizer.ggml.merges", merges)
+    for k, v in sd.items():
+        if isinstance(v, S.Packed):
+            w.add_tensor(gguf_name(k), v.data.reshape(v.rows, v.cols // 32 * S.BLOCK_BYTES[v.ggml_type]), raw_dtype=GT(v.ggml_type))
+        else:
+            w.add_tensor(gguf_name(k), v)
+    w.write_header_to_file(); w.write_kv_data_to_file(); w.write_tensors_to_file(); w.close()
+
+    g = load_gguf(str(path))
+    tok = gguf_to_bpe_tokenizer(g)
+    g.close()
+    ids = tok.encode("hello the")
+    assert ids == [tokens.index("hello"), tokens.index("Ġthe")]
+    m = make_gpt2_from_gguf(str(path), runtime=rt, batch=1)
+    out = gpt2_generate(m, [ids], max_length=12)
+    assert out.shape == (1, len(ids) + 12) and out.min() >= 0 and out.max() < len(tokens)
+    text = tok.decode(out[0])
+    assert isinstance(text, str) and tok.decode(out[0, :len(ids)]) == "hello the"
+    m.close()
