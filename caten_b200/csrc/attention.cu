@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
 }
 
 int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc, float *out, int64_t B, int64_t s,
-                     int64_t n, int64_t H, int64_t T, const int *d_n, BfOut bf, const PartIn *pending_qkv) {
+                     int64_t n, int64_t H, int64_t T, const int *d_n, BfOut bf, const PartIn *pending_qkv, int tensor_cores) {
   if (B <= 0 || s <= 0) return 0;
   if (pending_qkv && pending_qkv->splits > 0 && s != 1) return fail(ctx, CATEN_B200_EINVAL, "attention: a pending qkv is only supported for single-token steps");
   if (n < 0 || n + s > T) return fail(ctx, CATEN_B200_EINVAL, "attention: positions [%lld,%lld) outside the cache (T=%lld)", (long long)n, (long long)(n + s), (long long)T);
@@ -325,6 +325,7 @@ int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc
   if (d_n) return fail(ctx, CATEN_B200_EINVAL, "attention: a device-side position is only supported for single-token steps");
   launch_k(ctx, kv_append_kernel, dim3((unsigned)(B * s)), dim3(128), 0, qkv, kc, vc, (int)s, (int)n, (int)H, (int)T);
   CB_LAUNCH_CHECK(ctx, "kv_append_kernel");
+  if (tensor_cores) return launch_attention_tc(ctx, qkv, kc, vc, out, B, s, n, H, T, bf);
   const size_t smem = 4 * 64 * PF_LD * sizeof(float);
   CB_CUDA(ctx, cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   launch_k(ctx, attn_prefill_kernel, dim3((unsigned)((s + 63) / 64), (unsigned)H, (unsigned)B), dim3(256), smem, 

@@ -1,0 +1,319 @@
+// Prefill attention (s > 1) on the 5th-generation tensor cores, head dim 64, fp32 KV cache
+// [B, H, T, 64].  Same semantics as the SIMT kernels in attention.cu
+// (external/llm/layers.lisp:3-5,19-51: S = (q.K^T) * 0.125 + causal mask; P = softmax(S) with
+// exp(x) = exp2(x * 1/ln2), two passes: row maximum first, then exp and sum; O = P.V), with both
+// contractions as bf16 hi/lo split products accumulated in fp32 (every operand x = x_hi + x_lo,
+// all four products kept), so the result stays within about 2^-16 of the fp32 one.
+//
+// One CTA = 128 queries of one (sequence, head) = the 128 lanes of tensor memory; keys go in
+// steps of 128.  Per step:
+//   all 8 warps  load the step's K (and V) rows from the cache, split them into bf16 hi/lo and
+//                store them as 128-byte-swizzled K-major tiles in shared memory:
+//                K tile  = 256 rows [K_hi; K_lo] x 64 dims          (B operand of S = Q.K^T)
+//                V^T tile = 128 rows [V_hi^T; V_lo^T] x 128 keys     (B operand of O += P.V)
+//   one thread   issues S[128 x 256] = [Q_hi; Q_lo] . [K_hi; K_lo]^T: columns [0,128) hold the
+//                products with K_hi and [128,256) those with K_lo (Q tile in shared memory)
+//   all 8 warps  read their query's scores from tensor memory (warps w and w+4 share lanes and
+//                take 64 keys each), add the two column blocks, mask, and
+//                pass 1: track the row maximum; pass 2: p = exp2((s - max)/ln2), accumulate the
+//                row sum, split p into bf16 hi/lo and write it back to tensor memory as the A
+//                operand of the second product
+//   one thread   issues O[128 x 128] += [P_hi; P_lo] . [V_hi^T; V_lo^T] (columns [0,64): V_hi,
+//                [64,128): V_lo), accumulating over the key steps in tensor memory
+// Pass 1 runs the first product alone over all key steps to get the exact row maxima (no
+// rescaling of O is ever needed); pass 2 repeats it and does the rest.  The phases of a step
+// are sequential within the CTA (block-wide barriers + one mbarrier the MMAs commit to).
+// TMEM columns: [0,256) S, [256,384) O, [384,512) P (hi 64, lo 64).
+//
+// The mbarrier waits are bounded; when one runs out the CTA records it in the context's status
+// word, skips the remaining work and its output, frees its tensor memory and returns.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace cb {
+
+namespace {
+
+constexpr float kAtInvLn2 = 1.0f / 0.6931472f;  // (/ (log 2)) in single float, api/function.lisp:437-440
+constexpr int AT_Q = 128;                        // queries per CTA (MMA M)
+constexpr int AT_K = 128;                        // keys per step
+constexpr uint32_t AT_COL_S = 0, AT_COL_O = 256, AT_COL_P = 384;
+constexpr uint32_t AT_OFF_Q = 0, AT_OFF_K = 32768, AT_OFF_V = 65536, AT_OFF_MISC = 98304;
+// tiles + exchange buffer + barrier / TMEM slot / abort flag + alignment slack, padded past half of the SM's shared
+// memory: one CTA per SM, since each allocates all 512 TMEM columns
+constexpr size_t AT_SMEM = 116 * 1024;
+static_assert(AT_OFF_MISC + 1024 + 64 + 1024 <= AT_SMEM, "shared-memory layout");
+
+// byte offset of 16-byte chunk `chunk` (0..7) of row `row` in a K-major tile with 128-byte rows
+// and the 128-byte swizzle (8-row groups of 1024 bytes)
+__device__ __forceinline__ uint32_t sw128(int row, int chunk) {
+  return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+// 8 consecutive fp32 of one row -> one chunk of the hi row and one of the lo row
+__device__ __forceinline__ void st_split8(unsigned char *tile, int row_hi, int row_lo, int chunk, const float4 a, const float4 b) {
+  const uint4 hi = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+  const uint4 lo = make_uint4(pack_bf16(bf16_lo(a.x), bf16_lo(a.y)), pack_bf16(bf16_lo(a.z), bf16_lo(a.w)),
+                              pack_bf16(bf16_lo(b.x), bf16_lo(b.y)), pack_bf16(bf16_lo(b.z), bf16_lo(b.w)));
+  *reinterpret_cast<uint4 *>(tile + sw128(row_hi, chunk)) = hi;
+  *reinterpret_cast<uint4 *>(tile + sw128(row_lo, chunk)) = lo;
+}
+
+__device__ __forceinline__ float4 scale4(float4 v, float c) { return make_float4(v.x * c, v.y * c, v.z * c, v.w * c); }
+
+}  // namespace
+
+__global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__restrict__ qkv, const float *__restrict__ kc,
+                                                                  const float *__restrict__ vc, float *__restrict__ out,
+                                                                  int s, int n, int H, int T, __nv_bfloat16 *__restrict__ ohi,
+                                                                  __nv_bfloat16 *__restrict__ olo, int *status,
+                                                                  uint32_t idesc_s, uint32_t idesc_o) {
+  extern __shared__ unsigned char at_raw[];
+  unsigned char *sm = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(at_raw) + 1023) & ~(uintptr_t)1023);
+  float *red = reinterpret_cast<float *>(sm + AT_OFF_MISC);
+  const uint32_t bar = smem_u32(sm + AT_OFF_MISC + 1024);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + AT_OFF_MISC + 1024 + 8);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(sm + AT_OFF_MISC + 1024 + 12);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int quad = warp & 3;  // 32-lane quadrant of tensor memory this warp may access
+  const int hf = warp >> 2;   // which half (of the keys / of the head dims) this thread takes
+  const int r = quad * 32 + lane;  // query row within the tile = TMEM lane; also the key row this thread converts
+  const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * AT_Q;  // tiles with the longest history first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int d = H * 64, t = n + s;
+
+  if (tid == 0) {
+    mbar_init(bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
+  pdl_enter();
+
+  // Q tile: rows [0,128) hi, [128,256) lo; the 1/8 score scale is folded in (a power of two: exact)
+  {
+    const bool okq = q0 + r < s;
+    const float4 *src = reinterpret_cast<const float4 *>(qkv + ((int64_t)b * s + (okq ? q0 + r : 0)) * 3 * d + h * 64 + 32 * hf);
+    float4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = okq ? scale4(src[i], 0.125f) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) st_split8(sm + AT_OFF_Q, r, 128 + r, 4 * hf + c, v[2 * c], v[2 * c + 1]);
+  }
+
+  const float *kb = kc + ((int64_t)b * H + h) * T * 64;
+  const float *vb = vc + ((int64_t)b * H + h) * T * 64;
+  const int kend = min(t, n + q0 + AT_Q);  // keys beyond the last query of this tile are masked
+  const int nblk = (kend + AT_K - 1) / AT_K;
+  const int qi = min(q0 + r, s - 1);  // rows past the end of the step mask like the last row (their output is dropped)
+  const int jmax = n + qi;            // last visible key of this query (< t)
+
+  const uint64_t dq_hi = umma_desc(smem_u32(sm + AT_OFF_Q)), dq_lo = umma_desc(smem_u32(sm + AT_OFF_Q + 16384));
+  const uint64_t dk = umma_desc(smem_u32(sm + AT_OFF_K));
+  uint32_t ph = 0;
+  int ok = 1;
+
+  auto load_rows = [&](const float *base, int j0, float4 *v) {
+    const bool okk = j0 + r < t;
+    const float4 *src = reinterpret_cast<const float4 *>(base + (int64_t)(okk ? j0 + r : 0) * 64 + 32 * hf);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = okk ? __ldg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  };
+  auto store_k = [&](const float4 *v) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) st_split8(sm + AT_OFF_K, r, 128 + r, 4 * hf + c, v[2 * c], v[2 * c + 1]);
+  };
+  auto issue_s = [&]() {
+#pragma unroll
+    for (int k4 = 0; k4 < 4; ++k4) {
+      const uint64_t adv = (uint64_t)(2 * k4);  // 16 bf16 = 32 bytes = 2 descriptor units
+      umma_bf16(tmem_base + AT_COL_S, dq_hi + adv, dk + adv, idesc_s, k4 > 0 ? 1u : 0u);
+      umma_bf16(tmem_base + AT_COL_S, dq_lo + adv, dk + adv, idesc_s, 1u);
+    }
+    umma_commit(bar);
+  };
+  auto wait_mma = [&]() {
+    if (!mbar_wait(bar, ph, abort_flag)) {
+      ok = 0;
+      *abort_flag = 1;
+    }
+    ph ^= 1u;
+  };
+
+  // ---- pass 1: row maxima -------------------------------------------------------------------------
+  float m = -INFINITY;
+  for (int blk = 0; blk < nblk && ok; ++blk) {
+    const int j0 = blk * AT_K;
+    float4 kv[8];
+    load_rows(kb, j0, kv);
+    store_k(kv);
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      issue_s();
+    }
+    wait_mma();
+    tc_fence_after();
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t a[16], l[16];
+      tmem_ld16(tlane + AT_COL_S + 64 * hf + 16 * c, a);
+      tmem_ld16(tlane + AT_COL_S + 128 + 64 * hf + 16 * c, l);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const float val = __uint_as_float(a[e]) + __uint_as_float(l[e]);
+        if (j0 + 64 * hf + 16 * c + e <= jmax) m = fmaxf(m, val);
+      }
+    }
+    tc_fence_before();
+    ok = __syncthreads_and(ok);  // every thread has read S before the next step overwrites it
+  }
+  red[hf * 128 + r] = m;
+  __syncthreads();
+  m = fmaxf(red[r], red[128 + r]);  // key 0 is visible to every query, so this is finite
+  __syncthreads();
+
+  // ---- pass 2: probabilities, row sums, O ----------------------------------------------------------
+  float lsum = 0.0f;
+  for (int blk = 0; blk < nblk && ok; ++blk) {
+    const int j0 = blk * AT_K;
+    float4 kv[8], vv[8];
+    load_rows(kb, j0, kv);
+    load_rows(vb, j0, vv);
+    if (blk > 0) wait_mma();  // the previous step's P.V has read the V^T tile and P
+    store_k(kv);
+    {
+      // V^T tile: element (dim, key) of the hi rows [0,64) and lo rows [64,128); keys in two
+      // 64-key swizzle atoms of 128 rows each
+      unsigned char *vt = sm + AT_OFF_V + (r >> 6) * 16384 + (r & 7) * 2;
+      const int chunk = (r & 63) >> 3;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float e4[4] = {vv[i].x, vv[i].y, vv[i].z, vv[i].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int dim = 32 * hf + 4 * i + e;
+          const __nv_bfloat16 hh = __float2bfloat16_rn(e4[e]);
+          *reinterpret_cast<__nv_bfloat16 *>(vt + sw128(dim, chunk)) = hh;
+          *reinterpret_cast<__nv_bfloat16 *>(vt + sw128(64 + dim, chunk)) = __float2bfloat16_rn(e4[e] - __bfloat162float(hh));
+        }
+      }
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    if (tid == 0) {
+      tc_fence_after();
+      issue_s();
+    }
+    wait_mma();
+    tc_fence_after();
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t a[16], l[16];
+      tmem_ld16(tlane + AT_COL_S + 64 * hf + 16 * c, a);
+      tmem_ld16(tlane + AT_COL_S + 128 + 64 * hf + 16 * c, l);
+      tmem_ld_wait();
+      float p[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const float val = __uint_as_float(a[e]) + __uint_as_float(l[e]);
+        p[e] = (j0 + 64 * hf + 16 * c + e <= jmax) ? exp2f((val - m) * kAtInvLn2) : 0.0f;
+        lsum += p[e];
+      }
+      uint32_t phi[8], plo[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        phi[e] = pack_bf16(p[2 * e], p[2 * e + 1]);
+        plo[e] = pack_bf16(bf16_lo(p[2 * e]), bf16_lo(p[2 * e + 1]));
+      }
+      // 16 keys = 8 columns; key k of the step sits in column k / 2
+      tmem_st8(tlane + AT_COL_P + 8 * (4 * hf + c), phi);
+      tmem_st8(tlane + AT_COL_P + 64 + 8 * (4 * hf + c), plo);
+    }
+    tmem_st_wait();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int k8 = 0; k8 < 8; ++k8) {
+        const uint64_t dv = umma_desc(smem_u32(sm + AT_OFF_V + (k8 >> 2) * 16384)) + (uint64_t)(2 * (k8 & 3));
+        umma_bf16_ts(tmem_base + AT_COL_O, tmem_base + AT_COL_P + 8 * k8, dv, idesc_o, (blk > 0 || k8 > 0) ? 1u : 0u);
+        umma_bf16_ts(tmem_base + AT_COL_O, tmem_base + AT_COL_P + 64 + 8 * k8, dv, idesc_o, 1u);
+      }
+      umma_commit(bar);
+    }
+  }
+  if (ok && nblk > 0) wait_mma();
+  tc_fence_after();
+  red[hf * 128 + r] = lsum;
+  ok = __syncthreads_and(ok);
+  if (ok) {
+    const float inv = 1.0f / (red[r] + red[128 + r]);
+    float o[32];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      uint32_t a[16], l[16];
+      tmem_ld16(tlane + AT_COL_O + 32 * hf + 16 * c, a);
+      tmem_ld16(tlane + AT_COL_O + 64 + 32 * hf + 16 * c, l);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 16; ++e) o[16 * c + e] = (__uint_as_float(a[e]) + __uint_as_float(l[e])) * inv;
+    }
+    if (q0 + r < s) {
+      const int64_t at = ((int64_t)b * s + q0 + r) * d + h * 64 + 32 * hf;
+      if (ohi) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float *p = o + 8 * i;
+          *reinterpret_cast<uint4 *>(ohi + at + 8 * i) =
+              make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
+          if (olo)
+            *reinterpret_cast<uint4 *>(olo + at + 8 * i) =
+                make_uint4(pack_bf16(bf16_lo(p[0]), bf16_lo(p[1])), pack_bf16(bf16_lo(p[2]), bf16_lo(p[3])),
+                           pack_bf16(bf16_lo(p[4]), bf16_lo(p[5])), pack_bf16(bf16_lo(p[6]), bf16_lo(p[7])));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          *reinterpret_cast<float4 *>(out + at + 4 * i) = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+      }
+    }
+  } else if (tid == 0) {
+    atomicCAS(status, 0, DEV_WAIT_TIMEOUT);
+    status[1] = 10;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+int launch_attention_tc(caten_b200_ctx *ctx, const float *qkv, const float *kc, const float *vc, float *out, int64_t B, int64_t s,
+                        int64_t n, int64_t H, int64_t T, BfOut bf) {
+  const uint32_t base = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_Q >> 4) << 24);  // fp32 accumulate, bf16 x bf16, M = 128
+  const uint32_t idesc_s = base | ((uint32_t)(256 >> 3) << 17), idesc_o = base | ((uint32_t)(128 >> 3) << 17);
+  CB_CUDA(ctx, cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AT_SMEM));
+  launch_k(ctx, attn_prefill_tc_kernel, dim3((unsigned)((s + AT_Q - 1) / AT_Q), (unsigned)H, (unsigned)B), dim3(256), AT_SMEM, qkv, kc, vc,
+           out, (int)s, (int)n, (int)H, (int)T, bf.hi, bf.lo, ctx->d_status, idesc_s, idesc_o);
+  CB_LAUNCH_CHECK(ctx, "attn_prefill_tc_kernel");
+  return 0;
+}
+
+}  // namespace cb

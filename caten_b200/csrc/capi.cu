@@ -108,6 +108,7 @@ int caten_b200_init(int device, caten_b200_ctx **out) {
   ctx->sm_count = prop.multiProcessorCount;
   if (const char *e = getenv("CATEN_B200_PDL")) ctx->use_pdl = atoi(e) != 0;
   if (const char *e = getenv("CATEN_B200_SPLITK_CLUSTER")) ctx->splitk_cluster = atoi(e);
+  if (const char *e = getenv("CATEN_B200_ATTN_TC")) ctx->attn_tc = atoi(e);
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaStreamCreate"); }
   if ((e = cudaMalloc(&ctx->d_status, 4 * sizeof(int))) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaMalloc"); }
   cudaMemset(ctx->d_status, 0, 4 * sizeof(int));
@@ -389,6 +390,18 @@ int caten_b200_attention(caten_b200_ctx *ctx, const float *d_qkv, float *d_kcach
   return launch_attention(ctx, d_qkv, d_kcache, d_vcache, d_out, B, s, n, H, T);
 }
 
+int caten_b200_attention_ex(caten_b200_ctx *ctx, const float *d_qkv, float *d_kcache, float *d_vcache, float *d_out,
+                            int64_t B, int64_t s, int64_t n, int64_t H, int64_t T, int precision) {
+  NEED_CTX(ctx);
+  if (!d_qkv || !d_kcache || !d_vcache || !d_out) return fail(ctx, CATEN_B200_EINVAL, "attention: NULL argument");
+  if (B < 0 || s < 0 || H <= 0 || T <= 0) return fail(ctx, CATEN_B200_EINVAL, "attention: bad shape");
+  if (precision != CATEN_B200_PREC_FP32 && precision != CATEN_B200_PREC_BF16 && precision != CATEN_B200_PREC_BF16X3)
+    return fail(ctx, CATEN_B200_EINVAL, "attention: unknown precision %d", precision);
+  ProfScope prof(ctx, s == 1 ? CATEN_B200_K_ATTN_DECODE : CATEN_B200_K_ATTN_PREFILL);
+  return launch_attention(ctx, d_qkv, d_kcache, d_vcache, d_out, B, s, n, H, T, nullptr, cb::BfOut(), nullptr,
+                          precision != CATEN_B200_PREC_FP32);
+}
+
 int caten_b200_argmax(caten_b200_ctx *ctx, const float *d_x, int64_t rows, int64_t V, int64_t *d_out) {
   NEED_CTX(ctx);
   if (!d_x || !d_out) return fail(ctx, CATEN_B200_EINVAL, "argmax: NULL argument");
@@ -590,7 +603,7 @@ static int run_chunk(caten_b200_gpt2 *m, const float *ids_f32, const int64_t *id
   for (int64_t l = 0; l < L; ++l) {
     int rc = layernorm(pend_h, m->h2, m->h, m->ln1_g[l], m->ln1_b[l], m->xn, R, 1, bf(m->xn_bf));
     if (!rc) rc = model_linear(m, m->attn_w[l], m->xn, m->xn_bf, m->attn_b[l], nullptr, CATEN_B200_ACT_NONE, m->qkv, none, R, defer_ok ? &pend_qkv : nullptr);
-    if (!rc) { ProfScope prof(ctx, s == 1 ? CATEN_B200_K_ATTN_DECODE : CATEN_B200_K_ATTN_PREFILL); rc = launch_attention(ctx, m->qkv, m->kc[l] + kv_off, m->vc[l] + kv_off, m->att, nb, s, n, H, T, d_n, bf(m->att_bf), &pend_qkv); }
+    if (!rc) { ProfScope prof(ctx, s == 1 ? CATEN_B200_K_ATTN_DECODE : CATEN_B200_K_ATTN_PREFILL); rc = launch_attention(ctx, m->qkv, m->kc[l] + kv_off, m->vc[l] + kv_off, m->att, nb, s, n, H, T, d_n, bf(m->att_bf), &pend_qkv, prec != CATEN_B200_PREC_FP32 && ctx->attn_tc); }
     if (!rc) rc = model_linear(m, m->proj_w[l], m->att, m->att_bf, m->proj_b[l], m->h, CATEN_B200_ACT_NONE, m->h2, none, R, defer_ok ? &pend_h2 : nullptr);
     if (!rc) rc = layernorm(pend_h2, m->h, m->h2, m->ln2_g[l], m->ln2_b[l], m->xn, R, 1, bf(m->xn_bf));
     if (!rc) rc = model_linear(m, m->fc_w[l], m->xn, m->xn_bf, m->fc_b[l], nullptr, CATEN_B200_ACT_GELU, m->ff, bf(m->ff_bf), R);

@@ -91,6 +91,7 @@ struct caten_b200_ctx {
   // thread-block cluster through distributed shared memory (CATEN_B200_SPLITK_CLUSTER=1: every split-K
   // launch; =2: only launches whose epilogue cannot be handed to the consuming kernel)
   int splitk_cluster = 0;
+  int attn_tc = 1;           // prefill attention of a tensor-core model on the tensor cores (CATEN_B200_ATTN_TC=0: SIMT kernel)
   bool use_pdl = true;       // programmatic dependent launch between consecutive kernels (CATEN_B200_PDL=0 turns it off)
   // per-kernel-class event timing (caten_b200_profile_begin / _end)
   unsigned prof_mask = 0;
@@ -153,7 +154,9 @@ int launch_sample(caten_b200_ctx *ctx, const float *logits, int64_t rows, int64_
                   const float *uniform, int64_t *out);
 int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc, float *out, int64_t B,
                      int64_t s, int64_t n, int64_t H, int64_t T, const int *d_n = nullptr, cb::BfOut bf = cb::BfOut(),
-                     const cb::PartIn *pending_qkv = nullptr);
+                     const cb::PartIn *pending_qkv = nullptr, int tensor_cores = 0);
+int launch_attention_tc(caten_b200_ctx *ctx, const float *qkv, const float *kc, const float *vc, float *out, int64_t B,
+                        int64_t s, int64_t n, int64_t H, int64_t T, cb::BfOut bf);
 int launch_gemv(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
                 const float *res, int act, float *y);
 int launch_gemm_simt(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,

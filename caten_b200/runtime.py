@@ -211,11 +211,13 @@ class B200Runtime:
         L.check(self.ctx, self.lib.caten_b200_embed(self.ctx, f32, i64, wte.ptr, wpe.ptr, out.ptr, B, s, n, d, V, wpe.shape[0]))
         return out
 
-    def attention(self, qkv: B200Buffer, kcache: B200Buffer, vcache: B200Buffer, B: int, s: int, n: int) -> B200Buffer:
-        """kcache/vcache: [B, H, T, 64]; qkv: [B*s, 3*H*64]."""
+    def attention(self, qkv: B200Buffer, kcache: B200Buffer, vcache: B200Buffer, B: int, s: int, n: int,
+                  precision: int = L.PREC_FP32) -> B200Buffer:
+        """kcache/vcache: [B, H, T, 64]; qkv: [B*s, 3*H*64].  A tensor-core precision selects the
+        split-bf16 tensor-core kernel for steps of more than one token."""
         _, H, T, hd = kcache.shape
         out = self.open_buffer((B * s, H * hd), np.float32)
-        L.check(self.ctx, self.lib.caten_b200_attention(self.ctx, qkv.ptr, kcache.ptr, vcache.ptr, out.ptr, B, s, n, H, T))
+        L.check(self.ctx, self.lib.caten_b200_attention_ex(self.ctx, qkv.ptr, kcache.ptr, vcache.ptr, out.ptr, B, s, n, H, T, precision))
         return out
 
     def argmax(self, x: B200Buffer) -> B200Buffer:

@@ -192,6 +192,13 @@ int caten_b200_embed(caten_b200_ctx *ctx, const float *d_ids_f32, const int64_t 
  * is contiguous; the reference's [B, T, H, 64] holds the same values). */
 int caten_b200_attention(caten_b200_ctx *ctx, const float *d_qkv, float *d_kcache, float *d_vcache,
                          float *d_out, int64_t B, int64_t s, int64_t n, int64_t H, int64_t T);
+/* The same with a precision (CATEN_B200_PREC_*) for steps of more than one token: FP32 is
+ * caten_b200_attention; BF16 and BF16X3 run q.K^T and P.V on the tensor cores as bf16 hi/lo split
+ * products with fp32 accumulation (within about 2^-16 of the fp32 result; the softmax itself, exp2
+ * and the row sums stay fp32).  Single-token steps are the same kernel at every precision. */
+int caten_b200_attention_ex(caten_b200_ctx *ctx, const float *d_qkv, float *d_kcache, float *d_vcache,
+                            float *d_out, int64_t B, int64_t s, int64_t n, int64_t H, int64_t T,
+                            int precision);
 /* argmax over the last axis, lowest index on ties (api/high-level-ops.lisp:314-343). */
 int caten_b200_argmax(caten_b200_ctx *ctx, const float *d_x, int64_t rows, int64_t V, int64_t *d_out);
 /* Temperature / top-k sampling of one id per row.  No counterpart in the reference, whose generate

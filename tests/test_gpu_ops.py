@@ -315,6 +315,33 @@ def test_attention_prefill(rt, oracle, B, H, T, s, n):
     np.testing.assert_array_equal(dv.numpy(), _to_gpu_cache(vc))
 
 
+@pytest.mark.parametrize("B,H,T,s,n", [(2, 2, 64, 5, 0), (1, 3, 200, 64, 0), (2, 1, 200, 70, 9), (1, 2, 300, 130, 40),
+                                       (1, 1, 8, 2, 6), (2, 2, 600, 300, 0), (1, 2, 700, 257, 391), (1, 1, 1024, 128, 896),
+                                       (3, 1, 520, 129, 127)])
+def test_attention_prefill_tensor_cores(rt, oracle, B, H, T, s, n):
+    """q.K^T and P.V as split-bf16 tensor-core products: within 2^-16-class error of the fp32
+    statement, the cache append still exact; tiles of 128 queries x 128 keys, so the cases cover
+    partial tiles, several tiles, and a history that starts inside a key step."""
+    rng = np.random.Generator(np.random.PCG64(B + H + T + s + n))
+    d = H * 64
+    kc = np.zeros((B, T, H, 64), np.float32)
+    vc = np.zeros_like(kc)
+    kc[:, :n] = rng.standard_normal((B, n, H, 64), dtype=np.float32)
+    vc[:, :n] = rng.standard_normal((B, n, H, 64), dtype=np.float32)
+    # stale rows past the end of the context must not leak in (they are masked, and 0 * NaN would show)
+    kg, vg = _to_gpu_cache(kc), _to_gpu_cache(vc)
+    kg[:, :, n + s:] = np.nan
+    vg[:, :, n + s:] = np.nan
+    dk, dv = rt.transfer_from_array(kg), rt.transfer_from_array(vg)
+    qkv = rng.standard_normal((B * s, 3 * d), dtype=np.float32)
+    want = oracle.attention(qkv, kc, vc, B, s, n, H, mode=0)
+    for prec in (L.PREC_BF16X3, L.PREC_BF16):
+        got = rt.attention(rt.transfer_from_array(qkv), dk, dv, B, s, n, precision=prec).numpy()
+        np.testing.assert_allclose(got, want, atol=2e-5, rtol=2e-5)
+    np.testing.assert_array_equal(dk.numpy()[:, :, :n + s], _to_gpu_cache(kc)[:, :, :n + s])
+    np.testing.assert_array_equal(dv.numpy()[:, :, :n + s], _to_gpu_cache(vc)[:, :, :n + s])
+
+
 def test_attention_golden_sdpa(rt, golden):
     g = golden["torch_ops"]
     q, k, v = g["sdpa_q"], g["sdpa_k"], g["sdpa_v"]  # [4,4,8,64]
@@ -323,6 +350,8 @@ def test_attention_golden_sdpa(rt, golden):
     dk, dv = rt.open_buffer((B, H, T, hd)), rt.open_buffer((B, H, T, hd))
     got = rt.attention(rt.transfer_from_array(qkv), dk, dv, B, T, 0).numpy()
     np.testing.assert_allclose(got.reshape(B, T, H, hd).transpose(0, 2, 1, 3), g["sdpa_causal_o"], atol=1e-5, rtol=1e-5)
+    got = rt.attention(rt.transfer_from_array(qkv), dk, dv, B, T, 0, precision=L.PREC_BF16X3).numpy()
+    np.testing.assert_allclose(got.reshape(B, T, H, hd).transpose(0, 2, 1, 3), g["sdpa_causal_o"], atol=2e-5, rtol=2e-5)
 
 
 def test_attention_rejects_positions_outside_cache(rt):
