@@ -7,8 +7,10 @@
 //
 // One CTA = 128 queries of one (sequence, head) = the 128 lanes of tensor memory; keys go in
 // steps of 128.  Per step:
-//   all 8 warps  load the step's K (and V) rows from the cache, split them into bf16 hi/lo and
-//                store them as 128-byte-swizzled K-major tiles in shared memory:
+//   all 8 warps  copy the NEXT step's K (and V) rows from the cache into a staging buffer in shared
+//                memory (cp.async, 16 bytes per thread, coalesced; in flight during this step's
+//                MMAs and softmax), and split the current step's staged rows into bf16 hi/lo,
+//                stored as 128-byte-swizzled K-major tiles in shared memory:
 //                K tile  = 256 rows [K_hi; K_lo] x 64 dims          (B operand of S = Q.K^T)
 //                V^T tile = 128 rows [V_hi^T; V_lo^T] x 128 keys     (B operand of O += P.V)
 //   one thread   issues S[128 x 256] = [Q_hi; Q_lo] . [K_hi; K_lo]^T: columns [0,128) hold the
@@ -20,9 +22,11 @@
 //                operand of the second product
 //   one thread   issues O[128 x 128] += [P_hi; P_lo] . [V_hi^T; V_lo^T] (columns [0,64): V_hi,
 //                [64,128): V_lo), accumulating over the key steps in tensor memory
-// Pass 1 runs the first product alone over all key steps to get the exact row maxima (no
-// rescaling of O is ever needed); pass 2 repeats it and does the rest.  The phases of a step
-// are sequential within the CTA (block-wide barriers + one mbarrier the MMAs commit to).
+// Pass 1 runs a cheap form of the first product (Q_hi . K_hi only) over all key steps to get
+// the row maxima, so O never needs rescaling; softmax is invariant to the shift, so a maximum that
+// is off by the bf16 rounding of that product (a fraction of a unit) only changes rounding.
+// Pass 2 does the full products and the rest.  The phases of a step are sequential within the
+// CTA (block-wide barriers + one mbarrier the MMAs commit to).
 // TMEM columns: [0,256) S, [256,384) O, [384,512) P (hi 64, lo 64).
 //
 // The mbarrier waits are bounded; when one runs out the CTA records it in the context's status
@@ -38,11 +42,21 @@ constexpr float kAtInvLn2 = 1.0f / 0.6931472f;  // (/ (log 2)) in single float, 
 constexpr int AT_Q = 128;                        // queries per CTA (MMA M)
 constexpr int AT_K = 128;                        // keys per step
 constexpr uint32_t AT_COL_S = 0, AT_COL_O = 256, AT_COL_P = 384;
-constexpr uint32_t AT_OFF_Q = 0, AT_OFF_K = 32768, AT_OFF_V = 65536, AT_OFF_MISC = 98304;
-// tiles + exchange buffer + barrier / TMEM slot / abort flag + alignment slack, padded past half of the SM's shared
-// memory: one CTA per SM, since each allocates all 512 TMEM columns
-constexpr size_t AT_SMEM = 116 * 1024;
+constexpr uint32_t AT_OFF_Q = 0, AT_OFF_K = 32768, AT_OFF_V = 65536;
+// staging of the raw fp32 rows: 256 bytes per row padded to 272, so that threads reading one row
+// each (16 bytes at a time) spread over all banks
+constexpr uint32_t AT_STAGE_LD = 272;
+constexpr uint32_t AT_OFF_SK = 98304, AT_OFF_SV = AT_OFF_SK + 128 * AT_STAGE_LD, AT_OFF_MISC = AT_OFF_SV + 128 * AT_STAGE_LD;
+// tiles + staging + exchange buffer + barrier / TMEM slot / abort flag + alignment slack: more than half of the SM's
+// shared memory, so one CTA per SM (each allocates all 512 TMEM columns)
+constexpr size_t AT_SMEM = 168 * 1024;
 static_assert(AT_OFF_MISC + 1024 + 64 + 1024 <= AT_SMEM, "shared-memory layout");
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {  // src_bytes 0: zero fill
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 // byte offset of 16-byte chunk `chunk` (0..7) of row `row` in a K-major tile with 128-byte rows
 // and the 128-byte swizzle (8-row groups of 1024 bytes)
@@ -98,17 +112,6 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
   const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
   pdl_enter();
 
-  // Q tile: rows [0,128) hi, [128,256) lo; the 1/8 score scale is folded in (a power of two: exact)
-  {
-    const bool okq = q0 + r < s;
-    const float4 *src = reinterpret_cast<const float4 *>(qkv + ((int64_t)b * s + (okq ? q0 + r : 0)) * 3 * d + h * 64 + 32 * hf);
-    float4 v[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = okq ? scale4(src[i], 0.125f) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int c = 0; c < 4; ++c) st_split8(sm + AT_OFF_Q, r, 128 + r, 4 * hf + c, v[2 * c], v[2 * c + 1]);
-  }
-
   const float *kb = kc + ((int64_t)b * H + h) * T * 64;
   const float *vb = vc + ((int64_t)b * H + h) * T * 64;
   const int kend = min(t, n + q0 + AT_Q);  // keys beyond the last query of this tile are masked
@@ -121,15 +124,20 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
   uint32_t ph = 0;
   int ok = 1;
 
-  auto load_rows = [&](const float *base, int j0, float4 *v) {
-    const bool okk = j0 + r < t;
-    const float4 *src = reinterpret_cast<const float4 *>(base + (int64_t)(okk ? j0 + r : 0) * 64 + 32 * hf);
+  // copy the 128 rows [j0, j0+128) of one head's K or V history into a staging buffer; rows past
+  // the end of the context are zero-filled
+  auto prefetch = [&](const float *base, int j0, uint32_t stage_off) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = okk ? __ldg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < 8; ++i) {
+      const int piece = tid + 256 * i, row = piece >> 4, c16 = piece & 15;
+      const bool okk = j0 + row < t;
+      cp_async16(smem_u32(sm + stage_off + row * AT_STAGE_LD + c16 * 16), base + (int64_t)(okk ? j0 + row : 0) * 64 + c16 * 4, okk ? 16u : 0u);
+    }
   };
-  auto store_k = [&](const float4 *v) {
+  auto staged_row = [&](uint32_t stage_off, float4 *v) {
+    const float4 *src = reinterpret_cast<const float4 *>(sm + stage_off + r * AT_STAGE_LD + 128 * hf);
 #pragma unroll
-    for (int c = 0; c < 4; ++c) st_split8(sm + AT_OFF_K, r, 128 + r, 4 * hf + c, v[2 * c], v[2 * c + 1]);
+    for (int i = 0; i < 8; ++i) v[i] = src[i];
   };
   auto issue_s = [&]() {
 #pragma unroll
@@ -148,36 +156,65 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
     ph ^= 1u;
   };
 
-  // ---- pass 1: row maxima -------------------------------------------------------------------------
+  prefetch(kb, 0, AT_OFF_SK);
+  cp_async_commit();
+  // Q tile: rows [0,128) hi, [128,256) lo; the 1/8 score scale is folded in (a power of two: exact)
+  {
+    const bool okq = q0 + r < s;
+    const float4 *src = reinterpret_cast<const float4 *>(qkv + ((int64_t)b * s + (okq ? q0 + r : 0)) * 3 * d + h * 64 + 32 * hf);
+    float4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = okq ? scale4(src[i], 0.125f) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) st_split8(sm + AT_OFF_Q, r, 128 + r, 4 * hf + c, v[2 * c], v[2 * c + 1]);
+  }
+  cp_async_wait_all();
+  __syncthreads();  // step 0 of K is staged (and the Q tile is written)
+
+  // ---- pass 1: row maxima from Q_hi . K_hi^T --------------------------------------------------------
   float m = -INFINITY;
   for (int blk = 0; blk < nblk && ok; ++blk) {
     const int j0 = blk * AT_K;
-    float4 kv[8];
-    load_rows(kb, j0, kv);
-    store_k(kv);
+    {
+      float4 kv[8];
+      staged_row(AT_OFF_SK, kv);
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        *reinterpret_cast<uint4 *>(sm + AT_OFF_K + sw128(r, 4 * hf + c)) =
+            make_uint4(pack_bf16(kv[2 * c].x, kv[2 * c].y), pack_bf16(kv[2 * c].z, kv[2 * c].w),
+                       pack_bf16(kv[2 * c + 1].x, kv[2 * c + 1].y), pack_bf16(kv[2 * c + 1].z, kv[2 * c + 1].w));
+    }
     fence_proxy_async();
     tc_fence_before();
-    __syncthreads();
+    __syncthreads();  // K_hi tile complete, staging buffer free
+    if (blk + 1 < nblk) {
+      prefetch(kb, j0 + AT_K, AT_OFF_SK);
+    } else {  // first step of pass 2
+      prefetch(kb, 0, AT_OFF_SK);
+      prefetch(vb, 0, AT_OFF_SV);
+    }
+    cp_async_commit();
     if (tid == 0) {
       tc_fence_after();
-      issue_s();
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4)
+        umma_bf16(tmem_base + AT_COL_S, dq_hi + (uint64_t)(2 * k4), dk + (uint64_t)(2 * k4), idesc_o /* N = 128: the K_hi rows */, k4 > 0 ? 1u : 0u);
+      umma_commit(bar);
     }
     wait_mma();
     tc_fence_after();
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      uint32_t a[16], l[16];
+      uint32_t a[16];
       tmem_ld16(tlane + AT_COL_S + 64 * hf + 16 * c, a);
-      tmem_ld16(tlane + AT_COL_S + 128 + 64 * hf + 16 * c, l);
       tmem_ld_wait();
 #pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        const float val = __uint_as_float(a[e]) + __uint_as_float(l[e]);
-        if (j0 + 64 * hf + 16 * c + e <= jmax) m = fmaxf(m, val);
-      }
+      for (int e = 0; e < 16; ++e)
+        if (j0 + 64 * hf + 16 * c + e <= jmax) m = fmaxf(m, __uint_as_float(a[e]));
     }
     tc_fence_before();
-    ok = __syncthreads_and(ok);  // every thread has read S before the next step overwrites it
+    cp_async_wait_all();
+    ok = __syncthreads_and(ok);  // every thread has read S; the next step's rows are staged
   }
   red[hf * 128 + r] = m;
   __syncthreads();
@@ -188,14 +225,18 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
   float lsum = 0.0f;
   for (int blk = 0; blk < nblk && ok; ++blk) {
     const int j0 = blk * AT_K;
-    float4 kv[8], vv[8];
-    load_rows(kb, j0, kv);
-    load_rows(vb, j0, vv);
     if (blk > 0) wait_mma();  // the previous step's P.V has read the V^T tile and P
-    store_k(kv);
+    {
+      float4 kv[8];
+      staged_row(AT_OFF_SK, kv);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) st_split8(sm + AT_OFF_K, r, 128 + r, 4 * hf + c, kv[2 * c], kv[2 * c + 1]);
+    }
     {
       // V^T tile: element (dim, key) of the hi rows [0,64) and lo rows [64,128); keys in two
       // 64-key swizzle atoms of 128 rows each
+      float4 vv[8];
+      staged_row(AT_OFF_SV, vv);
       unsigned char *vt = sm + AT_OFF_V + (r >> 6) * 16384 + (r & 7) * 2;
       const int chunk = (r & 63) >> 3;
 #pragma unroll
@@ -212,8 +253,13 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
     }
     fence_proxy_async();
     tc_fence_before();
-    ok = __syncthreads_and(ok);
+    ok = __syncthreads_and(ok);  // tiles complete, staging buffers free
     if (!ok) break;
+    if (blk + 1 < nblk) {
+      prefetch(kb, j0 + AT_K, AT_OFF_SK);
+      prefetch(vb, j0 + AT_K, AT_OFF_SV);
+      cp_async_commit();
+    }
     if (tid == 0) {
       tc_fence_after();
       issue_s();
@@ -245,7 +291,8 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
     }
     tmem_st_wait();
     tc_fence_before();
-    ok = __syncthreads_and(ok);
+    cp_async_wait_all();
+    ok = __syncthreads_and(ok);  // P is written; the next step's rows are staged
     if (!ok) break;
     if (tid == 0) {
       tc_fence_after();

@@ -1,6 +1,7 @@
 """Single-kernel timings through the C ABI (CUDA events on the library's stream).
 
     python -m caten_b200.microbench attn_decode --batch 64 --heads 25 --context 700
+    python -m caten_b200.microbench attn_prefill --batch 16 --heads 25 --tokens 512 --precision bf16x3
     python -m caten_b200.microbench gemv --model gpt2-xl --wtype q4_0
     python -m caten_b200.microbench gemm --rows 256 --n 1600 --k 6400 --wtype q4_0 --precision bf16x3
     python -m caten_b200.microbench relu_matmul --precision bf16x3
@@ -50,6 +51,28 @@ def attn_decode(rt, a):
     hbm, _ = _peak()
     return {"kernel": "attn_decode_kernel", "batch": B, "heads": H, "context": n + 1, "us": 1e3 * ms / calls,
             "algorithmic_bytes": nbytes, "GB/s": nbytes / (ms / calls / 1e3) / 1e9, "frac_of_measured_hbm": nbytes / (ms / calls / 1e3) / 1e9 / hbm}
+
+
+def attn_prefill(rt, a):
+    """One prefill step of `tokens` tokens after `context` cached ones; the figure of merit is the
+    causal q.K^T + P.V work (4 * 64 flops per visible query-key pair) per second."""
+    B, H, s, n = a.batch, a.heads, a.tokens, a.context
+    T, d = n + s, H * 64
+    prec = {"fp32": L.PREC_FP32, "bf16": L.PREC_BF16, "bf16x3": L.PREC_BF16X3}[a.precision]
+    rng = np.random.Generator(np.random.PCG64(0))
+    dk, dv = rt.open_buffer((B, H, T, 64)), rt.open_buffer((B, H, T, 64))
+    qkv = rt.transfer_from_array(rng.standard_normal((B * s, 3 * d), dtype=np.float32))
+    for i in range(a.warmup):
+        rt.attention(qkv, dk, dv, B, s, n, precision=prec).close()
+    rt.profile_begin(["attn_prefill"])
+    for i in range(a.iters):
+        rt.attention(qkv, dk, dv, B, s, n, precision=prec).close()
+    ms, calls = rt.profile_end()["attn_prefill"]
+    pairs = B * H * (s * n + s * (s + 1) / 2)
+    flops = 4.0 * 64 * pairs
+    return {"kernel": "attn_prefill_kernel" if prec == L.PREC_FP32 else "attn_prefill_tc_kernel", "batch": B, "heads": H,
+            "tokens": s, "context": n, "precision": a.precision, "ms": ms / calls, "includes": "the cache append kernel",
+            "useful_TFLOP/s": flops / (ms / calls / 1e3) / 1e12, "tokens_per_s": B * s / (ms / calls / 1e3)}
 
 
 def gemv(rt, a):
@@ -157,11 +180,12 @@ def expr(rt, a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn_decode", "gemv", "gemm", "relu_matmul", "expr"])
+    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "gemv", "gemm", "relu_matmul", "expr"])
     ap.add_argument("--elements", type=int, default=1 << 26)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--heads", type=int, default=25)
     ap.add_argument("--context", type=int, default=700)
+    ap.add_argument("--tokens", type=int, default=512)
     ap.add_argument("--model", default="gpt2-xl")
     ap.add_argument("--wtype", default="q4_0", choices=["q4_0", "q8_0", "f32"])
     ap.add_argument("--rows", type=int, default=256)
@@ -172,7 +196,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
     with B200Runtime(0) as rt:
-        print(json.dumps({"attn_decode": attn_decode, "gemv": gemv, "gemm": gemm, "relu_matmul": relu_matmul, "expr": expr}[a.what](rt, a)))
+        print(json.dumps({"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemv": gemv, "gemm": gemm, "relu_matmul": relu_matmul, "expr": expr}[a.what](rt, a)))
 
 
 if __name__ == "__main__":
