@@ -2,32 +2,34 @@
 // [B, H, T, 64].  Same semantics as the SIMT kernels in attention.cu
 // (external/llm/layers.lisp:3-5,19-51: S = (q.K^T) * 0.125 + causal mask; P = softmax(S) with
 // exp(x) = exp2(x * 1/ln2), two passes: row maximum first, then exp and sum; O = P.V), with both
-// contractions as bf16 hi/lo split products accumulated in fp32 (every operand x = x_hi + x_lo,
-// all four products kept), so the result stays within about 2^-16 of the fp32 one.
+// contractions as bf16 hi/lo split products accumulated in fp32 (every operand x = x_hi + x_lo;
+// q.K^T keeps all four products, P.V drops only lo*lo), so the result stays within about 2^-16
+// of the fp32 one.
 //
 // One CTA = 128 queries of one (sequence, head) = the 128 lanes of tensor memory; keys go in
-// steps of 128.  Per step:
+// steps of 64.  A CTA uses 256 of the 512 TMEM columns and under half of the shared memory, so
+// two CTAs share an SM and one's MMAs overlap the other's softmax.  Per step:
 //   all 8 warps  copy the NEXT step's K (and V) rows from the cache into a staging buffer in shared
 //                memory (cp.async, 16 bytes per thread, coalesced; in flight during this step's
 //                MMAs and softmax), and split the current step's staged rows into bf16 hi/lo,
 //                stored as 128-byte-swizzled K-major tiles in shared memory:
-//                K tile  = 256 rows [K_hi; K_lo] x 64 dims          (B operand of S = Q.K^T)
-//                V^T tile = 128 rows [V_hi^T; V_lo^T] x 128 keys     (B operand of O += P.V)
-//   one thread   issues S[128 x 256] = [Q_hi; Q_lo] . [K_hi; K_lo]^T: columns [0,128) hold the
-//                products with K_hi and [128,256) those with K_lo (Q tile in shared memory)
+//                K tile   = 128 rows [K_hi; K_lo] x 64 dims          (B operand of S = Q.K^T)
+//                V^T tile = 128 rows [V_hi^T; V_lo^T] x 64 keys      (B operands of O += P.V)
+//   one thread   issues S[128 x 128] = [Q_hi; Q_lo] . [K_hi; K_lo]^T: columns [0,64) hold the
+//                products with K_hi and [64,128) those with K_lo (Q tile in shared memory)
 //   all 8 warps  read their query's scores from tensor memory (warps w and w+4 share lanes and
-//                take 64 keys each), add the two column blocks, mask, and
+//                take 32 keys each), add the two column blocks, mask, and
 //                pass 1: track the row maximum; pass 2: p = exp2((s - max)/ln2), accumulate the
 //                row sum, split p into bf16 hi/lo and write it back to tensor memory as the A
 //                operand of the second product
-//   one thread   issues O[128 x 128] += [P_hi; P_lo] . [V_hi^T; V_lo^T] (columns [0,64): V_hi,
-//                [64,128): V_lo), accumulating over the key steps in tensor memory
+//   one thread   issues O[128 x 64] += P_hi.V_hi + P_lo.V_hi + P_hi.V_lo, accumulating over the
+//                key steps in tensor memory
 // Pass 1 runs a cheap form of the first product (Q_hi . K_hi only) over all key steps to get
 // the row maxima, so O never needs rescaling; softmax is invariant to the shift, so a maximum that
 // is off by the bf16 rounding of that product (a fraction of a unit) only changes rounding.
 // Pass 2 does the full products and the rest.  The phases of a step are sequential within the
 // CTA (block-wide barriers + one mbarrier the MMAs commit to).
-// TMEM columns: [0,256) S, [256,384) O, [384,512) P (hi 64, lo 64).
+// TMEM columns: [0,128) S, [128,192) P (hi 32, lo 32), [192,256) O.
 //
 // The mbarrier waits are bounded; when one runs out the CTA records it in the context's status
 // word, skips the remaining work and its output, frees its tensor memory and returns.
@@ -40,17 +42,17 @@ namespace {
 
 constexpr float kAtInvLn2 = 1.0f / 0.6931472f;  // (/ (log 2)) in single float, api/function.lisp:437-440
 constexpr int AT_Q = 128;                        // queries per CTA (MMA M)
-constexpr int AT_K = 128;                        // keys per step
-constexpr uint32_t AT_COL_S = 0, AT_COL_O = 256, AT_COL_P = 384;
-constexpr uint32_t AT_OFF_Q = 0, AT_OFF_K = 32768, AT_OFF_V = 65536;
+constexpr int AT_K = 64;                         // keys per step
+constexpr uint32_t AT_COLS = 256;                // TMEM columns per CTA
+constexpr uint32_t AT_COL_S = 0, AT_COL_P = 128, AT_COL_O = 192;
+constexpr uint32_t AT_OFF_Q = 0, AT_OFF_K = 32768, AT_OFF_V = 49152;
 // staging of the raw fp32 rows: 256 bytes per row padded to 272, so that threads reading one row
 // each (16 bytes at a time) spread over all banks
 constexpr uint32_t AT_STAGE_LD = 272;
-constexpr uint32_t AT_OFF_SK = 98304, AT_OFF_SV = AT_OFF_SK + 128 * AT_STAGE_LD, AT_OFF_MISC = AT_OFF_SV + 128 * AT_STAGE_LD;
-// tiles + staging + exchange buffer + barrier / TMEM slot / abort flag + alignment slack: more than half of the SM's
-// shared memory, so one CTA per SM (each allocates all 512 TMEM columns)
-constexpr size_t AT_SMEM = 168 * 1024;
-static_assert(AT_OFF_MISC + 1024 + 64 + 1024 <= AT_SMEM, "shared-memory layout");
+constexpr uint32_t AT_OFF_SK = 65536, AT_OFF_SV = AT_OFF_SK + AT_K * AT_STAGE_LD, AT_OFF_MISC = AT_OFF_SV + AT_K * AT_STAGE_LD;
+// tiles + staging + exchange buffer + barrier / TMEM slot / abort flag + alignment slack; two CTAs fit one SM
+constexpr size_t AT_SMEM = AT_OFF_MISC + 1024 + 64 + 1024;
+static_assert(2 * (AT_SMEM + 1024) <= 227 * 1024, "two CTAs per SM");
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {  // src_bytes 0: zero fill
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -64,24 +66,28 @@ __device__ __forceinline__ uint32_t sw128(int row, int chunk) {
   return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
+__device__ __forceinline__ uint4 pack8(const float4 a, const float4 b) {
+  return make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+}
+__device__ __forceinline__ uint4 pack8_lo(const float4 a, const float4 b) {
+  return make_uint4(pack_bf16(bf16_lo(a.x), bf16_lo(a.y)), pack_bf16(bf16_lo(a.z), bf16_lo(a.w)),
+                    pack_bf16(bf16_lo(b.x), bf16_lo(b.y)), pack_bf16(bf16_lo(b.z), bf16_lo(b.w)));
+}
 // 8 consecutive fp32 of one row -> one chunk of the hi row and one of the lo row
 __device__ __forceinline__ void st_split8(unsigned char *tile, int row_hi, int row_lo, int chunk, const float4 a, const float4 b) {
-  const uint4 hi = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
-  const uint4 lo = make_uint4(pack_bf16(bf16_lo(a.x), bf16_lo(a.y)), pack_bf16(bf16_lo(a.z), bf16_lo(a.w)),
-                              pack_bf16(bf16_lo(b.x), bf16_lo(b.y)), pack_bf16(bf16_lo(b.z), bf16_lo(b.w)));
-  *reinterpret_cast<uint4 *>(tile + sw128(row_hi, chunk)) = hi;
-  *reinterpret_cast<uint4 *>(tile + sw128(row_lo, chunk)) = lo;
+  *reinterpret_cast<uint4 *>(tile + sw128(row_hi, chunk)) = pack8(a, b);
+  *reinterpret_cast<uint4 *>(tile + sw128(row_lo, chunk)) = pack8_lo(a, b);
 }
 
 __device__ __forceinline__ float4 scale4(float4 v, float c) { return make_float4(v.x * c, v.y * c, v.z * c, v.w * c); }
 
 }  // namespace
 
-__global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__restrict__ qkv, const float *__restrict__ kc,
+__global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__restrict__ qkv, const float *__restrict__ kc,
                                                                   const float *__restrict__ vc, float *__restrict__ out,
                                                                   int s, int n, int H, int T, __nv_bfloat16 *__restrict__ ohi,
                                                                   __nv_bfloat16 *__restrict__ olo, int *status,
-                                                                  uint32_t idesc_s, uint32_t idesc_o) {
+                                                                  uint32_t idesc_n128, uint32_t idesc_n64) {
   extern __shared__ unsigned char at_raw[];
   unsigned char *sm = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(at_raw) + 1023) & ~(uintptr_t)1023);
   float *red = reinterpret_cast<float *>(sm + AT_OFF_MISC);
@@ -90,8 +96,9 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
   volatile int *abort_flag = reinterpret_cast<volatile int *>(sm + AT_OFF_MISC + 1024 + 12);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int quad = warp & 3;  // 32-lane quadrant of tensor memory this warp may access
-  const int hf = warp >> 2;   // which half (of the keys / of the head dims) this thread takes
-  const int r = quad * 32 + lane;  // query row within the tile = TMEM lane; also the key row this thread converts
+  const int hf = warp >> 2;   // which half (of a step's keys / of the head dims) this thread takes
+  const int r = quad * 32 + lane;  // query row within the tile = TMEM lane
+  const int ck = tid & 63, cq = tid >> 6;  // conversion: key row of the step, and which 16 of its 64 dims
   const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * AT_Q;  // tiles with the longest history first
   const int h = blockIdx.y, b = blockIdx.z;
   const int d = H * 64, t = n + s;
@@ -102,7 +109,7 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(AT_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -121,32 +128,24 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
 
   const uint64_t dq_hi = umma_desc(smem_u32(sm + AT_OFF_Q)), dq_lo = umma_desc(smem_u32(sm + AT_OFF_Q + 16384));
   const uint64_t dk = umma_desc(smem_u32(sm + AT_OFF_K));
+  const uint64_t dv_hi = umma_desc(smem_u32(sm + AT_OFF_V)), dv_lo = umma_desc(smem_u32(sm + AT_OFF_V + 8192));
   uint32_t ph = 0;
   int ok = 1;
 
-  // copy the 128 rows [j0, j0+128) of one head's K or V history into a staging buffer; rows past
+  // copy the 64 rows [j0, j0+64) of one head's K or V history into a staging buffer; rows past
   // the end of the context are zero-filled
   auto prefetch = [&](const float *base, int j0, uint32_t stage_off) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
       const int piece = tid + 256 * i, row = piece >> 4, c16 = piece & 15;
       const bool okk = j0 + row < t;
       cp_async16(smem_u32(sm + stage_off + row * AT_STAGE_LD + c16 * 16), base + (int64_t)(okk ? j0 + row : 0) * 64 + c16 * 4, okk ? 16u : 0u);
     }
   };
-  auto staged_row = [&](uint32_t stage_off, float4 *v) {
-    const float4 *src = reinterpret_cast<const float4 *>(sm + stage_off + r * AT_STAGE_LD + 128 * hf);
+  auto staged_row = [&](uint32_t stage_off, float4 *v) {  // this thread's 16 dims of its key row
+    const float4 *src = reinterpret_cast<const float4 *>(sm + stage_off + ck * AT_STAGE_LD + 64 * cq);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = src[i];
-  };
-  auto issue_s = [&]() {
-#pragma unroll
-    for (int k4 = 0; k4 < 4; ++k4) {
-      const uint64_t adv = (uint64_t)(2 * k4);  // 16 bf16 = 32 bytes = 2 descriptor units
-      umma_bf16(tmem_base + AT_COL_S, dq_hi + adv, dk + adv, idesc_s, k4 > 0 ? 1u : 0u);
-      umma_bf16(tmem_base + AT_COL_S, dq_lo + adv, dk + adv, idesc_s, 1u);
-    }
-    umma_commit(bar);
+    for (int i = 0; i < 4; ++i) v[i] = src[i];
   };
   auto wait_mma = [&]() {
     if (!mbar_wait(bar, ph, abort_flag)) {
@@ -176,13 +175,11 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
   for (int blk = 0; blk < nblk && ok; ++blk) {
     const int j0 = blk * AT_K;
     {
-      float4 kv[8];
+      float4 kv[4];
       staged_row(AT_OFF_SK, kv);
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
-        *reinterpret_cast<uint4 *>(sm + AT_OFF_K + sw128(r, 4 * hf + c)) =
-            make_uint4(pack_bf16(kv[2 * c].x, kv[2 * c].y), pack_bf16(kv[2 * c].z, kv[2 * c].w),
-                       pack_bf16(kv[2 * c + 1].x, kv[2 * c + 1].y), pack_bf16(kv[2 * c + 1].z, kv[2 * c + 1].w));
+      for (int c = 0; c < 2; ++c)
+        *reinterpret_cast<uint4 *>(sm + AT_OFF_K + sw128(ck, 2 * cq + c)) = pack8(kv[2 * c], kv[2 * c + 1]);
     }
     fence_proxy_async();
     tc_fence_before();
@@ -197,20 +194,20 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
     if (tid == 0) {
       tc_fence_after();
 #pragma unroll
-      for (int k4 = 0; k4 < 4; ++k4)
-        umma_bf16(tmem_base + AT_COL_S, dq_hi + (uint64_t)(2 * k4), dk + (uint64_t)(2 * k4), idesc_o /* N = 128: the K_hi rows */, k4 > 0 ? 1u : 0u);
+      for (int k4 = 0; k4 < 4; ++k4)  // N = 64: the K_hi rows only
+        umma_bf16(tmem_base + AT_COL_S, dq_hi + (uint64_t)(2 * k4), dk + (uint64_t)(2 * k4), idesc_n64, k4 > 0 ? 1u : 0u);
       umma_commit(bar);
     }
     wait_mma();
     tc_fence_after();
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t a[16];
-      tmem_ld16(tlane + AT_COL_S + 64 * hf + 16 * c, a);
+    {
+      uint32_t a[32];
+      tmem_ld16(tlane + AT_COL_S + 32 * hf, a);
+      tmem_ld16(tlane + AT_COL_S + 32 * hf + 16, a + 16);
       tmem_ld_wait();
 #pragma unroll
-      for (int e = 0; e < 16; ++e)
-        if (j0 + 64 * hf + 16 * c + e <= jmax) m = fmaxf(m, __uint_as_float(a[e]));
+      for (int e = 0; e < 32; ++e)
+        if (j0 + 32 * hf + e <= jmax) m = fmaxf(m, __uint_as_float(a[e]));
     }
     tc_fence_before();
     cp_async_wait_all();
@@ -227,24 +224,23 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
     const int j0 = blk * AT_K;
     if (blk > 0) wait_mma();  // the previous step's P.V has read the V^T tile and P
     {
-      float4 kv[8];
+      float4 kv[4];
       staged_row(AT_OFF_SK, kv);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) st_split8(sm + AT_OFF_K, r, 128 + r, 4 * hf + c, kv[2 * c], kv[2 * c + 1]);
+      for (int c = 0; c < 2; ++c) st_split8(sm + AT_OFF_K, ck, 64 + ck, 2 * cq + c, kv[2 * c], kv[2 * c + 1]);
     }
     {
-      // V^T tile: element (dim, key) of the hi rows [0,64) and lo rows [64,128); keys in two
-      // 64-key swizzle atoms of 128 rows each
-      float4 vv[8];
+      // V^T tile: element (dim, key) of the hi rows [0,64) and the lo rows [64,128)
+      float4 vv[4];
       staged_row(AT_OFF_SV, vv);
-      unsigned char *vt = sm + AT_OFF_V + (r >> 6) * 16384 + (r & 7) * 2;
-      const int chunk = (r & 63) >> 3;
+      unsigned char *vt = sm + AT_OFF_V + (ck & 7) * 2;
+      const int chunk = ck >> 3;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 4; ++i) {
         const float e4[4] = {vv[i].x, vv[i].y, vv[i].z, vv[i].w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int dim = 32 * hf + 4 * i + e;
+          const int dim = 16 * cq + 4 * i + e;
           const __nv_bfloat16 hh = __float2bfloat16_rn(e4[e]);
           *reinterpret_cast<__nv_bfloat16 *>(vt + sw128(dim, chunk)) = hh;
           *reinterpret_cast<__nv_bfloat16 *>(vt + sw128(64 + dim, chunk)) = __float2bfloat16_rn(e4[e] - __bfloat162float(hh));
@@ -262,21 +258,27 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
     }
     if (tid == 0) {
       tc_fence_after();
-      issue_s();
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4) {
+        const uint64_t adv = (uint64_t)(2 * k4);  // 16 bf16 = 32 bytes = 2 descriptor units
+        umma_bf16(tmem_base + AT_COL_S, dq_hi + adv, dk + adv, idesc_n128, k4 > 0 ? 1u : 0u);
+        umma_bf16(tmem_base + AT_COL_S, dq_lo + adv, dk + adv, idesc_n128, 1u);
+      }
+      umma_commit(bar);
     }
     wait_mma();
     tc_fence_after();
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
       uint32_t a[16], l[16];
-      tmem_ld16(tlane + AT_COL_S + 64 * hf + 16 * c, a);
-      tmem_ld16(tlane + AT_COL_S + 128 + 64 * hf + 16 * c, l);
+      tmem_ld16(tlane + AT_COL_S + 32 * hf + 16 * c, a);
+      tmem_ld16(tlane + AT_COL_S + 64 + 32 * hf + 16 * c, l);
       tmem_ld_wait();
       float p[16];
 #pragma unroll
       for (int e = 0; e < 16; ++e) {
         const float val = __uint_as_float(a[e]) + __uint_as_float(l[e]);
-        p[e] = (j0 + 64 * hf + 16 * c + e <= jmax) ? exp2f((val - m) * kAtInvLn2) : 0.0f;
+        p[e] = (j0 + 32 * hf + 16 * c + e <= jmax) ? exp2f((val - m) * kAtInvLn2) : 0.0f;
         lsum += p[e];
       }
       uint32_t phi[8], plo[8];
@@ -286,8 +288,8 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
         plo[e] = pack_bf16(bf16_lo(p[2 * e]), bf16_lo(p[2 * e + 1]));
       }
       // 16 keys = 8 columns; key k of the step sits in column k / 2
-      tmem_st8(tlane + AT_COL_P + 8 * (4 * hf + c), phi);
-      tmem_st8(tlane + AT_COL_P + 64 + 8 * (4 * hf + c), plo);
+      tmem_st8(tlane + AT_COL_P + 16 * hf + 8 * c, phi);
+      tmem_st8(tlane + AT_COL_P + 32 + 16 * hf + 8 * c, plo);
     }
     tmem_st_wait();
     tc_fence_before();
@@ -297,10 +299,12 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
     if (tid == 0) {
       tc_fence_after();
 #pragma unroll
-      for (int k8 = 0; k8 < 8; ++k8) {
-        const uint64_t dv = umma_desc(smem_u32(sm + AT_OFF_V + (k8 >> 2) * 16384)) + (uint64_t)(2 * (k8 & 3));
-        umma_bf16_ts(tmem_base + AT_COL_O, tmem_base + AT_COL_P + 8 * k8, dv, idesc_o, (blk > 0 || k8 > 0) ? 1u : 0u);
-        umma_bf16_ts(tmem_base + AT_COL_O, tmem_base + AT_COL_P + 64 + 8 * k8, dv, idesc_o, 1u);
+      for (int k4 = 0; k4 < 4; ++k4) {
+        const uint64_t adv = (uint64_t)(2 * k4);
+        const uint32_t p_hi = tmem_base + AT_COL_P + 8 * k4, p_lo = p_hi + 32;
+        umma_bf16_ts(tmem_base + AT_COL_O, p_hi, dv_hi + adv, idesc_n64, (blk > 0 || k4 > 0) ? 1u : 0u);
+        umma_bf16_ts(tmem_base + AT_COL_O, p_lo, dv_hi + adv, idesc_n64, 1u);
+        umma_bf16_ts(tmem_base + AT_COL_O, p_hi, dv_lo + adv, idesc_n64, 1u);
       }
       umma_commit(bar);
     }
@@ -311,16 +315,13 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
   ok = __syncthreads_and(ok);
   if (ok) {
     const float inv = 1.0f / (red[r] + red[128 + r]);
+    uint32_t a[32];
+    tmem_ld16(tlane + AT_COL_O + 32 * hf, a);
+    tmem_ld16(tlane + AT_COL_O + 32 * hf + 16, a + 16);
+    tmem_ld_wait();
     float o[32];
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t a[16], l[16];
-      tmem_ld16(tlane + AT_COL_O + 32 * hf + 16 * c, a);
-      tmem_ld16(tlane + AT_COL_O + 64 + 32 * hf + 16 * c, l);
-      tmem_ld_wait();
-#pragma unroll
-      for (int e = 0; e < 16; ++e) o[16 * c + e] = (__uint_as_float(a[e]) + __uint_as_float(l[e])) * inv;
-    }
+    for (int e = 0; e < 32; ++e) o[e] = __uint_as_float(a[e]) * inv;
     if (q0 + r < s) {
       const int64_t at = ((int64_t)b * s + q0 + r) * d + h * 64 + 32 * hf;
       if (ohi) {
@@ -348,17 +349,17 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const float *__
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(AT_COLS) : "memory");
   }
 }
 
 int launch_attention_tc(caten_b200_ctx *ctx, const float *qkv, const float *kc, const float *vc, float *out, int64_t B, int64_t s,
                         int64_t n, int64_t H, int64_t T, BfOut bf) {
   const uint32_t base = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_Q >> 4) << 24);  // fp32 accumulate, bf16 x bf16, M = 128
-  const uint32_t idesc_s = base | ((uint32_t)(256 >> 3) << 17), idesc_o = base | ((uint32_t)(128 >> 3) << 17);
+  const uint32_t idesc_n128 = base | ((uint32_t)(128 >> 3) << 17), idesc_n64 = base | ((uint32_t)(64 >> 3) << 17);
   CB_CUDA(ctx, cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AT_SMEM));
   launch_k(ctx, attn_prefill_tc_kernel, dim3((unsigned)((s + AT_Q - 1) / AT_Q), (unsigned)H, (unsigned)B), dim3(256), AT_SMEM, qkv, kc, vc,
-           out, (int)s, (int)n, (int)H, (int)T, bf.hi, bf.lo, ctx->d_status, idesc_s, idesc_o);
+           out, (int)s, (int)n, (int)H, (int)T, bf.hi, bf.lo, ctx->d_status, idesc_n128, idesc_n64);
   CB_LAUNCH_CHECK(ctx, "attn_prefill_tc_kernel");
   return 0;
 }
