@@ -222,29 +222,42 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
   float lsum = 0.0f;
   for (int blk = 0; blk < nblk && ok; ++blk) {
     const int j0 = blk * AT_K;
-    if (blk > 0) wait_mma();  // the previous step's P.V has read the V^T tile and P
     {
-      float4 kv[4];
+      // split this thread's part of the staged rows in registers, then (once the previous step's
+      // P.V has read the V^T tile and P) store it into the tiles
+      float4 kv[4], vv[4];
       staged_row(AT_OFF_SK, kv);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) st_split8(sm + AT_OFF_K, ck, 64 + ck, 2 * cq + c, kv[2 * c], kv[2 * c + 1]);
-    }
-    {
-      // V^T tile: element (dim, key) of the hi rows [0,64) and the lo rows [64,128)
-      float4 vv[4];
       staged_row(AT_OFF_SV, vv);
-      unsigned char *vt = sm + AT_OFF_V + (ck & 7) * 2;
-      const int chunk = ck >> 3;
+      uint4 khi[2], klo[2];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        khi[c] = pack8(kv[2 * c], kv[2 * c + 1]);
+        klo[c] = pack8_lo(kv[2 * c], kv[2 * c + 1]);
+      }
+      __nv_bfloat16 vhi[16], vlo[16];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float e4[4] = {vv[i].x, vv[i].y, vv[i].z, vv[i].w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int dim = 16 * cq + 4 * i + e;
-          const __nv_bfloat16 hh = __float2bfloat16_rn(e4[e]);
-          *reinterpret_cast<__nv_bfloat16 *>(vt + sw128(dim, chunk)) = hh;
-          *reinterpret_cast<__nv_bfloat16 *>(vt + sw128(64 + dim, chunk)) = __float2bfloat16_rn(e4[e] - __bfloat162float(hh));
+          vhi[4 * i + e] = __float2bfloat16_rn(e4[e]);
+          vlo[4 * i + e] = __float2bfloat16_rn(e4[e] - __bfloat162float(vhi[4 * i + e]));
         }
+      }
+      if (blk > 0) wait_mma();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        *reinterpret_cast<uint4 *>(sm + AT_OFF_K + sw128(ck, 2 * cq + c)) = khi[c];
+        *reinterpret_cast<uint4 *>(sm + AT_OFF_K + sw128(64 + ck, 2 * cq + c)) = klo[c];
+      }
+      // V^T tile: element (dim, key) of the hi rows [0,64) and the lo rows [64,128)
+      unsigned char *vt = sm + AT_OFF_V + (ck & 7) * 2;
+      const int chunk = ck >> 3;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const int dim = 16 * cq + e;
+        *reinterpret_cast<__nv_bfloat16 *>(vt + sw128(dim, chunk)) = vhi[e];
+        *reinterpret_cast<__nv_bfloat16 *>(vt + sw128(64 + dim, chunk)) = vlo[e];
       }
     }
     fence_proxy_async();
@@ -268,28 +281,33 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
     }
     wait_mma();
     tc_fence_after();
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t a[16], l[16];
-      tmem_ld16(tlane + AT_COL_S + 32 * hf + 16 * c, a);
-      tmem_ld16(tlane + AT_COL_S + 64 + 32 * hf + 16 * c, l);
+    {
+      // this thread's 32 keys: both column blocks in one round trip to tensor memory
+      uint32_t a[32], l[32];
+      tmem_ld16(tlane + AT_COL_S + 32 * hf, a);
+      tmem_ld16(tlane + AT_COL_S + 32 * hf + 16, a + 16);
+      tmem_ld16(tlane + AT_COL_S + 64 + 32 * hf, l);
+      tmem_ld16(tlane + AT_COL_S + 64 + 32 * hf + 16, l + 16);
       tmem_ld_wait();
-      float p[16];
 #pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        const float val = __uint_as_float(a[e]) + __uint_as_float(l[e]);
-        p[e] = (j0 + 32 * hf + 16 * c + e <= jmax) ? exp2f((val - m) * kAtInvLn2) : 0.0f;
-        lsum += p[e];
-      }
-      uint32_t phi[8], plo[8];
+      for (int c = 0; c < 2; ++c) {
+        float p[16];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        phi[e] = pack_bf16(p[2 * e], p[2 * e + 1]);
-        plo[e] = pack_bf16(bf16_lo(p[2 * e]), bf16_lo(p[2 * e + 1]));
+        for (int e = 0; e < 16; ++e) {
+          const float val = __uint_as_float(a[16 * c + e]) + __uint_as_float(l[16 * c + e]);
+          p[e] = (j0 + 32 * hf + 16 * c + e <= jmax) ? exp2f((val - m) * kAtInvLn2) : 0.0f;
+          lsum += p[e];
+        }
+        uint32_t phi[8], plo[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          phi[e] = pack_bf16(p[2 * e], p[2 * e + 1]);
+          plo[e] = pack_bf16(bf16_lo(p[2 * e]), bf16_lo(p[2 * e + 1]));
+        }
+        // 16 keys = 8 columns; key k of the step sits in column k / 2
+        tmem_st8(tlane + AT_COL_P + 16 * hf + 8 * c, phi);
+        tmem_st8(tlane + AT_COL_P + 32 + 16 * hf + 8 * c, plo);
       }
-      // 16 keys = 8 columns; key k of the step sits in column k / 2
-      tmem_st8(tlane + AT_COL_P + 16 * hf + 8 * c, phi);
-      tmem_st8(tlane + AT_COL_P + 32 + 16 * hf + 8 * c, plo);
     }
     tmem_st_wait();
     tc_fence_before();

@@ -44,6 +44,10 @@ def run_parity(rt, oracle, p, wtype, precision, B, prompt_len, steps, T, logit_t
         bound = logit_tol * (np.abs(l32).max() if rel else 1.0)
         assert err <= bound, f"step {step}: logits differ by {err} (bound {bound})"
         ok = comparable_rows(l32, lmix, l64)
+        # with logits within `err` of the oracle's, the greedy id is only determined where the
+        # oracle's top-2 gap exceeds 2 * err (this matters for the bf16 class, whose err is large)
+        top2 = np.sort(l32, axis=1)[:, -2:]
+        ok &= (top2[:, 1] - top2[:, 0]) > 2.0 * err
         np.testing.assert_array_equal(ids[ok], res[0][0][ok])
         np.testing.assert_array_equal(ids, logits.argmax(1))  # the kernel's argmax agrees with its own logits
         checked += int(ok.sum()); total += B
