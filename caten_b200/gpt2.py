@@ -145,6 +145,9 @@ class GPT2:
 
     def close(self):
         if getattr(self, "_h", None):
+            if self.rt.ctx is None:   # the runtime (and with it the stream the model uses) is already gone
+                self._h = None
+                return
             self.rt.lib.caten_b200_gpt2_destroy(self._h)
             self._h = None
             for w in self._weights:

@@ -34,7 +34,7 @@ class B200Buffer:
         return self.runtime.transfer_into_array(self)
 
     def close(self):
-        if self.owned and self.ptr:
+        if self.owned and self.ptr and self.runtime.ctx is not None:
             self.runtime.close_buffer(self)
 
     def view(self, offset_elems: int, shape: Sequence[int]) -> "B200Buffer":
@@ -61,9 +61,9 @@ class B200Weight:
         return a
 
     def close(self):
-        if self.handle:
+        if self.handle and self.runtime.ctx is not None:
             self.runtime.lib.caten_b200_weight_free(self.runtime.ctx, self.handle)
-            self.handle = 0
+        self.handle = 0
 
 
 class B200Runtime:

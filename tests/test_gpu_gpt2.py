@@ -224,3 +224,18 @@ def test_step_errors(rt):
 def test_make_gpt2_by_name(rt):
     with pytest.raises(KeyError):
         make_gpt2("gpt3", {}, runtime=rt)
+
+
+def test_closing_after_the_runtime_is_gone_is_harmless():
+    """A model, weight or buffer that outlives its runtime (a failed test, interpreter exit) must
+    not call into the library with a destroyed context."""
+    from caten_b200.runtime import B200Runtime
+    r = B200Runtime(0)
+    sd = S.synth_state_dict(TINY, "q8_0", seed=1, max_seq_len=16, trivial_affine=False, weight_std=0.08)
+    g = GPT2(r, TINY, sd, max_seq_len=16, batch=2)
+    buf = r.open_buffer((4, 4))
+    g.forward(S.synth_prompts(2, 3, TINY.vocab_size, seed=1), 3, 0)
+    r.close()
+    buf.close()
+    g.close()
+    del g
