@@ -14,8 +14,8 @@ LIB_PATH = os.path.join(HERE, "libcaten_b200.so")
 
 OK, EINVAL, ECUDA, EUNSUPPORTED, EDEVICE = 0, 1, 2, 3, 4
 F32, F16, Q4_0, Q8_0 = 0, 1, 2, 8
-Q4_1, Q5_0, Q5_1, Q4_K, Q5_K, Q6_K = 3, 6, 7, 12, 13, 14   # expanded to fp32 at upload
-BLOCK_FORMATS = (Q4_0, Q8_0, Q4_1, Q5_0, Q5_1, Q4_K, Q5_K, Q6_K)
+Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K = 3, 6, 7, 10, 11, 12, 13, 14   # expanded to fp32 at upload
+BLOCK_FORMATS = (Q4_0, Q8_0, Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K)
 ACT_NONE, ACT_GELU, ACT_RELU = 0, 1, 2
 PREC_FP32, PREC_BF16, PREC_BF16X3 = 0, 1, 2
 K_EMBED, K_LAYERNORM, K_GEMV, K_GEMM, K_ATTN_DECODE, K_ATTN_PREFILL, K_ARGMAX, K_COUNT = 0, 1, 2, 3, 4, 5, 6, 8

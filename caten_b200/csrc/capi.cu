@@ -238,7 +238,7 @@ int caten_b200_weight_upload_device(caten_b200_ctx *ctx, int type, const void *d
   if (!d_blocks || rows <= 0 || cols <= 0) return fail(ctx, CATEN_B200_EINVAL, "weight_upload: NULL data or empty shape %lldx%lld", (long long)rows, (long long)cols);
   const int64_t nbytes = caten_b200_weight_nbytes(type, rows, cols);
   if (nbytes < 0)
-    return fail(ctx, CATEN_B200_EUNSUPPORTED, "weight_upload: ggml type %d with cols=%lld (types: F32=0 F16=1 Q4_0=2 Q4_1=3 Q5_0=6 Q5_1=7 Q8_0=8 Q4_K=12 Q5_K=13 Q6_K=14; cols a multiple of the block size)", type, (long long)cols);
+    return fail(ctx, CATEN_B200_EUNSUPPORTED, "weight_upload: ggml type %d with cols=%lld (types: F32=0 F16=1 Q4_0=2 Q4_1=3 Q5_0=6 Q5_1=7 Q8_0=8 Q2_K=10 Q3_K=11 Q4_K=12 Q5_K=13 Q6_K=14; cols a multiple of the block size)", type, (long long)cols);
   caten_b200_weight *w = new (std::nothrow) caten_b200_weight();
   if (!w) return fail(ctx, CATEN_B200_ECUDA, "out of host memory");
   w->type = type; w->rows = rows; w->cols = cols; w->ctx = ctx;
@@ -273,7 +273,7 @@ int caten_b200_weight_upload(caten_b200_ctx *ctx, int type, const void *h_blocks
   if (!h_blocks || rows <= 0 || cols <= 0) return fail(ctx, CATEN_B200_EINVAL, "weight_upload: NULL data or empty shape %lldx%lld", (long long)rows, (long long)cols);
   const int64_t nbytes = caten_b200_weight_nbytes(type, rows, cols);
   if (nbytes < 0)
-    return fail(ctx, CATEN_B200_EUNSUPPORTED, "weight_upload: ggml type %d with cols=%lld (types: F32=0 F16=1 Q4_0=2 Q4_1=3 Q5_0=6 Q5_1=7 Q8_0=8 Q4_K=12 Q5_K=13 Q6_K=14; cols a multiple of the block size)", type, (long long)cols);
+    return fail(ctx, CATEN_B200_EUNSUPPORTED, "weight_upload: ggml type %d with cols=%lld (types: F32=0 F16=1 Q4_0=2 Q4_1=3 Q5_0=6 Q5_1=7 Q8_0=8 Q2_K=10 Q3_K=11 Q4_K=12 Q5_K=13 Q6_K=14; cols a multiple of the block size)", type, (long long)cols);
   void *staging = nullptr;
   CB_CUDA(ctx, cudaMalloc(&staging, (size_t)nbytes));
   cudaError_t e = cudaMemcpyAsync(staging, h_blocks, (size_t)nbytes, cudaMemcpyHostToDevice, ctx->stream);

@@ -1,5 +1,5 @@
 // GGUF block formats beyond the two the kernels consume packed (Q4_0, Q8_0): Q4_1, Q5_0, Q5_1
-// and the 256-element "K" formats Q4_K, Q5_K, Q6_K.  The reference lists these type ids but
+// and the 256-element "K" formats Q2_K, Q3_K, Q4_K, Q5_K, Q6_K.  The reference lists these type ids but
 // implements none of them (external/gguf/tensor-info.lisp:3-34, 36-41); what it does for the
 // types it knows is dequantise to fp32 at load (external/gguf/dequantize.lisp:14-53), and that is
 // what happens here for these formats: the raw blocks are expanded once, on the device, into an
@@ -68,6 +68,26 @@ __global__ void dequant_block256_kernel(int type, const uint8_t *__restrict__ bl
     int q = upper ? qs[32 * g + l] >> 4 : qs[32 * g + l] & 15;
     if (type == CATEN_B200_Q5_K) q += (b[16 + l] >> sub) & 1 ? 16 : 0;
     w = d * (float)q - m;
+  } else if (type == CATEN_B200_Q2_K) {
+    // scales[16] (low nibble: scale, high nibble: minimum, per 16 weights), qs[64] (2-bit codes), d, dmin;
+    // element = 128 half + 32 j + l uses bits [2j, 2j+2) of byte 32 half + l
+    const uint8_t *b = blocks + blk * 84;
+    const int half = e >> 7, j = (e >> 5) & 3, l = e & 31;
+    const int sc = b[e >> 4];
+    const float dl = h2f(b + 80) * (float)(sc & 15), ml = h2f(b + 82) * (float)(sc >> 4);
+    const int q = (b[16 + 32 * half + l] >> (2 * j)) & 3;
+    w = dl * (float)q - ml;
+  } else if (type == CATEN_B200_Q3_K) {
+    // hmask[32] (bit e/32 of byte e%32: high bit of the code), qs[64] (low 2 bits, laid out as in Q2_K),
+    // scales[12] (16 six-bit scales: low nibbles in bytes 0..7, two more bits each in bytes 8..11), d
+    const uint8_t *b = blocks + blk * 110;
+    const int half = e >> 7, j = (e >> 5) & 3, l = e & 31, i = e >> 4;
+    const uint8_t *s = b + 96;
+    const int lo4 = (i < 8 ? s[i] : s[i - 8] >> 4) & 15, hi2 = (s[8 + (i & 3)] >> (2 * (i >> 2))) & 3;
+    const float dl = h2f(b + 108) * (float)((lo4 | (hi2 << 4)) - 32);
+    const int ql = (b[32 + 32 * half + l] >> (2 * j)) & 3;
+    const int q = ql - (((b[l] >> (e >> 5)) & 1) ? 0 : 4);
+    w = dl * (float)q;
   } else {  // Q6_K: ql[128], qh[64], scales[16] (int8), d
     const uint8_t *b = blocks + blk * 210;
     const int half = e >> 7, r = e & 127, quarter = r >> 5, l = r & 31;  // element = 128 half + 32 quarter + l
@@ -88,6 +108,8 @@ int64_t extra_type_nbytes(int type, int64_t n, int64_t cols) {
     case CATEN_B200_Q4_1: return cols % 32 ? -1 : n / 32 * 20;
     case CATEN_B200_Q5_0: return cols % 32 ? -1 : n / 32 * 22;
     case CATEN_B200_Q5_1: return cols % 32 ? -1 : n / 32 * 24;
+    case CATEN_B200_Q2_K: return cols % 256 ? -1 : n / 256 * 84;
+    case CATEN_B200_Q3_K: return cols % 256 ? -1 : n / 256 * 110;
     case CATEN_B200_Q4_K: return cols % 256 ? -1 : n / 256 * 144;
     case CATEN_B200_Q5_K: return cols % 256 ? -1 : n / 256 * 176;
     case CATEN_B200_Q6_K: return cols % 256 ? -1 : n / 256 * 210;

@@ -226,7 +226,7 @@ int caten_b200_gguf_upload(caten_b200_ctx *ctx, const caten_b200_gguf *g, int64_
   if (!g || i < 0 || i >= (int64_t)g->tensors.size()) return cb::fail(ctx, CATEN_B200_EINVAL, "gguf_upload: index out of range");
   const Tensor &t = g->tensors[(size_t)i];
   if (t.n_dims != 2) return cb::fail(ctx, CATEN_B200_EUNSUPPORTED, "gguf_upload: %s has %d dimensions; Linear weights are 2-D", t.name.c_str(), t.n_dims);
-  if (t.nbytes < 0) return cb::fail(ctx, CATEN_B200_EUNSUPPORTED, "gguf_upload: %s has ggml type %d (held: F32, F16, Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q4_K, Q5_K, Q6_K)", t.name.c_str(), t.type);
+  if (t.nbytes < 0) return cb::fail(ctx, CATEN_B200_EUNSUPPORTED, "gguf_upload: %s has ggml type %d (held: F32, F16, Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K)", t.name.c_str(), t.type);
   // GGUF lists the contiguous dimension first: [cols, rows] (tensor-info.lisp:108 reverses it on load)
   return caten_b200_weight_upload(ctx, t.type, t.data, t.dims[1], t.dims[0], w);
 }

@@ -45,7 +45,7 @@ enum {
 enum {
   CATEN_B200_F32 = 0, CATEN_B200_F16 = 1, CATEN_B200_Q4_0 = 2, CATEN_B200_Q8_0 = 8,
   CATEN_B200_Q4_1 = 3, CATEN_B200_Q5_0 = 6, CATEN_B200_Q5_1 = 7,
-  CATEN_B200_Q4_K = 12, CATEN_B200_Q5_K = 13, CATEN_B200_Q6_K = 14
+  CATEN_B200_Q2_K = 10, CATEN_B200_Q3_K = 11, CATEN_B200_Q4_K = 12, CATEN_B200_Q5_K = 13, CATEN_B200_Q6_K = 14
 };
 
 /* epilogue applied by the Linear kernels after the bias: the scheduler fuses the activation

@@ -148,10 +148,10 @@ def test_malformed_files_are_rejected(tmp_path, sample):
 
 def test_types_outside_the_supported_set_are_listed_but_not_served(tmp_path):
     path = tmp_path / "q.gguf"
-    raw = np.zeros((2, 84), np.uint8)   # one Q2_K block (84 bytes) per row of 256 elements
-    write_file(path, {"w": (raw, GT.Q2_K)})
+    raw = np.zeros((2, 136), np.uint8)   # one IQ4_XS block (136 bytes) per row of 256 elements
+    write_file(path, {"w": (raw, GT.IQ4_XS)})
     g = load_gguf(path)
-    assert g.tensors["w"].ggml_type == int(GT.Q2_K) and g.tensors["w"].nbytes == -1
+    assert g.tensors["w"].ggml_type == int(GT.IQ4_XS) and g.tensors["w"].nbytes == -1
     with pytest.raises(B200Error):
         g.tensors["w"].raw()
     g.close()

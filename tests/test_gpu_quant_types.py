@@ -1,5 +1,5 @@
-"""GPU tests of the GGUF block formats that are expanded to fp32 at upload (Q4_1, Q5_0, Q5_1, Q4_K,
-Q5_K, Q6_K): the device expansion must give, bit for bit, what the Python `gguf` package's
+"""GPU tests of the GGUF block formats that are expanded to fp32 at upload (Q4_1, Q5_0, Q5_1, Q2_K,
+Q3_K, Q4_K, Q5_K, Q6_K): the device expansion must give, bit for bit, what the Python `gguf` package's
 dequantiser gives (the library the reference's own GGUF tests use as their oracle,
 source/test-suite/external/test-gguf.lisp:53-75), and a Linear over such a weight must match the
 product with those values."""
@@ -18,6 +18,7 @@ from gguf.quants import dequantize  # noqa: E402
 # type -> (elements per block, bytes per block, byte offsets of the fp16 fields)
 FORMATS = {
     L.Q4_1: (32, 20, (0, 2)), L.Q5_0: (32, 22, (0,)), L.Q5_1: (32, 24, (0, 2)),
+    L.Q2_K: (256, 84, (80, 82)), L.Q3_K: (256, 110, (108,)),
     L.Q4_K: (256, 144, (0, 2)), L.Q5_K: (256, 176, (0, 2)), L.Q6_K: (256, 210, (208,)),
 }
 
