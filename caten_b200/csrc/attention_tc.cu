@@ -13,12 +13,12 @@
 //                memory (cp.async, 16 bytes per thread, coalesced; in flight during this step's
 //                MMAs and softmax), and split the current step's staged rows into bf16 hi/lo,
 //                stored as 128-byte-swizzled K-major tiles in shared memory:
-//                K tile   = 128 rows [K_hi; K_lo] x 64 dims          (B operand of S = Q.K^T)
-//                V^T tile = 128 rows [V_hi^T; V_lo^T] x 64 keys      (B operands of O += P.V)
-//   one thread   issues S[128 x 128] = [Q_hi; Q_lo] . [K_hi; K_lo]^T: columns [0,64) hold the
-//                products with K_hi and [64,128) those with K_lo (Q tile in shared memory)
+//                K tiles  = 64 keys x 64 dims, hi and lo             (K-major B operands of S = Q.K^T)
+//                V tiles  = 64 keys x 64 dims, hi and lo             (MN-major B operands of O += P.V)
+//   one thread   issues S[128 x 64] = (Q_hi + Q_lo) . (K_hi + K_lo)^T as four MMAs per 16 dims into
+//                the same 64 columns (Q tile in shared memory)
 //   all 8 warps  read their query's scores from tensor memory (warps w and w+4 share lanes and
-//                take 32 keys each), add the two column blocks, mask, and
+//                take 32 keys each), mask, and
 //                pass 1: track the row maximum; pass 2: p = exp2((s - max)/ln2), accumulate the
 //                row sum, split p into bf16 hi/lo and write it back to tensor memory as the A
 //                operand of the second product
@@ -29,7 +29,7 @@
 // is off by the bf16 rounding of that product (a fraction of a unit) only changes rounding.
 // Pass 2 does the full products and the rest.  The phases of a step are sequential within the
 // CTA (block-wide barriers + one mbarrier the MMAs commit to).
-// TMEM columns: [0,128) S, [128,192) P (hi 32, lo 32), [192,256) O.
+// TMEM columns: [0,64) S, [128,192) P (hi 32, lo 32), [192,256) O.
 //
 // The mbarrier waits are bounded; when one runs out the CTA records it in the context's status
 // word, skips the remaining work and its output, frees its tensor memory and returns.
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
                                                                   const float *__restrict__ vc, float *__restrict__ out,
                                                                   int s, int n, int H, int T, __nv_bfloat16 *__restrict__ ohi,
                                                                   __nv_bfloat16 *__restrict__ olo, int *status,
-                                                                  uint32_t idesc_n128, uint32_t idesc_n64) {
+                                                                  uint32_t idesc_n64) {
   extern __shared__ unsigned char at_raw[];
   unsigned char *sm = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(at_raw) + 1023) & ~(uintptr_t)1023);
   float *red = reinterpret_cast<float *>(sm + AT_OFF_MISC);
@@ -127,8 +127,9 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
   const int jmax = n + qi;            // last visible key of this query (< t)
 
   const uint64_t dq_hi = umma_desc(smem_u32(sm + AT_OFF_Q)), dq_lo = umma_desc(smem_u32(sm + AT_OFF_Q + 16384));
-  const uint64_t dk = umma_desc(smem_u32(sm + AT_OFF_K));
+  const uint64_t dk = umma_desc(smem_u32(sm + AT_OFF_K)), dk_lo = umma_desc(smem_u32(sm + AT_OFF_K + 8192));
   const uint64_t dv_hi = umma_desc(smem_u32(sm + AT_OFF_V)), dv_lo = umma_desc(smem_u32(sm + AT_OFF_V + 8192));
+  const uint32_t idesc_pv = idesc_n64 | (1u << 16);  // B operand MN-major: V rows (keys) with the dims contiguous
   uint32_t ph = 0;
   int ok = 1;
 
@@ -147,12 +148,15 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
 #pragma unroll
     for (int i = 0; i < 4; ++i) v[i] = src[i];
   };
+  // one warp polls the mbarrier; the others park at the block barrier instead of spinning (their
+  // issue slots go to the other CTA of the SM)
   auto wait_mma = [&]() {
-    if (!mbar_wait(bar, ph, abort_flag)) {
+    if (warp == 0 && !mbar_wait(bar, ph, abort_flag)) {
       ok = 0;
       *abort_flag = 1;
     }
     ph ^= 1u;
+    ok = __syncthreads_and(ok);
   };
 
   prefetch(kb, 0, AT_OFF_SK);
@@ -234,15 +238,11 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
         khi[c] = pack8(kv[2 * c], kv[2 * c + 1]);
         klo[c] = pack8_lo(kv[2 * c], kv[2 * c + 1]);
       }
-      __nv_bfloat16 vhi[16], vlo[16];
+      uint4 vhi[2], vlo[2];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float e4[4] = {vv[i].x, vv[i].y, vv[i].z, vv[i].w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          vhi[4 * i + e] = __float2bfloat16_rn(e4[e]);
-          vlo[4 * i + e] = __float2bfloat16_rn(e4[e] - __bfloat162float(vhi[4 * i + e]));
-        }
+      for (int c = 0; c < 2; ++c) {
+        vhi[c] = pack8(vv[2 * c], vv[2 * c + 1]);
+        vlo[c] = pack8_lo(vv[2 * c], vv[2 * c + 1]);
       }
       if (blk > 0) wait_mma();
 #pragma unroll
@@ -250,14 +250,11 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
         *reinterpret_cast<uint4 *>(sm + AT_OFF_K + sw128(ck, 2 * cq + c)) = khi[c];
         *reinterpret_cast<uint4 *>(sm + AT_OFF_K + sw128(64 + ck, 2 * cq + c)) = klo[c];
       }
-      // V^T tile: element (dim, key) of the hi rows [0,64) and the lo rows [64,128)
-      unsigned char *vt = sm + AT_OFF_V + (ck & 7) * 2;
-      const int chunk = ck >> 3;
+      // V tiles (hi, then lo): rows = keys, the 64 dims contiguous: the MMA reads them as an MN-major B operand
 #pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        const int dim = 16 * cq + e;
-        *reinterpret_cast<__nv_bfloat16 *>(vt + sw128(dim, chunk)) = vhi[e];
-        *reinterpret_cast<__nv_bfloat16 *>(vt + sw128(64 + dim, chunk)) = vlo[e];
+      for (int c = 0; c < 2; ++c) {
+        *reinterpret_cast<uint4 *>(sm + AT_OFF_V + sw128(ck, 2 * cq + c)) = vhi[c];
+        *reinterpret_cast<uint4 *>(sm + AT_OFF_V + 8192 + sw128(ck, 2 * cq + c)) = vlo[c];
       }
     }
     fence_proxy_async();
@@ -274,27 +271,27 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
 #pragma unroll
       for (int k4 = 0; k4 < 4; ++k4) {
         const uint64_t adv = (uint64_t)(2 * k4);  // 16 bf16 = 32 bytes = 2 descriptor units
-        umma_bf16(tmem_base + AT_COL_S, dq_hi + adv, dk + adv, idesc_n128, k4 > 0 ? 1u : 0u);
-        umma_bf16(tmem_base + AT_COL_S, dq_lo + adv, dk + adv, idesc_n128, 1u);
+        umma_bf16(tmem_base + AT_COL_S, dq_hi + adv, dk + adv, idesc_n64, k4 > 0 ? 1u : 0u);
+        umma_bf16(tmem_base + AT_COL_S, dq_lo + adv, dk + adv, idesc_n64, 1u);
+        umma_bf16(tmem_base + AT_COL_S, dq_hi + adv, dk_lo + adv, idesc_n64, 1u);
+        umma_bf16(tmem_base + AT_COL_S, dq_lo + adv, dk_lo + adv, idesc_n64, 1u);
       }
       umma_commit(bar);
     }
     wait_mma();
     tc_fence_after();
     {
-      // this thread's 32 keys: both column blocks in one round trip to tensor memory
-      uint32_t a[32], l[32];
+      // this thread's 32 keys in one round trip to tensor memory
+      uint32_t a[32];
       tmem_ld16(tlane + AT_COL_S + 32 * hf, a);
       tmem_ld16(tlane + AT_COL_S + 32 * hf + 16, a + 16);
-      tmem_ld16(tlane + AT_COL_S + 64 + 32 * hf, l);
-      tmem_ld16(tlane + AT_COL_S + 64 + 32 * hf + 16, l + 16);
       tmem_ld_wait();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         float p[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float val = __uint_as_float(a[16 * c + e]) + __uint_as_float(l[16 * c + e]);
+          const float val = __uint_as_float(a[16 * c + e]);
           p[e] = (j0 + 32 * hf + 16 * c + e <= jmax) ? exp2f((val - m) * kAtInvLn2) : 0.0f;
           lsum += p[e];
         }
@@ -318,11 +315,11 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
       tc_fence_after();
 #pragma unroll
       for (int k4 = 0; k4 < 4; ++k4) {
-        const uint64_t adv = (uint64_t)(2 * k4);
+        const uint64_t adv = (uint64_t)(128 * k4);  // 16 keys = 16 rows of 128 bytes = 128 descriptor units
         const uint32_t p_hi = tmem_base + AT_COL_P + 8 * k4, p_lo = p_hi + 32;
-        umma_bf16_ts(tmem_base + AT_COL_O, p_hi, dv_hi + adv, idesc_n64, (blk > 0 || k4 > 0) ? 1u : 0u);
-        umma_bf16_ts(tmem_base + AT_COL_O, p_lo, dv_hi + adv, idesc_n64, 1u);
-        umma_bf16_ts(tmem_base + AT_COL_O, p_hi, dv_lo + adv, idesc_n64, 1u);
+        umma_bf16_ts(tmem_base + AT_COL_O, p_hi, dv_hi + adv, idesc_pv, (blk > 0 || k4 > 0) ? 1u : 0u);
+        umma_bf16_ts(tmem_base + AT_COL_O, p_lo, dv_hi + adv, idesc_pv, 1u);
+        umma_bf16_ts(tmem_base + AT_COL_O, p_hi, dv_lo + adv, idesc_pv, 1u);
       }
       umma_commit(bar);
     }
@@ -374,10 +371,10 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
 int launch_attention_tc(caten_b200_ctx *ctx, const float *qkv, const float *kc, const float *vc, float *out, int64_t B, int64_t s,
                         int64_t n, int64_t H, int64_t T, BfOut bf) {
   const uint32_t base = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_Q >> 4) << 24);  // fp32 accumulate, bf16 x bf16, M = 128
-  const uint32_t idesc_n128 = base | ((uint32_t)(128 >> 3) << 17), idesc_n64 = base | ((uint32_t)(64 >> 3) << 17);
+  const uint32_t idesc_n64 = base | ((uint32_t)(64 >> 3) << 17);
   CB_CUDA(ctx, cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AT_SMEM));
   launch_k(ctx, attn_prefill_tc_kernel, dim3((unsigned)((s + AT_Q - 1) / AT_Q), (unsigned)H, (unsigned)B), dim3(256), AT_SMEM, qkv, kc, vc,
-           out, (int)s, (int)n, (int)H, (int)T, bf.hi, bf.lo, ctx->d_status, idesc_n128, idesc_n64);
+           out, (int)s, (int)n, (int)H, (int)T, bf.hi, bf.lo, ctx->d_status, idesc_n64);
   CB_LAUNCH_CHECK(ctx, "attn_prefill_tc_kernel");
   return 0;
 }
