@@ -195,12 +195,15 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
       prefetch(vb, 0, AT_OFF_SV);
     }
     cp_async_commit();
-    if (tid == 0) {
+    if (warp == 0) {  // converged warp, one elected lane: the descriptors stay in uniform registers
       tc_fence_after();
+      if (elect_one()) {
 #pragma unroll
-      for (int k4 = 0; k4 < 4; ++k4)  // N = 64: the K_hi rows only
-        umma_bf16(tmem_base + AT_COL_S, dq_hi + (uint64_t)(2 * k4), dk + (uint64_t)(2 * k4), idesc_n64, k4 > 0 ? 1u : 0u);
-      umma_commit(bar);
+        for (int k4 = 0; k4 < 4; ++k4)  // N = 64: the K_hi rows only
+          umma_bf16(tmem_base + AT_COL_S, dq_hi + (uint64_t)(2 * k4), dk + (uint64_t)(2 * k4), idesc_n64, k4 > 0 ? 1u : 0u);
+        umma_commit(bar);
+      }
+      __syncwarp();
     }
     wait_mma();
     tc_fence_after();
@@ -266,17 +269,20 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
       prefetch(vb, j0 + AT_K, AT_OFF_SV);
       cp_async_commit();
     }
-    if (tid == 0) {
+    if (warp == 0) {  // converged warp, one elected lane: the descriptors stay in uniform registers
       tc_fence_after();
+      if (elect_one()) {
 #pragma unroll
-      for (int k4 = 0; k4 < 4; ++k4) {
-        const uint64_t adv = (uint64_t)(2 * k4);  // 16 bf16 = 32 bytes = 2 descriptor units
-        umma_bf16(tmem_base + AT_COL_S, dq_hi + adv, dk + adv, idesc_n64, k4 > 0 ? 1u : 0u);
-        umma_bf16(tmem_base + AT_COL_S, dq_lo + adv, dk + adv, idesc_n64, 1u);
-        umma_bf16(tmem_base + AT_COL_S, dq_hi + adv, dk_lo + adv, idesc_n64, 1u);
-        umma_bf16(tmem_base + AT_COL_S, dq_lo + adv, dk_lo + adv, idesc_n64, 1u);
+        for (int k4 = 0; k4 < 4; ++k4) {
+          const uint64_t adv = (uint64_t)(2 * k4);  // 16 bf16 = 32 bytes = 2 descriptor units
+          umma_bf16(tmem_base + AT_COL_S, dq_hi + adv, dk + adv, idesc_n64, k4 > 0 ? 1u : 0u);
+          umma_bf16(tmem_base + AT_COL_S, dq_lo + adv, dk + adv, idesc_n64, 1u);
+          umma_bf16(tmem_base + AT_COL_S, dq_hi + adv, dk_lo + adv, idesc_n64, 1u);
+          umma_bf16(tmem_base + AT_COL_S, dq_lo + adv, dk_lo + adv, idesc_n64, 1u);
+        }
+        umma_commit(bar);
       }
-      umma_commit(bar);
+      __syncwarp();
     }
     wait_mma();
     tc_fence_after();
@@ -311,17 +317,20 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
     cp_async_wait_all();
     ok = __syncthreads_and(ok);  // P is written; the next step's rows are staged
     if (!ok) break;
-    if (tid == 0) {
+    if (warp == 0) {  // converged warp, one elected lane: the descriptors stay in uniform registers
       tc_fence_after();
+      if (elect_one()) {
 #pragma unroll
-      for (int k4 = 0; k4 < 4; ++k4) {
-        const uint64_t adv = (uint64_t)(128 * k4);  // 16 keys = 16 rows of 128 bytes = 128 descriptor units
-        const uint32_t p_hi = tmem_base + AT_COL_P + 8 * k4, p_lo = p_hi + 32;
-        umma_bf16_ts(tmem_base + AT_COL_O, p_hi, dv_hi + adv, idesc_pv, (blk > 0 || k4 > 0) ? 1u : 0u);
-        umma_bf16_ts(tmem_base + AT_COL_O, p_lo, dv_hi + adv, idesc_pv, 1u);
-        umma_bf16_ts(tmem_base + AT_COL_O, p_hi, dv_lo + adv, idesc_pv, 1u);
+        for (int k4 = 0; k4 < 4; ++k4) {
+          const uint64_t adv = (uint64_t)(128 * k4);  // 16 keys = 16 rows of 128 bytes = 128 descriptor units
+          const uint32_t p_hi = tmem_base + AT_COL_P + 8 * k4, p_lo = p_hi + 32;
+          umma_bf16_ts(tmem_base + AT_COL_O, p_hi, dv_hi + adv, idesc_pv, (blk > 0 || k4 > 0) ? 1u : 0u);
+          umma_bf16_ts(tmem_base + AT_COL_O, p_lo, dv_hi + adv, idesc_pv, 1u);
+          umma_bf16_ts(tmem_base + AT_COL_O, p_hi, dv_lo + adv, idesc_pv, 1u);
+        }
+        umma_commit(bar);
       }
-      umma_commit(bar);
+      __syncwarp();
     }
   }
   if (ok && nblk > 0) wait_mma();
