@@ -19,16 +19,17 @@
 //                the same 64 columns (Q tile in shared memory)
 //   all 8 warps  read their query's scores from tensor memory (warps w and w+4 share lanes and
 //                take 32 keys each), mask, and
-//                pass 1: track the row maximum; pass 2: p = exp2((s - max)/ln2), accumulate the
-//                row sum, split p into bf16 hi/lo and write it back to tensor memory as the A
-//                operand of the second product
+//                p = exp2((s - max)/ln2), accumulate the row sum, split p into bf16 hi/lo and
+//                write it back to tensor memory as the A operand of the second product
 //   one thread   issues O[128 x 64] += P_hi.V_hi + P_lo.V_hi + P_hi.V_lo, accumulating over the
 //                key steps in tensor memory
-// Pass 1 runs a cheap form of the first product (Q_hi . K_hi only) over all key steps to get
-// the row maxima, so O never needs rescaling; softmax is invariant to the shift, so a maximum that
-// is off by the bf16 rounding of that product (a fraction of a unit) only changes rounding.
-// Pass 2 does the full products and the rest.  The phases of a step are sequential within the
-// CTA (block-wide barriers + one mbarrier the MMAs commit to).
+// The softmax is single-pass with a lazily moved reference maximum: each step exchanges the
+// maximum of its visible scores between the row's two threads; the reference only moves (and O and
+// the row sum are rescaled, O by a TMEM load / multiply / store) when a step exceeds it by more
+// than AT_TAU, which in causal attention happens in the first steps and then rarely.  Softmax is
+// invariant to the reference, so this equals the reference's two-pass form up to rounding.  The
+// phases of a step are sequential within the CTA (block-wide barriers + one mbarrier the MMAs
+// commit to).
 // TMEM columns: [0,64) S, [128,192) P (hi 32, lo 32), [192,256) O.
 //
 // The mbarrier waits are bounded; when one runs out the CTA records it in the context's status
@@ -43,6 +44,7 @@ namespace {
 constexpr float kAtInvLn2 = 1.0f / 0.6931472f;  // (/ (log 2)) in single float, api/function.lisp:437-440
 constexpr int AT_Q = 128;                        // queries per CTA (MMA M)
 constexpr int AT_K = 64;                         // keys per step
+constexpr float AT_TAU = 8.0f;                   // slack of the running maximum, in units of the score
 constexpr uint32_t AT_COLS = 256;                // TMEM columns per CTA
 constexpr uint32_t AT_COL_S = 0, AT_COL_P = 128, AT_COL_O = 192;
 constexpr uint32_t AT_OFF_Q = 0, AT_OFF_K = 32768, AT_OFF_V = 49152;
@@ -160,6 +162,7 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
   };
 
   prefetch(kb, 0, AT_OFF_SK);
+  prefetch(vb, 0, AT_OFF_SV);
   cp_async_commit();
   // Q tile: rows [0,128) hi, [128,256) lo; the 1/8 score scale is folded in (a power of two: exact)
   {
@@ -172,61 +175,11 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
     for (int c = 0; c < 4; ++c) st_split8(sm + AT_OFF_Q, r, 128 + r, 4 * hf + c, v[2 * c], v[2 * c + 1]);
   }
   cp_async_wait_all();
-  __syncthreads();  // step 0 of K is staged (and the Q tile is written)
+  __syncthreads();  // step 0 of K and V is staged (and the Q tile is written)
 
-  // ---- pass 1: row maxima from Q_hi . K_hi^T --------------------------------------------------------
-  float m = -INFINITY;
-  for (int blk = 0; blk < nblk && ok; ++blk) {
-    const int j0 = blk * AT_K;
-    {
-      float4 kv[4];
-      staged_row(AT_OFF_SK, kv);
-#pragma unroll
-      for (int c = 0; c < 2; ++c)
-        *reinterpret_cast<uint4 *>(sm + AT_OFF_K + sw128(ck, 2 * cq + c)) = pack8(kv[2 * c], kv[2 * c + 1]);
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();  // K_hi tile complete, staging buffer free
-    if (blk + 1 < nblk) {
-      prefetch(kb, j0 + AT_K, AT_OFF_SK);
-    } else {  // first step of pass 2
-      prefetch(kb, 0, AT_OFF_SK);
-      prefetch(vb, 0, AT_OFF_SV);
-    }
-    cp_async_commit();
-    if (warp == 0) {  // converged warp, one elected lane: the descriptors stay in uniform registers
-      tc_fence_after();
-      if (elect_one()) {
-#pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4)  // N = 64: the K_hi rows only
-          umma_bf16(tmem_base + AT_COL_S, dq_hi + (uint64_t)(2 * k4), dk + (uint64_t)(2 * k4), idesc_n64, k4 > 0 ? 1u : 0u);
-        umma_commit(bar);
-      }
-      __syncwarp();
-    }
-    wait_mma();
-    tc_fence_after();
-    {
-      uint32_t a[32];
-      tmem_ld16(tlane + AT_COL_S + 32 * hf, a);
-      tmem_ld16(tlane + AT_COL_S + 32 * hf + 16, a + 16);
-      tmem_ld_wait();
-#pragma unroll
-      for (int e = 0; e < 32; ++e)
-        if (j0 + 32 * hf + e <= jmax) m = fmaxf(m, __uint_as_float(a[e]));
-    }
-    tc_fence_before();
-    cp_async_wait_all();
-    ok = __syncthreads_and(ok);  // every thread has read S; the next step's rows are staged
-  }
-  red[hf * 128 + r] = m;
-  __syncthreads();
-  m = fmaxf(red[r], red[128 + r]);  // key 0 is visible to every query, so this is finite
-  __syncthreads();
-
-  // ---- pass 2: probabilities, row sums, O ----------------------------------------------------------
-  float lsum = 0.0f;
+  // ---- key steps: scores, running maximum, probabilities, row sums, O ---------------------------------
+  float m = -INFINITY;  // the row's reference maximum: the same value in both threads of a row
+  float lsum = 0.0f;    // this thread's part of the row sum, relative to m
   for (int blk = 0; blk < nblk && ok; ++blk) {
     const int j0 = blk * AT_K;
     {
@@ -292,13 +245,41 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
       tmem_ld16(tlane + AT_COL_S + 32 * hf, a);
       tmem_ld16(tlane + AT_COL_S + 32 * hf + 16, a + 16);
       tmem_ld_wait();
+      // maximum of the visible scores of this step: over this thread's 32 keys, then over the row's two threads
+      const int lim = jmax - j0 - 32 * hf;  // key e of this thread is visible iff e <= lim
+      float mloc = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 32; ++e)
+        if (e <= lim) mloc = fmaxf(mloc, __uint_as_float(a[e]));
+      red[hf * 128 + r] = mloc;
+      __syncthreads();
+      const float mstep = fmaxf(red[r], red[128 + r]);
+      // The reference maximum only moves when the step's maximum exceeds it by more than AT_TAU
+      // (probabilities then stay below e^AT_TAU, harmless in fp32 / split bf16); when it moves, O and
+      // the row sum accumulated so far are rescaled.  Softmax is invariant to the shift, so this is
+      // the two-pass result up to rounding.  Step 0 always sees key 0, so m is finite from then on.
+      const bool move = mstep > m + AT_TAU;  // also true at step 0 (m = -inf)
+      const float m_new = move ? mstep : m;
+      if (blk > 0 && __any_sync(0xffffffffu, move)) {
+        const float scale = move ? exp2f((m - m_new) * kAtInvLn2) : 1.0f;
+        lsum *= scale;
+        uint32_t o[32];
+        tmem_ld16(tlane + AT_COL_O + 32 * hf, o);
+        tmem_ld16(tlane + AT_COL_O + 32 * hf + 16, o + 16);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * scale);
+        tmem_st16(tlane + AT_COL_O + 32 * hf, o);
+        tmem_st16(tlane + AT_COL_O + 32 * hf + 16, o + 16);
+      }
+      m = m_new;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         float p[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           const float val = __uint_as_float(a[16 * c + e]);
-          p[e] = (j0 + 32 * hf + 16 * c + e <= jmax) ? exp2f((val - m) * kAtInvLn2) : 0.0f;
+          p[e] = (16 * c + e <= lim) ? exp2f((val - m) * kAtInvLn2) : 0.0f;
           lsum += p[e];
         }
         uint32_t phi[8], plo[8];

@@ -342,6 +342,31 @@ def test_attention_prefill_tensor_cores(rt, oracle, B, H, T, s, n):
     np.testing.assert_array_equal(dv.numpy()[:, :, :n + s], _to_gpu_cache(vc)[:, :, :n + s])
 
 
+@pytest.mark.parametrize("B,H,T,s,n,grow", [(2, 2, 600, 300, 0, 1.0), (1, 2, 700, 257, 391, 1.02), (1, 1, 512, 512, 0, 1.01)])
+def test_attention_prefill_tensor_cores_moving_maximum(rt, oracle, B, H, T, s, n, grow):
+    """Large scores whose maximum keeps rising along the keys (key j scaled by grow^j on top of
+    3x inputs): the kernel's reference maximum has to move, and O and the row sums have to be
+    rescaled, many times per row."""
+    rng = np.random.Generator(np.random.PCG64(7 + s + n))
+    d = H * 64
+    t = n + s
+    ramp = (grow ** np.arange(t, dtype=np.float64)).astype(np.float32)
+    ramp = ramp / ramp.max() * 3.0                         # the largest keys are 3x
+    kc = np.zeros((B, T, H, 64), np.float32)
+    vc = np.zeros_like(kc)
+    kc[:, :n] = rng.standard_normal((B, n, H, 64), dtype=np.float32) * ramp[None, :n, None, None]
+    vc[:, :n] = rng.standard_normal((B, n, H, 64), dtype=np.float32)
+    dk, dv = rt.transfer_from_array(_to_gpu_cache(kc)), rt.transfer_from_array(_to_gpu_cache(vc))
+    qkv = rng.standard_normal((B * s, 3 * d), dtype=np.float32)
+    qkv[:, :d] *= 3.0
+    qkv[:, d:2 * d] = (qkv[:, d:2 * d].reshape(B, s, d) * ramp[None, n:, None]).reshape(B * s, d)
+    want = oracle.attention(qkv, kc, vc, B, s, n, H, mode=0)
+    got = rt.attention(rt.transfer_from_array(qkv), dk, dv, B, s, n, precision=L.PREC_BF16X3).numpy()
+    # scores reach the hundreds here, so the split-bf16 products carry an absolute error of a few 1e-4 in the
+    # exponent; the outputs are convex combinations of unit-normal V rows
+    np.testing.assert_allclose(got, want, atol=2e-3, rtol=0)
+
+
 def test_attention_golden_sdpa(rt, golden):
     g = golden["torch_ops"]
     q, k, v = g["sdpa_q"], g["sdpa_k"], g["sdpa_v"]  # [4,4,8,64]
