@@ -217,11 +217,6 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
     tc_fence_before();
     ok = __syncthreads_and(ok);  // tiles complete, staging buffers free
     if (!ok) break;
-    if (blk + 1 < nblk) {
-      prefetch(kb, j0 + AT_K, AT_OFF_SK);
-      prefetch(vb, j0 + AT_K, AT_OFF_SV);
-      cp_async_commit();
-    }
     if (warp == 0) {  // converged warp, one elected lane: the descriptors stay in uniform registers
       tc_fence_after();
       if (elect_one()) {
@@ -236,6 +231,12 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
         umma_commit(bar);
       }
       __syncwarp();
+    }
+    // the next step's rows start to arrive while the MMAs run (issued after them: the MMAs are the critical path)
+    if (blk + 1 < nblk) {
+      prefetch(kb, j0 + AT_K, AT_OFF_SK);
+      prefetch(vb, j0 + AT_K, AT_OFF_SV);
+      cp_async_commit();
     }
     wait_mma();
     tc_fence_after();
