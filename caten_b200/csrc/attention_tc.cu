@@ -81,6 +81,14 @@ __device__ __forceinline__ void st_split8(unsigned char *tile, int row_hi, int r
   *reinterpret_cast<uint4 *>(tile + sw128(row_lo, chunk)) = pack8_lo(a, b);
 }
 
+// 2^x by the special-function unit alone (what exp2f uses inside, without its scaling of results
+// below 2^-126, which flush to zero here: such probabilities do not register in a row sum >= 1/e^8)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ float4 scale4(float4 v, float c) { return make_float4(v.x * c, v.y * c, v.z * c, v.w * c); }
 
 }  // namespace
@@ -280,7 +288,7 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(const float *__
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           const float val = __uint_as_float(a[16 * c + e]);
-          p[e] = (16 * c + e <= lim) ? exp2f((val - m) * kAtInvLn2) : 0.0f;
+          p[e] = (16 * c + e <= lim) ? ex2_approx((val - m) * kAtInvLn2) : 0.0f;
           lsum += p[e];
         }
         uint32_t phi[8], plo[8];
