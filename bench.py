@@ -1,13 +1,16 @@
 """Benchmark of the GPT-2 decode path on B200 (one process per GPU).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
-                    [--workload xl-q4_0-b256|medium-q4_0-b64|small-q8_0-b1|small-f32-b1] [--precision bf16x3|bf16|fp32]
+                    [--workload xl-q4_0-b256|medium-q4_0-b64|small-q8_0-b1|small-f32-b1|xl-q4_0-b1]
+                    [--precision bf16x3|bf16|fp32] [--scaling strong|weak]
 
 A "step" is one KV-cached greedy decode step of the whole batch (one new token per sequence).
-Default workload: GPT-2 XL, Q4_0 weights, 256 sequences per GPU, 512-token prompts, fp32 KV cache.
-Sequences are independent, so they are sharded over the N GPUs with replicated weights and no
-collective on the data path; `--scaling weak` (default) keeps the workload's batch on every GPU
-(global batch = batch x N), `--scaling strong` splits one batch of that size over the GPUs.
+Default workload: GPT-2 XL, Q4_0 weights, ONE batch of 256 sequences, 512-token prompts, 256 decoded
+tokens, fp32 KV cache.  Sequences are independent, so the batch is sharded over the N GPUs (256 / N
+each) with replicated weights and no collective on the data path (`--scaling strong`, the default);
+`--scaling weak` instead keeps the workload's whole batch on every GPU (global batch = batch x N).
+The timed steps are centred on the middle of the decode phase (context = prompt + decode / 2), so
+`value` is the configuration's average step, and the CPU arm is timed at the same contexts.
 Prints ONE JSON line on rank 0.
 
 * ``value``  decode tokens/s with token ids resident in HBM (CUDA events on the library's stream,
@@ -44,6 +47,7 @@ WORKLOADS = {
     "medium-q4_0-b64": ("gpt2-medium", "q4_0", 64, 128, 128),
     "small-q8_0-b1": ("gpt2", "q8_0", 1, 128, 256),
     "small-f32-b1": ("gpt2", "f32", 1, 16, 100),
+    "xl-q4_0-b1": ("gpt2-xl", "q4_0", 1, 512, 256),   # one sequence: every linear is a dequant-GEMV
 }
 METRIC = "gpt2_decode_tokens_per_s"
 BPW = {"f32": 4.0, "q8_0": 34 / 32, "q4_0": 18 / 32}
@@ -54,7 +58,7 @@ def load_peaks():
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
     except Exception:
-        return 6650.0, "fallback (earlier measurement on this pool)"
+        return 6650.0, "fallback (no MEASURED_PEAKS.json beside bench.py)"
 
 
 class ClockSampler:
@@ -101,25 +105,43 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_decode_sample(params, sd, context: int, steps: int, threads: int, budget_s: float):
-    """Times the CPU oracle on `steps` decode steps of ONE sequence at a context of `context`
-    tokens (KV cache pre-filled with a value pattern: its contents do not change the work)."""
+def host_cores() -> int:
+    """Host threads this process may use: the affinity mask, not OMP_NUM_THREADS (which
+    `torch.distributed.run` sets to 1 for every rank)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def dequantised_state_dict(sd):
+    """fp32 copies of the packed matrices, as the reference holds its weights (oracle side only)."""
     import oracle as O
     from caten_b200 import synthetic as S
     O.build()
-    fsd = {k: (O.dequant(v.ggml_type, v.data, v.rows * v.cols).reshape(v.rows, v.cols) if isinstance(v, S.Packed) else v)
-           for k, v in sd.items()}
-    T = context + steps + 2
-    fsd["wpe.weight"] = fsd["wpe.weight"][:T] if fsd["wpe.weight"].shape[0] >= T else fsd["wpe.weight"]
-    steps = max(1, min(steps, fsd["wpe.weight"].shape[0] - context - 1))
+    return {k: (O.dequant(v.ggml_type, v.data, v.rows * v.cols).reshape(v.rows, v.cols) if isinstance(v, S.Packed) else v)
+            for k, v in sd.items()}
+
+
+def cpu_decode_sample(params, fsd, first_context: int, warmup: int, steps: int, threads: int, budget_s: float):
+    """Times the CPU oracle on `steps` decode steps of ONE sequence whose first timed step sees
+    `first_context` cached tokens (KV cache pre-filled with a value pattern: its contents do not
+    change the work), after `warmup` untimed steps."""
+    import oracle as O
+    need = first_context + steps + 2
+    wpe = fsd["wpe.weight"]
+    T = min(need, wpe.shape[0])
+    steps = max(1, min(steps, T - first_context - 1))
+    warmup = max(1, min(warmup, first_context - 1))
     O.set_threads(threads)
-    m = O.GPT2(params.n_layers, params.dim, params.n_heads, params.vocab_size, fsd["wpe.weight"].shape[0], 1, fsd)
+    m = O.GPT2(params.n_layers, params.dim, params.n_heads, params.vocab_size, T, 1, {**fsd, "wpe.weight": wpe[:T]})
     m.fill_cache(0.01)
     ids = np.zeros((1, 1), np.float32)
-    m.step(ids, context - 1, want_logits=False)  # warm the caches / page in the weights
+    for i in range(warmup):  # page in the weights, warm the caches
+        m.step(ids, first_context - warmup + i, want_logits=False)
     done, t0 = 0, time.perf_counter()
     for i in range(steps):
-        out, _ = m.step(ids, context + i, want_logits=False)
+        out, _ = m.step(ids, first_context + i, want_logits=False)
         ids = out.reshape(1, 1).astype(np.float32)
         done += 1
         if time.perf_counter() - t0 > budget_s:
@@ -128,6 +150,44 @@ def cpu_decode_sample(params, sd, context: int, steps: int, threads: int, budget
     m.close()
     O.set_threads(1)
     return done / dt, done, dt
+
+
+def oracle_parity(model, params, fsd, nb: int, precision: str, threads: int, prompt_len: int = 16, steps: int = 3):
+    """A short run of the benchmarked model object (same weights, batch, precision, kernels and
+    CUDA-graph path) against the strict-fp32 CPU oracle: the first one or two sequences are
+    compared, teacher-forced on the oracle's ids, logits within the tolerance of the precision."""
+    import oracle as O
+    from caten_b200 import synthetic as S
+    nchk = min(2, nb)
+    T = prompt_len + steps + 1
+    prompts = S.synth_prompts(nb, prompt_len, params.vocab_size, seed=7)
+    O.set_threads(threads)
+    ref = O.GPT2(params.n_layers, params.dim, params.n_heads, params.vocab_size, T, nchk, {**fsd, "wpe.weight": fsd["wpe.weight"][:T]})
+    tokens, pos = prompts.copy(), 0
+    worst_abs, worst_rel, ids_equal, ids_checked = 0.0, 0.0, 0, 0
+    for _ in range(1 + steps):
+        ids_ref, lg_ref = ref.step(tokens[:nchk, pos:], pos)
+        ids = model.forward(tokens[:, pos:], tokens.shape[1] - pos, pos)
+        lg = model.logits()[:nchk]
+        err = float(np.abs(lg - lg_ref).max())
+        worst_abs = max(worst_abs, err)
+        worst_rel = max(worst_rel, err / float(np.abs(lg_ref).max()))
+        top2 = np.sort(lg_ref, axis=1)[:, -2:]
+        decisive = (top2[:, 1] - top2[:, 0]) > 20.0 * err + 1e-6
+        ids_equal += int((ids[:nchk][decisive] == ids_ref[decisive]).sum())
+        ids_checked += int(decisive.sum())
+        nxt = ids.copy()
+        nxt[:nchk] = ids_ref          # teacher forcing on the checked sequences
+        pos = tokens.shape[1]
+        tokens = np.concatenate([tokens, nxt.reshape(-1, 1)], axis=1)
+    ref.close()
+    O.set_threads(1)
+    ok = (worst_rel <= 2e-2) if precision == "bf16" else (worst_abs <= 1e-3)
+    ok = ok and ids_equal == ids_checked
+    return {"ok": bool(ok), "against": "CPU oracle, strict fp32", "sequences": nchk, "prompt": prompt_len, "decode_steps": steps,
+            "logits_max_abs_err": worst_abs, "logits_max_rel_err": worst_rel,
+            "tolerance": "relative 2e-2" if precision == "bf16" else "max-abs 1e-3",
+            "ids_equal_where_decisive": f"{ids_equal}/{ids_checked}"}
 
 
 def main():
@@ -139,9 +199,10 @@ def main():
     ap.add_argument("--workload", default="xl-q4_0-b256", choices=sorted(WORKLOADS))
     ap.add_argument("--precision", default="bf16x3", choices=["fp32", "bf16", "bf16x3"])
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"], help="replay decode steps from a CUDA graph (auto = on; off launches kernel by kernel)")
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
-                    help="weak: the workload's batch on every GPU; strong: one batch of that size split over the GPUs")
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong"],
+                    help="strong: one batch of the workload's size split over the GPUs; weak: that batch on every GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the short oracle check of the benchmarked model")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill/GEMV/kernel-breakdown side measurements")
     args = ap.parse_args()
 
@@ -155,27 +216,34 @@ def main():
     K = args.steps if args.steps is not None else max(1, min(64, decode_len - W - 1))
     if W + K > decode_len:
         K = max(1, decode_len - W)
+    # untimed steps after the prompt that bring the cache to the middle of the decode phase
+    A = max(0, min(decode_len // 2 - K // 2 - W, decode_len - W - K))
     T = prompt_len + decode_len
+    first_timed_context = prompt_len + A + W    # tokens already cached when the first timed step starts
 
     from caten_b200 import synthetic as S
     params = S.GPT2_SIZES[model_name]
-    config = {"workload": f"{model_name} {wtype} batch {batch} prompt {prompt_len} decode", "model_dims": f"L{params.n_layers} d{params.dim} H{params.n_heads} V{params.vocab_size}",
-              "kv_cache": f"fp32 [B,H,{T},64] per layer", "weights_seed": 0, "prompt_seed": 0}
+    # identical in both arms: what is computed, not how
+    config = {"workload": f"{model_name} {wtype} batch {batch} prompt {prompt_len} decode {decode_len}",
+              "model_dims": f"L{params.n_layers} d{params.dim} H{params.n_heads} V{params.vocab_size}",
+              "kv_cache": f"fp32 [B,H,{T},64] per layer", "weights_seed": 0, "prompt_seed": 0,
+              "timed_context_tokens": [first_timed_context + 1, first_timed_context + K],
+              "l2": "inputs larger than L2: every step re-reads the KV cache and all weights"}
 
     # ------------------------------------------------------------------ reference arm (CPU)
     if args.impl == "reference":
         if rank != 0:
             return
         sd = S.synth_state_dict(params, wtype, seed=0, max_seq_len=T)
-        import oracle as O
-        threads = O.max_threads()
-        ctx_len = prompt_len + decode_len // 2
-        tps, done, dt = cpu_decode_sample(params, sd, ctx_len, K, threads, budget_s=150.0)
-        line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": done, "warmup": 1,
+        threads = host_cores()
+        fsd = dequantised_state_dict(sd)
+        tps, done, dt = cpu_decode_sample(params, fsd, first_timed_context, W, K, threads, budget_s=150.0)
+        sample = (f"{done} decode steps of 1 of the {batch} sequences at contexts {first_timed_context + 1}..{first_timed_context + done}, "
+                  f"KV cache pre-filled, {threads} threads (OpenMP over output rows and heads)")
+        line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": done, "warmup": W,
                 "ms_per_step": 1000.0 * dt / done, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
                 "data": "synthetic", "config": config,
-                "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
-                                 "sample": f"{done} decode steps of 1 sequence at context {ctx_len}, KV cache pre-filled, OpenMP over output rows"},
+                "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
                 "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
         return
@@ -256,18 +324,20 @@ def main():
     # ---- timed region 1: device-resident decode
     # graph mode: one C call per token replaying a captured CUDA graph (what a serving loop uses when
     # the per-GPU batch is small and kernel launches would otherwise pace the step); eager mode:
-    # one launch per kernel, which lets CUDA events bracket the attention kernel inside the region
+    # one launch per kernel, which lets CUDA events bracket the attention kernel inside the region.
+    # Untimed first: A steps that advance the cache to mid-decode, then W warm-up steps.
     use_graph = args.graph != "off"
-    hist = rt.open_buffer((W + K, nb), np.int64)
+    pre = A + W
+    hist = rt.open_buffer((pre + K, nb), np.int64)   # row i = ids produced by the step at position prompt_len + i
     first_dev = rt.transfer_from_array(first_ids)
     if use_graph:
-        model.decode_device_buffers(first_dev, prompt_len, max(W, 2), None)   # warm-up; also captures the graph
-        if W:
-            model.decode_device_buffers(first_dev, prompt_len, W, hist)
-        cur = hist.view((W - 1) * nb, (nb,)) if W else first_dev
+        model.decode_device_buffers(first_dev, prompt_len, 2, None)   # captures the graph
+        if pre:
+            model.decode_device_buffers(first_dev, prompt_len, pre, hist)
+        cur = hist.view((pre - 1) * nb, (nb,)) if pre else first_dev
     else:
         rt.lib.caten_b200_h2d(rt.ctx, a.ptr, first_ids.ctypes.data, first_ids.nbytes)
-        cur, nxt = run_device_steps(prompt_len, W, a, b, hist, 0)
+        cur, nxt = run_device_steps(prompt_len, pre, a, b, hist, 0)
     rt.sync(); barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     launches0 = model.launch_count
@@ -276,9 +346,9 @@ def main():
     torch.cuda.synchronize(); barrier()
     e0 = ev()
     if use_graph:
-        model.decode_device_buffers(cur, prompt_len + W, K, hist.view(W * nb, (K, nb)))
+        model.decode_device_buffers(cur, first_timed_context, K, hist.view(pre * nb, (K, nb)))
     else:
-        cur, nxt = run_device_steps(prompt_len + W, K, cur, nxt, hist, W)
+        cur, nxt = run_device_steps(first_timed_context, K, cur, nxt, hist, pre)
     e1 = ev()
     rt.sync(); torch.cuda.synchronize(); barrier()
     dec_ms = max_over_ranks(e0.elapsed_time(e1))
@@ -290,12 +360,12 @@ def main():
         # launches inside a graph cannot be bracketed: time the attention kernel in an eager replay
         # of the same steps (same inputs, same positions) right after the timed region
         rt.profile_begin(["attn_decode"])
-        model.decode_device_buffers(cur, prompt_len + W, K, None)
+        model.decode_device_buffers(cur, first_timed_context, K, None)
     prof = rt.profile_end()
 
     # roofline of the attention-decode kernel: average context over the timed steps
     attn_ms, attn_calls = prof.get("attn_decode", (0.0, 0))
-    t_mean = prompt_len + W + (K - 1) / 2.0 + 1            # keys read per step incl. the new one
+    t_mean = first_timed_context + (K - 1) / 2.0 + 1       # keys read per step incl. the new one
     attn_bytes = nb * 2 * t_mean * params.dim * 4.0        # per launch (one layer), K and V rows once
     peak, peak_src = load_peaks()
     attn_avg_s = (attn_ms / attn_calls / 1e3) if attn_calls else float("nan")
@@ -315,26 +385,26 @@ def main():
     step_bytes = p_lin * BPW[wtype] + 4 * (13 * d * Ln + 2 * d) + nb * (2 * d * 4 + Ln * 2 * t_mean * d * 4 + Ln * 2 * d * 4 + 8)
     step_frac = step_bytes / (dec_ms / K / 1e3) / 1e9 / peak
 
-    # ---- timed region 2: the public host API, host ids in / out every step
-    tok = first_ids.reshape(nb, 1)
+    # ---- timed region 2: the public host API, host ids in / out every step (same positions)
+    tok = (ids_device_path[A - 1] if A else first_ids).reshape(nb, 1)
     for i in range(W):
-        tok = model.forward(tok, 1, prompt_len + i).reshape(nb, 1)
+        tok = model.forward(tok, 1, prompt_len + A + i).reshape(nb, 1)
     rt.sync(); barrier()
     t0 = time.perf_counter()
     e2e_ids = []
     for i in range(K):
-        tok = model.forward(tok, 1, prompt_len + W + i).reshape(nb, 1)
+        tok = model.forward(tok, 1, first_timed_context + i).reshape(nb, 1)
         e2e_ids.append(tok[:, 0].copy())
     rt.sync(); barrier()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     e2e = {"value": batch * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": nb * 4 * world, "d2h_bytes_per_step": nb * 8 * world,
            "ms_per_step": 1000.0 * e2e_s / K, "timer": "host wall clock between barrier+synchronize pairs, max over ranks"}
-    same_ids = bool((np.stack(e2e_ids) == ids_device_path[W:]).all())
+    same_ids = bool((np.stack(e2e_ids) == ids_device_path[pre:]).all())
 
     # gather the generated ids on all ranks (the only collective after load)
     if world > 1:
         gathered = D.gather_ids(torch.from_numpy(ids_device_path).to(dev), batch, world)
-        assert gathered.shape == (W + K, batch)
+        assert gathered.shape == (pre + K, batch)
 
     extras = {}
     if not args.no_extras:
@@ -342,7 +412,7 @@ def main():
         rt.lib.caten_b200_h2d(rt.ctx, a.ptr, first_ids.ctypes.data, first_ids.nbytes)
         rt.sync()
         rt.profile_begin(None)
-        run_device_steps(prompt_len + W, min(K, 8), a, b)
+        run_device_steps(first_timed_context, min(K, 8), a, b)
         br = rt.profile_end()
         tot = sum(v[0] for v in br.values()) or 1.0
         extras["kernel_ms_share"] = {k: round(v[0] / tot, 4) for k, v in br.items()}
@@ -381,24 +451,29 @@ def main():
                                "note": "a 45 MB matrix can stay resident in the 126 MB L2 between launches"}
             extras["dequant_gemv"] = res
 
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        ctx_len = prompt_len + decode_len // 2
-        tps, done, dt = cpu_decode_sample(params, sd, ctx_len, 24, 1, budget_s=15.0)   # about 10-15 s of CPU work
-        cpu = {"value": tps, "unit": "tokens/s", "cores": 1, "kind": "port",
-               "sample": f"{done} decode steps of 1 sequence at context {ctx_len} (KV cache pre-filled), {dt:.1f} s; "
-                         "BACKEND=CLANG executes its kernels on one thread"}
+    # ---- outside the timed regions, rank 0: oracle check of the benchmarked model, CPU baseline
+    cpu, parity = None, None
+    need_oracle = rank == 0 and ((not args.no_parity) or (world == 1 and not args.no_cpu_baseline))
+    if need_oracle:
+        fsd = dequantised_state_dict(sd)
+        if not args.no_parity:
+            parity = oracle_parity(model, params, fsd, nb, args.precision, host_cores())
+        if world == 1 and not args.no_cpu_baseline:
+            tps, done, dt = cpu_decode_sample(params, fsd, first_timed_context, 1, 24, 1, budget_s=15.0)   # about 10-15 s of CPU work
+            cpu = {"value": tps, "unit": "tokens/s", "cores": 1, "kind": "port",
+                   "sample": f"{done} decode steps of 1 of the {batch} sequences at contexts {first_timed_context + 1}..{first_timed_context + done} "
+                             f"(KV cache pre-filled), {dt:.1f} s; BACKEND=CLANG executes its kernels on one thread"}
 
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
                 "ms_per_step": dec_ms / K, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
                 "dtype": "f32 (attention, LayerNorm, accumulation); linears " + {"fp32": "f32", "bf16": "bf16 operands", "bf16x3": "split-bf16 operands (3 products)"}[args.precision] + " on tcgen05",
-                "data": "synthetic",
-                "config": {**config, "parallelism": f"batch-sharded x{world}, weights replicated", "global_batch": batch, "local_batch": nb, "precision": args.precision,
-                           "context_tokens": [prompt_len + W + 1, prompt_len + W + K], "cuda_graph": use_graph,
-                           "l2": "inputs larger than L2: every step re-reads the whole KV cache and all weights (>= hundreds of MB)"},
+                "data": "synthetic", "config": config,
+                "run": {"parallelism": f"batch-sharded x{world}, weights replicated", "global_batch": batch, "local_batch": nb, "precision": args.precision,
+                        "cuda_graph": use_graph, "untimed_steps_before": pre},
                 "roofline": roofline, "whole_step": {"algorithmic_bytes": step_bytes, "frac_of_hbm_peak": step_frac},
                 "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+                "parity_checked": bool(parity and parity["ok"]), "parity": parity,
                 "ids_host_path_equal_device_path": same_ids, **extras}
         print(json.dumps(line))
     model.close()

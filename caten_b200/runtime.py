@@ -6,8 +6,8 @@ auto-scheduler jit-p)`` (source/codegen/backend.lisp:22-34); its buffer class an
 (source/runtime/buffer.lisp:78-89) and its runtime runs the kernels.  A Common Lisp image is not
 available where this package is developed, so the same roles are written in Python over the C
 ABI with the reference's names: :class:`B200Runtime` (context + kernel calls) and
-:class:`B200Buffer` (shape/dtype/device pointer).  The Lisp glue that binds the same C symbols
-through CFFI is listed in INTEGRATION.md.
+:class:`B200Buffer` (shape/dtype/device pointer).  The Common Lisp glue that binds the same C symbols
+through CFFI is ``lisp/b200.lisp`` at the top of this repository.
 """
 from __future__ import annotations
 

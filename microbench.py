@@ -1,11 +1,11 @@
 """Single-kernel timings through the C ABI (CUDA events on the library's stream).
 
-    python -m caten_b200.microbench attn_decode --batch 64 --heads 25 --context 700
-    python -m caten_b200.microbench attn_prefill --batch 16 --heads 25 --tokens 512 --precision bf16x3
-    python -m caten_b200.microbench gemv --model gpt2-xl --wtype q4_0
-    python -m caten_b200.microbench gemm --rows 256 --n 1600 --k 6400 --wtype q4_0 --precision bf16x3
-    python -m caten_b200.microbench relu_matmul --precision bf16x3
-    python -m caten_b200.microbench expr --elements 67108864
+    python microbench.py attn_decode --batch 64 --heads 25 --context 700
+    python microbench.py attn_prefill --batch 16 --heads 25 --tokens 512 --precision bf16x3
+    python microbench.py gemv --model gpt2-xl --wtype q4_0
+    python microbench.py gemm --rows 256 --n 1600 --k 6400 --wtype q4_0 --precision bf16x3
+    python microbench.py relu_matmul --precision bf16x3
+    python microbench.py expr --elements 67108864
 
 Each prints one JSON line.  Operands are rotated over several copies larger in total than the
 126 MB L2, so every launch streams from HBM.  Events bracket each launch (the profile API of the
@@ -19,15 +19,21 @@ import json
 
 import numpy as np
 
-from . import _lib as L
-from . import synthetic as S
-from .runtime import B200Runtime
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from caten_b200 import _lib as L  # noqa: E402
+from caten_b200 import synthetic as S  # noqa: E402
+from caten_b200.runtime import B200Runtime  # noqa: E402
 
 
 def _peak():
-    import os
     try:
-        with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")) as f:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             j = json.load(f)
             return float(j["hbm_gbs"]), float(j["bf16_tflops"])
     except Exception:
@@ -144,7 +150,7 @@ def relu_matmul(rt, a):
 def expr(rt, a):
     """Generic schedule items (`caten_b200_eval_expr`): algorithmic bytes = operand + output elements x 4."""
     import torch
-    from . import expr as E
+    from caten_b200 import expr as E
     n = a.elements
     rng = np.random.Generator(np.random.PCG64(0))
     host = rng.standard_normal(n, dtype=np.float32)

@@ -49,7 +49,9 @@ def test_weight_nbytes(lib):
     assert lib.caten_b200_weight_nbytes(2, 3, 64) == 3 * 2 * 18
     assert lib.caten_b200_weight_nbytes(8, 3, 64) == 3 * 2 * 34
     assert lib.caten_b200_weight_nbytes(2, 3, 48) == -1   # not whole blocks
-    assert lib.caten_b200_weight_nbytes(12, 3, 64) == -1  # Q4_K etc.: not covered
+    assert lib.caten_b200_weight_nbytes(12, 3, 64) == -1  # Q4_K super-blocks hold 256 weights: 64 columns are not whole blocks
+    assert lib.caten_b200_weight_nbytes(12, 3, 256) == 3 * 144
+    assert lib.caten_b200_weight_nbytes(99, 3, 256) == -1  # unknown type id
     assert lib.caten_b200_arch() == b"sm_100a"
 
 
