@@ -261,6 +261,7 @@ int caten_b200_weight_upload_device(caten_b200_ctx *ctx, int type, const void *d
     if ((e = cudaMalloc((void **)&w->d, (size_t)nblocks * 2)) != cudaSuccess) { cudaFree(w->qs); delete w; return cuda_fail(ctx, e, "cudaMalloc(weight scales)"); }
     if (int rc = launch_repack(ctx, type, (const uint8_t *)d_blocks, nblocks, w->qs, w->d)) { cudaFree(w->qs); cudaFree(w->d); delete w; return rc; }
   }
+  ctx->weights_pending = true;  // the next kernel launch must not start reading weights early
   *out = w;
   return 0;
 }
@@ -336,6 +337,7 @@ int caten_b200_linear_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, c
   if (M == 0) return 0;
   if (act < 0 || act > 2) return fail(ctx, CATEN_B200_EINVAL, "linear_noalloc: unknown activation %d", act);
   if (!aligned16(d_x) || !aligned16(d_y)) return fail(ctx, CATEN_B200_EINVAL, "linear_noalloc: x and y must be 16-byte aligned");
+  ProfScope prof(ctx, M <= 4 ? CATEN_B200_K_GEMV : CATEN_B200_K_GEMM);
   if (M <= 4) {  // the dequant-GEMV uses no scratch memory
     for (int64_t m = 0; m < M; ++m)
       if (int rc = launch_gemv(ctx, w, d_x + m * w->cols, d_bias, d_residual ? d_residual + m * w->rows : nullptr, act,

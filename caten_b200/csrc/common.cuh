@@ -93,6 +93,10 @@ struct caten_b200_ctx {
   int splitk_cluster = 0;
   int attn_tc = 1;           // prefill attention of a tensor-core model on the tensor cores (CATEN_B200_ATTN_TC=0: SIMT kernel)
   bool use_pdl = true;       // programmatic dependent launch between consecutive kernels (CATEN_B200_PDL=0 turns it off)
+  // A weight upload queued copy / re-layout kernels on the stream.  The Linear kernels read their
+  // weights BEFORE waiting for the preceding kernel (weights are assumed static), so the next launch
+  // after an upload is made as an ordinary stream-ordered launch, which completes everything before it.
+  bool weights_pending = false;
   // per-kernel-class event timing (caten_b200_profile_begin / _end)
   unsigned prof_mask = 0;
   struct ProfRec { int klass; cudaEvent_t a, b; };
@@ -178,6 +182,13 @@ int launch_relu_matmul_simt(caten_b200_ctx *ctx, const float *a, const float *b,
 int launch_relu_matmul_tc(caten_b200_ctx *ctx, const float *a, const float *b, float *c, int64_t M, int64_t K,
                           int64_t N, int nsplit);
 
+// Whether the next launch may be a programmatic dependent launch; clears the pending-upload mark.
+inline bool take_pdl(caten_b200_ctx *ctx) {
+  const bool ok = ctx->use_pdl && !ctx->weights_pending;
+  ctx->weights_pending = false;
+  return ok;
+}
+
 // Kernel launch with programmatic dependent launch allowed: the next kernel in the stream may be
 // scheduled (and run its prologue) while this one drains; every kernel launched this way calls
 // pdl_wait() before it touches memory another kernel produces or still reads.
@@ -192,7 +203,7 @@ inline cudaError_t launch_k(caten_b200_ctx *ctx, void (*kernel)(KArgs...), dim3 
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = ctx->use_pdl ? 1 : 0;
+  cfg.numAttrs = take_pdl(ctx) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 

@@ -395,6 +395,8 @@ static void expr_collapse(caten_b200_expr *c) {
       for (int i = 0; i < c->n_operands && ok; ++i) ok = c->operand_stride[i][d] == c->operand_stride[i][d + 1] * c->shape[d + 1];
       if (ok && kept) ok = c->out_stride[d] == c->out_stride[d + 1] * c->shape[d + 1];
     }
+    // the kernels index a loop with an int: never build a fused loop longer than that
+    if (ok && c->shape[d] > 1 && c->shape[d + 1] > 1 && c->shape[d] > (int64_t)INT32_MAX / c->shape[d + 1]) ok = false;
     if (!ok) { ++d; continue; }
     if (c->shape[d] == 1) {          // drop loop d
       remove_loop(d);

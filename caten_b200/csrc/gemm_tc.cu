@@ -27,6 +27,8 @@
 //
 // Every mbarrier wait is bounded; when one runs out the kernel records it in the context's
 // status word, stops issuing work, waits (bounded) for its own TMA copies, frees TMEM and returns.
+#include <atomic>
+
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -323,6 +325,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
     // a phase of a stage's `empty` barrier: with S stages at most S groups take chunks (then a
     // group's previous wait guarantees that its stage is at most one phase behind).
     const int ga = S < GROUPS ? S : GROUPS;
+    if (WT == WT_F32_T) pdl_wait();  // this "weight" is an ordinary activation: another kernel may have just written it
     WRow<WT> ring[DEPTH];
 #pragma unroll
     for (int j = 0; j < DEPTH; ++j)
@@ -616,7 +619,7 @@ static int launch_tc_t(caten_b200_ctx *ctx, const CUtensorMap &mh, const CUtenso
   cfg.stream = ctx->stream;
   cudaLaunchAttribute at[2];
   int na = 0;
-  if (ctx->use_pdl) {
+  if (take_pdl(ctx)) {
     at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;
@@ -770,15 +773,17 @@ static __device__ __align__(256) unsigned char g_fixed_scratch[FIXED_SCRATCH_BYT
 // The array's name is only a stand-in on the host; its device address is looked up once per
 // device (with that device current) and cached.
 static int fixed_scratch_ptr(caten_b200_ctx *ctx, uint8_t **out) {
-  static uint8_t *cached[64] = {nullptr};
+  static std::atomic<uint8_t *> cached[64];  // zero-initialised; host threads of different contexts may race here
   if (ctx->device < 0 || ctx->device >= 64) return fail(ctx, CATEN_B200_EUNSUPPORTED, "linear_noalloc: device index %d", ctx->device);
-  if (!cached[ctx->device]) {
+  uint8_t *have = cached[ctx->device].load(std::memory_order_acquire);
+  if (!have) {
     void *p = nullptr;
-    const cudaError_t e = cudaGetSymbolAddress(&p, g_fixed_scratch);
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_fixed_scratch);  // the same address whoever asks first
     if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaGetSymbolAddress(g_fixed_scratch)");
-    cached[ctx->device] = (uint8_t *)p;
+    have = (uint8_t *)p;
+    cached[ctx->device].store(have, std::memory_order_release);
   }
-  *out = cached[ctx->device];
+  *out = have;
   return 0;
 }
 

@@ -154,7 +154,11 @@ int caten_b200_gguf_open(const char *path, caten_b200_gguf **out) {
     t.name = c.str();
     t.n_dims = (int)c.get<uint32_t>();
     if (!c.ok || t.n_dims < 1 || t.n_dims > 4) return bad("tensor with an unsupported number of dimensions");
-    for (int k = 0; k < t.n_dims; ++k) t.dims[k] = (int64_t)c.get<uint64_t>();
+    for (int k = 0; k < t.n_dims; ++k) {
+      const uint64_t dim = c.get<uint64_t>();
+      if (dim == 0 || dim > (uint64_t)1 << 31) return bad("tensor dimension is zero or larger than 2^31");
+      t.dims[k] = (int64_t)dim;
+    }
     t.type = (int)c.get<uint32_t>();
     t.rel_offset = c.get<uint64_t>();
     if (!c.ok) return bad("truncated tensor table");
@@ -163,10 +167,13 @@ int caten_b200_gguf_open(const char *path, caten_b200_gguf **out) {
   const uint64_t table_end = (uint64_t)(c.p - g->base);
   const uint64_t data_start = (table_end + g->alignment - 1) / g->alignment * g->alignment;
   for (Tensor &t : g->tensors) {
-    int64_t rows = 1;
-    for (int k = 1; k < t.n_dims; ++k) rows *= t.dims[k];
+    int64_t rows = 1, count = 0;
+    for (int k = 1; k < t.n_dims; ++k)
+      if (__builtin_mul_overflow(rows, t.dims[k], &rows)) return bad("tensor element count overflows");
+    if (__builtin_mul_overflow(rows, t.dims[0], &count) || count > INT64_MAX / 8) return bad("tensor element count overflows");
     t.nbytes = caten_b200_weight_nbytes(t.type, rows, t.dims[0]);  // -1: a ggml type this library does not hold
-    const uint64_t off = data_start + t.rel_offset;
+    uint64_t off = 0;
+    if (__builtin_add_overflow(data_start, t.rel_offset, &off)) return bad("tensor offset overflows");
     if (t.rel_offset % g->alignment) return bad("tensor offset is not a multiple of the alignment");
     if (t.nbytes >= 0 && (off > g->size || (uint64_t)t.nbytes > g->size - off)) return bad("tensor data runs past the end of the file");
     t.data = off <= g->size ? g->base + off : nullptr;

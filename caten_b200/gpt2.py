@@ -33,9 +33,32 @@ class GPT2:
         p, rt = params, runtime
         Lr = p.n_layers
 
-        def f32(key) -> int:
+        def shape_of(key):
             a = state_dict[key]
-            if device_blobs is not None and key in device_blobs:
+            return (a.rows, a.cols) if hasattr(a, "ggml_type") and getattr(a, "ggml_type", -1) >= 0 else tuple(a.shape)
+
+        # the embedding tables are indexed by the kernels: refuse tables that do not cover what will be read
+        if shape_of("wte.weight") != (p.vocab_size, p.dim):
+            raise ValueError(f"wte.weight is {shape_of('wte.weight')}, expected {(p.vocab_size, p.dim)}")
+        if len(shape_of("wpe.weight")) != 2 or shape_of("wpe.weight")[1] != p.dim or shape_of("wpe.weight")[0] < max_seq_len:
+            raise ValueError(f"wpe.weight is {shape_of('wpe.weight')}: need at least max_seq_len={max_seq_len} rows of {p.dim}")
+
+        def f32(key) -> int:
+            """fp32 device array.  A tensor stored in a GGUF block format or as F16 (what a quantised
+            GPT-2 file holds for its embedding tables) is expanded on the device, which gives the values
+            the reference's loader computes (external/gguf/dequantize.lisp:14-53)."""
+            a = state_dict[key]
+            packed = getattr(a, "ggml_type", -1) >= 0
+            if packed or (isinstance(a, np.ndarray) and a.dtype == np.float16 and a.ndim == 2):
+                if packed and device_blobs is not None and key in device_blobs:
+                    w = rt.upload_weight_device(a.ggml_type, device_blobs[key], a.rows, a.cols)
+                else:
+                    w = rt.upload_weight(a)
+                b = rt.open_buffer((w.rows, w.cols), np.float32)
+                L.check(rt.ctx, rt.lib.caten_b200_weight_dequant(rt.ctx, w.handle, b.ptr))
+                rt.sync()
+                w.close()
+            elif device_blobs is not None and key in device_blobs:
                 b = rt.open_buffer(a.shape, np.float32)
                 L.check(rt.ctx, rt.lib.caten_b200_d2d(rt.ctx, b.ptr, device_blobs[key], b.nbytes))
             else:
@@ -202,15 +225,20 @@ def make_gpt2_from_gguf(path: str, runtime: Optional[B200Runtime] = None, max_se
     try:
         sd = gguf_to_state_dict(g)
         md = g.metadata
-        vocab, dim = sd["wte.weight"].shape
+        wte, wpe = sd["wte.weight"], sd["wpe.weight"]
+        vocab, dim = (wte.rows, wte.cols) if isinstance(wte, Packed) else wte.shape
+        wpe_rows = wpe.rows if isinstance(wpe, Packed) else wpe.shape[0]
         n_layers = int(md.get("gpt2.block_count", 1 + max(int(k.split(".")[1]) for k in sd if k.startswith("h."))))
         n_heads = int(md.get("gpt2.attention.head_count", dim // 64))
         eps = float(md.get("gpt2.attention.layer_norm_epsilon", 1e-5))
-        T = int(max_seq_len or md.get("gpt2.context_length", sd["wpe.weight"].shape[0]))
+        T = int(max_seq_len) if max_seq_len else min(int(md.get("gpt2.context_length", wpe_rows)), wpe_rows)
+        if T > wpe_rows:
+            raise ValueError(f"max_seq_len={T} exceeds the {wpe_rows} rows of the file's position table")
         if "lm_head.weight" not in sd:   # GGUF exports of GPT-2 may tie the output matrix to the embeddings
             sd["lm_head.weight"] = sd["wte.weight"]
         params = GPT2Params(n_layers, n_heads, int(dim), int(vocab), eps)
-        sd["wpe.weight"] = sd["wpe.weight"][:T]
+        if not isinstance(wpe, Packed):
+            sd["wpe.weight"] = wpe[:T]
         return GPT2(runtime or B200Runtime(0), params, sd, max_seq_len=T, batch=batch, precision=precision, **kw)
     finally:
         g.close()

@@ -12,7 +12,10 @@ oracle (source/test-suite/package.lisp:15-29 imports them through py4cl):
 * PyTorch: matmul, softmax, scaled-dot-product attention, LayerNorm and tanh-GeLU on seeded
   inputs, the comparisons of test-gemm.lisp:3-22, test-llm.lisp:6-102, test-normalization.lisp:48-55
   and test-activations.lisp:176-184; and a float64 GPT-2 forward (prefill + cached decode) of a
-  tiny random model, which pins the oracle's whole-model wiring.
+  tiny random model, which pins the oracle's whole-model wiring; and the attention block of
+  test-llm.lisp:257-301 (`attn_impl_torch`: c_attn, split into heads, softmax attention, c_proj)
+  at the reference test's own shape (10 x 3 x 32, 4 heads, no mask) and at head dim 64 with the
+  causal mask the Transformer passes (external/llm/layers.lisp:86), the shape the CUDA kernels cover.
 
 Neither PyTorch nor gguf is needed to *use* the fixtures.
 """
@@ -77,6 +80,39 @@ def torch_ops():
     np.savez_compressed(os.path.join(OUT, "torch_ops.npz"), **out)
 
 
+def attn_block():
+    """`attn_impl_torch` of source/test-suite/test-llm.lisp:273-287, restated: the projection to
+    q, k, v, per-head softmax(q.k^T / sqrt(hd)) . v with the softmax composed as in the file's
+    `softmax` helper (:9-13), heads merged, output projection."""
+    def softmax(x):
+        m = x - x.max(-1, keepdims=True)[0]
+        e = m.exp()
+        return e / e.sum(axis=-1, keepdims=True)
+
+    def block(x, n_heads, wa, ba, wp, bp, causal):
+        xqkv = torch.matmul(x, wa.T) + ba
+        B, T, _ = x.size()
+        shp = (B, T, n_heads, x.size(-1) // n_heads)
+        q, k, v = (z.reshape(shp).transpose(1, 2) for z in xqkv.chunk(3, dim=2))
+        qk = torch.matmul(q, k.transpose(-2, -1)) * (1 / np.sqrt(q.size(-1)))
+        if causal:
+            qk = qk + torch.full((T, T), float("-inf")).triu(1)
+        o = torch.matmul(softmax(qk), v).permute(0, 2, 1, 3).reshape(B, T, -1)
+        return torch.matmul(o, wp.T) + bp
+
+    g = torch.Generator().manual_seed(23)
+    out = {}
+    for tag, (B, T, d, H, causal) in (("ref", (10, 3, 32, 4, False)), ("hd64", (3, 7, 128, 2, True))):
+        x = torch.rand(B, T, d, generator=g)
+        wa, ba = torch.rand(3 * d, d, generator=g) * (2.0 / d), torch.rand(3 * d, generator=g)
+        wp, bp = torch.rand(d, d, generator=g) * (2.0 / d), torch.rand(d, generator=g)
+        if tag == "ref":   # the reference test draws everything from rand() in [0, 1)
+            wa, wp = wa * (d / 2.0), wp * (d / 2.0)
+        out.update({f"{tag}_x": x.numpy(), f"{tag}_wa": wa.numpy(), f"{tag}_ba": ba.numpy(), f"{tag}_wp": wp.numpy(),
+                    f"{tag}_bp": bp.numpy(), f"{tag}_heads": np.int64(H), f"{tag}_y": block(x, H, wa, ba, wp, bp, causal).numpy()})
+    np.savez_compressed(os.path.join(OUT, "attn_block.npz"), **out)
+
+
 def torch_gpt2_f64(sd, tokens, p, n_new):
     """float64 GPT-2 (tanh GeLU, eps 1e-5, causal mask) recomputed from scratch for every new
     token: no KV cache, so it also checks the oracle's cache protocol."""
@@ -121,7 +157,8 @@ def gpt2_tiny():
 
 
 if __name__ == "__main__":
-    gguf_fixtures()
-    torch_ops()
-    gpt2_tiny()
+    only = sys.argv[1:]
+    for fn in (gguf_fixtures, torch_ops, gpt2_tiny, attn_block):
+        if not only or fn.__name__ in only:
+            fn()
     print("wrote", sorted(f for f in os.listdir(OUT) if f.endswith(".npz")))

@@ -117,3 +117,56 @@ def test_text_in_text_out_from_one_gguf_file(rt, tmp_path):
     text = tok.decode(out[0])
     assert isinstance(text, str) and tok.decode(out[0, :len(ids)]) == "hello the"
     m.close()
+
+
+def test_gpt2_from_gguf_with_quantised_embeddings_and_tied_output(rt, oracle, tmp_path):
+    """What llama.cpp's quantiser writes for GPT-2: token_embd.weight in Q8_0, position_embd.weight in
+    F16, and no output.weight (the output matrix is the token embedding).  The reference dequantises
+    such tables at load (external/gguf/dequantize.lisp:27-53); here they are expanded on the device."""
+    from gguf import GGMLQuantizationType as GT
+    from gguf import GGUFWriter
+    from gguf.quants import dequantize
+    p = S.GPT2Params(n_layers=1, n_heads=2, dim=128, vocab_size=300)
+    T = 24
+    sd = S.synth_state_dict(p, "q8_0", seed=31, max_seq_len=T, trivial_affine=False, weight_std=0.08)
+    rng = np.random.Generator(np.random.PCG64(32))
+    wte = S._rand_packed(rng, p.vocab_size, p.dim, "q8_0", 0.08)
+    wpe16 = sd["wpe.weight"].astype(np.float16)
+    del sd["lm_head.weight"]
+    path = tmp_path / "gpt2-tied.gguf"
+    w = GGUFWriter(str(path), "gpt2")
+    w.add_uint32("gpt2.block_count", p.n_layers)
+    w.add_uint32("gpt2.embedding_length", p.dim)
+    w.add_uint32("gpt2.attention.head_count", p.n_heads)
+    w.add_uint32("gpt2.context_length", T)
+    for k, v in sd.items():
+        if k == "wte.weight":
+            w.add_tensor(gguf_name(k), wte.data.reshape(wte.rows, wte.cols // 32 * 34), raw_dtype=GT.Q8_0)
+        elif k == "wpe.weight":
+            w.add_tensor(gguf_name(k), wpe16)
+        elif isinstance(v, S.Packed):
+            w.add_tensor(gguf_name(k), v.data.reshape(v.rows, v.cols // 32 * S.BLOCK_BYTES[v.ggml_type]), raw_dtype=GT(v.ggml_type))
+        else:
+            w.add_tensor(gguf_name(k), v)
+    w.write_header_to_file(); w.write_kv_data_to_file(); w.write_tensors_to_file(); w.close()
+
+    fsd = {k: (oracle.dequant(v.ggml_type, v.data, v.rows * v.cols).reshape(v.rows, v.cols) if isinstance(v, S.Packed) else v)
+           for k, v in sd.items()}
+    fsd["wte.weight"] = dequantize(wte.data.reshape(-1, 34), GT.Q8_0).reshape(p.vocab_size, p.dim)
+    fsd["lm_head.weight"] = fsd["wte.weight"]
+    fsd["wpe.weight"] = wpe16.astype(np.float32)
+    B = 2
+    prompt = S.synth_prompts(B, 5, p.vocab_size, seed=6)
+    ref = oracle.GPT2(p.n_layers, p.dim, p.n_heads, p.vocab_size, T, B, fsd)
+    m = make_gpt2_from_gguf(str(path), runtime=rt, batch=B)
+    tokens, pos = prompt, 0
+    for _ in range(4):
+        ids_ref, lg_ref = ref.step(tokens[:, pos:], pos)
+        m.forward(tokens[:, pos:], tokens.shape[1] - pos, pos)
+        assert np.abs(m.logits() - lg_ref).max() <= 1e-3
+        pos = tokens.shape[1]
+        tokens = np.concatenate([tokens, ids_ref.reshape(-1, 1)], 1)
+    m.close(); ref.close()
+    # a position table shorter than the requested context is refused, not read past its end
+    with pytest.raises(ValueError):
+        make_gpt2_from_gguf(str(path), runtime=rt, batch=1, max_seq_len=T + 8)

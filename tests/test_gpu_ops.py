@@ -423,3 +423,42 @@ def test_gemm_split_k_cluster_reduction_matches_global_reduction(oracle, monkeyp
     for y in outs:
         assert np.abs(y - ref).max() <= 1e-4 * max(1.0, np.abs(ref).max())
     assert np.abs(outs[0] - outs[1]).max() <= 1e-5
+
+
+@pytest.mark.parametrize("prec", [L.PREC_FP32, L.PREC_BF16X3])
+def test_attention_block_golden(rt, golden, prec):
+    """The attention block of source/test-suite/test-llm.lisp:257-301 (c_attn -> heads -> softmax
+    attention -> c_proj vs `attn_impl_torch`, atol 1e-4 / rtol 1e-4) at head dim 64 with the causal
+    mask of external/llm/layers.lisp:86, through the three C-ABI calls the block lowers to."""
+    g = golden["attn_block"]
+    x, H = g["hd64_x"], int(g["hd64_heads"])
+    B, T, d = x.shape
+    wa, wp = rt.upload_weight(g["hd64_wa"]), rt.upload_weight(g["hd64_wp"])
+    ba, bp = rt.transfer_from_array(g["hd64_ba"]), rt.transfer_from_array(g["hd64_bp"])
+    qkv = rt.linear(wa, rt.transfer_from_array(x.reshape(B * T, d)), ba, precision=prec)
+    dk, dv = rt.open_buffer((B, H, T, 64)), rt.open_buffer((B, H, T, 64))
+    o = rt.attention(qkv, dk, dv, B, T, 0, precision=prec)
+    y = rt.linear(wp, o, bp, precision=prec).numpy()
+    np.testing.assert_allclose(y.reshape(B, T, d), g["hd64_y"], atol=1e-4, rtol=1e-4)
+    wa.close(); wp.close()
+
+
+def test_kv_cache_protocol(rt):
+    """source/test-suite/test-dynamic-shape.lisp:189-222: a prompt of 10 rows at start_pos 0, then one
+    row per call; after every call cache rows [0, start_pos + seq_len) are exactly the rows fed so
+    far, in order, and the rest of the cache is still zero."""
+    rng = np.random.Generator(np.random.PCG64(4))
+    B, T, H = 1, 128, 4
+    d = H * 64
+    dk, dv = rt.open_buffer((B, H, T, 64)), rt.open_buffer((B, H, T, 64))
+    fed_k, fed_v, start = [], [], 0
+    for nth in range(10):
+        s = 10 if nth == 0 else 1
+        qkv = rng.random((B * s, 3 * d), dtype=np.float32)
+        rt.attention(rt.transfer_from_array(qkv), dk, dv, B, s, start).close()
+        fed_k.append(qkv[:, d:2 * d]); fed_v.append(qkv[:, 2 * d:])
+        start += s
+        k, v = dk.numpy(), dv.numpy()   # [B, H, T, 64]
+        np.testing.assert_array_equal(k[0, :, :start].transpose(1, 0, 2).reshape(start, d), np.concatenate(fed_k))
+        np.testing.assert_array_equal(v[0, :, :start].transpose(1, 0, 2).reshape(start, d), np.concatenate(fed_v))
+        assert not k[0, :, start:].any() and not v[0, :, start:].any()

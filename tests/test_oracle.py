@@ -162,3 +162,39 @@ def test_variants_agree_to_rounding(oracle):
         lg.append(m.step(toks, 0)[1])
         m.close()
     assert np.abs(lg[0] - lg[2]).max() < 1e-4 and np.abs(lg[1] - lg[2]).max() < 1e-4
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_attention_block_vs_torch(oracle, golden, mode):
+    """source/test-suite/test-llm.lisp:257-301: c_attn -> heads -> softmax attention -> c_proj against
+    `attn_impl_torch` at the reference test's shape (10 x 3 x 32, 4 heads, no mask) and tolerance
+    (atol 1e-4, rtol 1e-4); then the same block at head dim 64 with the causal mask."""
+    g = golden["attn_block"]
+    for tag, causal in (("ref", False), ("hd64", True)):
+        x, H = g[f"{tag}_x"], int(g[f"{tag}_heads"])
+        B, T, d = x.shape
+        qkv = oracle.linear(x.reshape(B * T, d), g[f"{tag}_wa"], g[f"{tag}_ba"], mode=mode)
+        q, k, v = (qkv[:, i * d:(i + 1) * d].reshape(B, T, H, d // H).transpose(0, 2, 1, 3) for i in range(3))
+        o = _sdpa_via_oracle(oracle, q, k, v, causal, mode)
+        y = oracle.linear(o.transpose(0, 2, 1, 3).reshape(B * T, d), g[f"{tag}_wp"], g[f"{tag}_bp"], mode=mode)
+        np.testing.assert_allclose(y.reshape(B, T, d), g[f"{tag}_y"], atol=1e-4, rtol=1e-4)
+
+
+def test_kv_cache_protocol(oracle):
+    """source/test-suite/test-dynamic-shape.lisp:189-222 (`symbolic-k-cache-test`): a prompt of 10
+    rows at start_pos 0, then one row per call; after every call the cache rows [0, start_pos + seq_len)
+    are exactly the rows fed so far, in order, and the rest of the cache is still zero."""
+    rng = np.random.Generator(np.random.PCG64(4))
+    B, T, H, hd = 1, 128, 4, 4
+    d = H * hd
+    kc, vc = np.zeros((B, T, H, hd), np.float32), np.zeros((B, T, H, hd), np.float32)
+    fed_k, fed_v, start = [], [], 0
+    for nth in range(10):
+        s = 10 if nth == 0 else 1
+        qkv = rng.random((B * s, 3 * d), dtype=np.float32)
+        oracle.attention(qkv, kc, vc, B, s, start, H)
+        fed_k.append(qkv[:, d:2 * d]); fed_v.append(qkv[:, 2 * d:])
+        start += s
+        np.testing.assert_array_equal(kc[0, :start].reshape(start, d), np.concatenate(fed_k))
+        np.testing.assert_array_equal(vc[0, :start].reshape(start, d), np.concatenate(fed_v))
+        assert not kc[0, start:].any() and not vc[0, start:].any()
