@@ -93,6 +93,17 @@ def make_bpe_tokenizer(tokens: Sequence[str], merges: Sequence[str]) -> BPEToken
     return BPETokenizer(encoder, ranks)
 
 
+def make_bpe_tokenizer_from_text(tokens: str, merges: str) -> BPETokenizer:
+    """`make-bpe-tokenizer` on its own argument form (bpe.lisp:12-36): ``tokens`` is one string of
+    tokens separated by single spaces, ``merges`` one string of "left right" lines; as there, the
+    piece before the first separator of each is dropped (both files start with a separator)."""
+    tok = tokens.split(" ")[1:]
+    if tok and tok[-1].endswith("\n"):
+        tok[-1] = tok[-1].rstrip("\n")
+    lines = [" ".join(part for part in line.split(" ") if part) for line in merges.split("\n")[1:]]
+    return make_bpe_tokenizer(tok, [ln for ln in lines if ln])
+
+
 def gguf_to_bpe_tokenizer(gguf, metadata_tokens: str = "tokenizer.ggml.tokens",
                           metadata_merges: str = "tokenizer.ggml.merges") -> BPETokenizer:
     md = gguf.metadata

@@ -1,12 +1,16 @@
 """CPU tests of the BPE tokenizer against `tiktoken`, the checker the reference's own tokenizer
-test uses (source/test-suite/external/test-tokenizer.lisp:26-37).  The GPT-2 vocabulary files
-need a download, so both sides are built from one small vocabulary trained here on a fixed text."""
+test uses (source/test-suite/external/test-tokenizer.lisp:26-37): on the GPT-2 vocabulary files
+that test loads (kept compressed under tests/golden/gpt2_tokenizer/) with its three sentences, and
+on a small vocabulary trained here on a fixed text (edge cases of the merge rule)."""
 import collections
+import gzip
+import os
 
 import numpy as np
 import pytest
 
-from caten_b200.bpe import BYTE2UNICODE, PAT, UNICODE2BYTE, gguf_to_bpe_tokenizer, make_bpe_tokenizer
+from caten_b200.bpe import (BYTE2UNICODE, PAT, UNICODE2BYTE, gguf_to_bpe_tokenizer, make_bpe_tokenizer,
+                            make_bpe_tokenizer_from_text)
 
 tiktoken = pytest.importorskip("tiktoken")
 
@@ -134,3 +138,39 @@ def test_tokenizer_from_gguf_metadata(tmp_path, pair):
     with pytest.raises(KeyError):
         gguf_to_bpe_tokenizer(g)
     g.close()
+
+
+# ---- the reference's own vocabulary and sentences ---------------------------------------------------
+GPT2_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "gpt2_tokenizer")
+
+
+@pytest.fixture(scope="module")
+def gpt2_pair():
+    def read(name):
+        with gzip.open(os.path.join(GPT2_DIR, name + ".gz"), "rt", encoding="utf-8", newline="") as f:
+            return f.read()
+    mine = make_bpe_tokenizer_from_text(read("tokens.txt"), read("merges.txt"))   # make-bpe-gpt2, test-tokenizer.lisp:19-24
+    assert len(mine.encoder) == 50257 and len(mine.merges) == 50000
+    special = {"<|endoftext|>": mine.encoder["<|endoftext|>"]}
+    ranks = {bytes(UNICODE2BYTE[c] for c in t): i for t, i in mine.encoder.items() if t not in special}
+    theirs = tiktoken.Encoding("gpt2-offline", pat_str=PAT.pattern, mergeable_ranks=ranks, special_tokens=special)
+    return mine, theirs
+
+
+REFERENCE_SENTENCES = ["Say hello to me", "Hello world", "What is the answer to the life, the world, and everything?"]   # test-tokenizer.lisp:35-37
+
+
+@pytest.mark.parametrize("text", REFERENCE_SENTENCES + SENTENCES)
+def test_gpt2_vocabulary_matches_tiktoken(gpt2_pair, text):
+    mine, theirs = gpt2_pair
+    ids = mine.encode(text)
+    assert ids == theirs.encode(text)
+    assert mine.decode(ids) == theirs.decode(ids) == text
+
+
+def test_gpt2_vocabulary_known_ids(gpt2_pair):
+    """Ids of GPT-2's published vocabulary for the second reference sentence: a fixed point that does
+    not depend on tiktoken being importable in the same way elsewhere."""
+    mine, _ = gpt2_pair
+    assert mine.encode("Hello world") == [15496, 995]
+    assert mine.decode([15496, 995]) == "Hello world"

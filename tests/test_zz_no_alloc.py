@@ -19,20 +19,29 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("prec", ["bf16x3", "bf16"])
-def test_noalloc_matches_linear_on_consecutive_calls(rt, prec):
+def test_noalloc_matches_linear_on_consecutive_calls(rt, oracle, prec):
     rng = np.random.Generator(np.random.PCG64(101))
-    w = rt.upload_weight(S._rand_packed(rng, 1600, 1600, "q4_0", 0.05))   # few output tiles: split-K partials in use
-    bias = rt.transfer_from_array(rng.standard_normal(1600, dtype=np.float32) * 0.1)
+    packed = S._rand_packed(rng, 1600, 1600, "q4_0", 0.05)
+    w = rt.upload_weight(packed)   # few output tiles: split-K partials in use
+    wf = oracle.dequant(packed.ggml_type, packed.data, 1600 * 1600).reshape(1600, 1600)
+    bias_h = rng.standard_normal(1600, dtype=np.float32) * 0.1
+    bias = rt.transfer_from_array(bias_h)
     p = L.PRECISIONS[prec]
     # second call: fewer rows and another activation, so stale bytes of the first call stay in the buffer
     for M, act in ((64, L.ACT_GELU), (24, L.ACT_NONE)):
-        x = rt.transfer_from_array(rng.standard_normal((M, 1600), dtype=np.float32))
-        res = rt.transfer_from_array(rng.standard_normal((M, 1600), dtype=np.float32) * 0.1)
+        x_h = rng.standard_normal((M, 1600), dtype=np.float32)
+        res_h = rng.standard_normal((M, 1600), dtype=np.float32) * 0.1
+        x, res = rt.transfer_from_array(x_h), rt.transfer_from_array(res_h)
         want = rt.linear(w, x, bias, res, act, p).numpy()
         out = rt.open_buffer((M, 1600))
         got = rt.linear_noalloc(w, x, out, bias, res, act, p).numpy()
         rt.sync()
-        assert np.abs(got - want).max() <= 1e-4 * max(1.0, np.abs(want).max())
+        # same kernels, same tile and split-K plan, only the working memory differs: the same bits
+        np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+        # and the value itself against the CPU oracle (the reference's Linear, source/nn/linear.lisp:12-17)
+        ref = oracle.linear(x_h, wf, bias_h, res_h, act)
+        scale = max(1.0, float(np.abs(ref).max()))
+        assert np.abs(got - ref).max() <= (2e-2 if prec == "bf16" else 1e-4) * scale
     w.close()
 
 
