@@ -201,6 +201,9 @@ def main():
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"], help="replay decode steps from a CUDA graph (auto = on; off launches kernel by kernel)")
     ap.add_argument("--scaling", default="strong", choices=["weak", "strong"],
                     help="strong: one batch of the workload's size split over the GPUs; weak: that batch on every GPU")
+    ap.add_argument("--dist-plane", default="capi", choices=["capi", "torch"],
+                    help="who moves the weights and the ids between GPUs: the library's own NCCL entry points "
+                         "(caten_b200_dist_*, what a Lisp host would call) or torch.distributed")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the short oracle check of the benchmarked model")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill/GEMV/kernel-breakdown side measurements")
@@ -283,7 +286,19 @@ def main():
 
     rt = B200Runtime(local_rank)
     sd = S.synth_state_dict(params, wtype, seed=0, max_seq_len=T) if rank == 0 else None
-    if world > 1:
+    def exchange(obj):   # rank 0's small host object on every rank (control plane: the launcher's store)
+        box = [obj]
+        dist.broadcast_object_list(box, src=0)
+        return box[0]
+
+    if world > 1 and args.dist_plane == "capi":
+        D.capi_group_init(rt, rank, world, exchange)
+        arena, index = D.capi_broadcast_state_dict(rt, sd, rank, exchange)   # ncclBroadcast of the packed weights at load
+        stubs, ptrs = D.arena_views(arena.ptr, index)
+        model = GPT2(rt, params, stubs, max_seq_len=T, batch=nb, precision=args.precision, device_blobs=ptrs)
+        rt.sync()
+        arena.close()
+    elif world > 1:
         arena, index = D.broadcast_state_dict(sd, dev)   # NCCL broadcast of the packed weights at load
         stubs, ptrs = D.device_views(arena, index)
         torch.cuda.synchronize()
@@ -403,8 +418,12 @@ def main():
 
     # gather the generated ids on all ranks (the only collective after load)
     if world > 1:
-        gathered = D.gather_ids(torch.from_numpy(ids_device_path).to(dev), batch, world)
-        assert gathered.shape == (pre + K, batch)
+        if args.dist_plane == "capi":
+            gathered = D.capi_gather_ids(rt, ids_device_path, batch, world)
+        else:
+            gathered = D.gather_ids(torch.from_numpy(ids_device_path).to(dev), batch, world)
+        assert tuple(gathered.shape) == (pre + K, batch)
+        assert (np.asarray(gathered.cpu() if hasattr(gathered, "cpu") else gathered)[:, b0:b0 + nb] == ids_device_path).all()
 
     extras = {}
     if not args.no_extras:
@@ -469,7 +488,7 @@ def main():
                 "ms_per_step": dec_ms / K, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
                 "dtype": "f32 (attention, LayerNorm, accumulation); linears " + {"fp32": "f32", "bf16": "bf16 operands", "bf16x3": "split-bf16 operands (3 products)"}[args.precision] + " on tcgen05",
                 "data": "synthetic", "config": config,
-                "run": {"parallelism": f"batch-sharded x{world}, weights replicated", "global_batch": batch, "local_batch": nb, "precision": args.precision,
+                "run": {"parallelism": f"batch-sharded x{world}, weights replicated", "dist_plane": args.dist_plane if world > 1 else None, "global_batch": batch, "local_batch": nb, "precision": args.precision,
                         "cuda_graph": use_graph, "untimed_steps_before": pre},
                 "roofline": roofline, "whole_step": {"algorithmic_bytes": step_bytes, "frac_of_hbm_peak": step_frac},
                 "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,

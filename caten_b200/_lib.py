@@ -20,6 +20,7 @@ ACT_NONE, ACT_GELU, ACT_RELU = 0, 1, 2
 PREC_FP32, PREC_BF16, PREC_BF16X3 = 0, 1, 2
 K_EMBED, K_LAYERNORM, K_GEMV, K_GEMM, K_ATTN_DECODE, K_ATTN_PREFILL, K_ARGMAX, K_COUNT = 0, 1, 2, 3, 4, 5, 6, 8
 KERNEL_CLASSES = ["embed", "layernorm", "gemv", "gemm", "attn_decode", "attn_prefill", "argmax", "other"]
+DIST_ID_BYTES = 128
 PRECISIONS = {"fp32": PREC_FP32, "bf16": PREC_BF16, "bf16x3": PREC_BF16X3}
 
 
@@ -110,6 +111,14 @@ SIGNATURES = {
     "caten_b200_gpt2_logits": (_vp, [_vp]),
     "caten_b200_gpt2_kv": (C.c_int, [_vp, C.c_int, _PFP, _PFP]),
     "caten_b200_gpt2_launch_count": (_i64, [_vp]),
+    "caten_b200_dist_unique_id": (C.c_int, [_vp]),
+    "caten_b200_dist_init": (C.c_int, [_vp, C.c_int, C.c_int, _vp]),
+    "caten_b200_dist_finalize": (C.c_int, [_vp]),
+    "caten_b200_dist_rank": (C.c_int, [_vp]),
+    "caten_b200_dist_world": (C.c_int, [_vp]),
+    "caten_b200_dist_shard": (C.c_int, [_i64, C.c_int, C.c_int, C.POINTER(_i64), C.POINTER(_i64)]),
+    "caten_b200_dist_bcast_weights": (C.c_int, [_vp, _vp, C.c_size_t, C.c_int]),
+    "caten_b200_dist_gather_ids": (C.c_int, [_vp, _vp, _i64, _vp]),
     "caten_b200_profile_begin": (C.c_int, [_vp, C.c_uint]),
     "caten_b200_profile_end": (C.c_int, [_vp, _vp, _vp]),
     "caten_b200_arch": (C.c_char_p, []),

@@ -18,7 +18,7 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libcaten_b200.so")
-SOURCES = ["capi.cu", "kernels_misc.cu", "gemv.cu", "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "attention_tc.cu", "gguf.cu", "expr.cu", "dequant_extra.cu", "sample.cu"]
+SOURCES = ["capi.cu", "kernels_misc.cu", "gemv.cu", "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "attention_tc.cu", "gguf.cu", "expr.cu", "dequant_extra.cu", "sample.cu", "dist.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-fmad=false", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 
@@ -63,7 +63,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             objs.append(obj)
             with open(os.path.join(OBJ_DIR, src + ".ptxas.log"), "w") as f:
                 f.write(r.stderr)
-    link = [nvcc, "-ccbin", host, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs]
+    link = [nvcc, "-ccbin", host, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs, "-ldl"]
     r = subprocess.run(link, capture_output=True, text=True, env=env)
     if r.returncode:
         sys.stderr.write(r.stdout + r.stderr)

@@ -128,6 +128,7 @@ int caten_b200_destroy(caten_b200_ctx *ctx) {
   if (!ctx) return 0;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  caten_b200_dist_finalize(ctx);
   for (auto &r : ctx->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
   for (auto e : ctx->prof_pool) cudaEventDestroy(e);
   if (ctx->xbf.ptr) cudaFree(ctx->xbf.ptr);

@@ -97,6 +97,9 @@ struct caten_b200_ctx {
   // weights BEFORE waiting for the preceding kernel (weights are assumed static), so the next launch
   // after an upload is made as an ordinary stream-ordered launch, which completes everything before it.
   bool weights_pending = false;
+  // multi-GPU group (caten_b200_dist_init): an NCCL communicator, bound at run time
+  void *dist_comm = nullptr;
+  int dist_rank = 0, dist_world = 1;
   // per-kernel-class event timing (caten_b200_profile_begin / _end)
   unsigned prof_mask = 0;
   struct ProfRec { int klass; cudaEvent_t a, b; };

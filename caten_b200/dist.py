@@ -113,3 +113,70 @@ def gather_ids(local_ids, batch: int, world: int):
     dist.all_gather(out, pad)
     cols = [out[r][:, :shard_batch(batch, world, r)[1]] for r in range(world)]
     return torch.cat(cols, dim=1)
+
+
+# ---------------------------------------------------------------------------------------------------
+# The same two collectives through the library's own C ABI (`caten_b200_dist_*`: NCCL calls on the
+# context's stream), i.e. the path a host without torch.distributed takes.  The 128-byte group id
+# and the arena index are small host objects; how they travel between the processes is the host's
+# business (`exchange` below: any callable that returns rank 0's object on every rank).
+# ---------------------------------------------------------------------------------------------------
+def capi_group_init(rt, rank: int, world: int, exchange) -> None:
+    """Joins ``world`` processes into one group.  ``exchange(obj_or_None)`` must return, on every
+    rank, the object rank 0 passed (e.g. a broadcast over the launcher's rendezvous store)."""
+    import ctypes as C
+
+    from . import _lib as L
+    ident = None
+    if world > 1 and rank == 0:
+        buf = C.create_string_buffer(L.DIST_ID_BYTES)
+        L.check(None, rt.lib.caten_b200_dist_unique_id(buf))
+        ident = bytes(buf.raw)
+    ident = exchange(ident) if world > 1 else None
+    L.check(rt.ctx, rt.lib.caten_b200_dist_init(rt.ctx, int(rank), int(world), ident))
+
+
+def capi_broadcast_state_dict(rt, sd: Optional[dict], rank: int, exchange, src: int = 0):
+    """Rank ``src`` passes its state dict, the others None.  Returns (device arena buffer, index);
+    the arena holds every tensor's bytes and may be closed once the weights are uploaded."""
+    from . import _lib as L
+    if rank == src:
+        arena_np, index = pack_arena(sd)
+        meta = (index, int(arena_np.size))
+    else:
+        arena_np, meta = None, None
+    index, size = exchange(meta)
+    arena = rt.open_buffer((size,), np.uint8)
+    if rank == src:
+        L.check(rt.ctx, rt.lib.caten_b200_h2d(rt.ctx, arena.ptr, arena_np.ctypes.data, arena_np.nbytes))
+    L.check(rt.ctx, rt.lib.caten_b200_dist_bcast_weights(rt.ctx, arena.ptr, size, src))
+    rt.sync()
+    return arena, index
+
+
+def arena_views(arena_ptr: int, index: Dict[str, Entry]):
+    """(stub state dict, {key: device pointer}) for an arena at device address ``arena_ptr``."""
+    return {k: Stub(e) for k, e in index.items()}, {k: arena_ptr + e.offset for k, e in index.items()}
+
+
+def assemble_gathered(flat: np.ndarray, steps: int, batch: int, world: int) -> np.ndarray:
+    """``flat``: [world, steps * nb_max] as `caten_b200_dist_gather_ids` returns it (every rank's
+    [steps, nb_local] block padded to the widest slice) -> [steps, batch] in sequence order."""
+    nb_max = max(shard_batch(batch, world, r)[1] for r in range(world))
+    blocks = np.asarray(flat).reshape(world, steps, nb_max)
+    return np.concatenate([blocks[r][:, :shard_batch(batch, world, r)[1]] for r in range(world)], axis=1)
+
+
+def capi_gather_ids(rt, local_ids: np.ndarray, batch: int, world: int) -> np.ndarray:
+    """local_ids: int64 [steps, nb_local] on every rank -> [steps, batch] on every rank."""
+    from . import _lib as L
+    steps = local_ids.shape[0]
+    nb_max = max(shard_batch(batch, world, r)[1] for r in range(world))
+    pad = np.zeros((steps, nb_max), np.int64)
+    pad[:, :local_ids.shape[1]] = local_ids
+    src = rt.transfer_from_array(pad)
+    dst = rt.open_buffer((world, steps * nb_max), np.int64)
+    L.check(rt.ctx, rt.lib.caten_b200_dist_gather_ids(rt.ctx, src.ptr, steps * nb_max, dst.ptr))
+    out = assemble_gathered(dst.numpy(), steps, batch, world)
+    src.close(); dst.close()
+    return out

@@ -257,6 +257,32 @@ int caten_b200_gpt2_kv(caten_b200_gpt2 *m, int layer, float **d_k, float **d_v);
 /* Number of kernel launches issued by this model's steps since creation. */
 int64_t caten_b200_gpt2_launch_count(caten_b200_gpt2 *m);
 
+/* ---- multi-GPU plane -------------------------------------------------------------------------------
+ * No counterpart in the reference (multi-device execution is an item of its roadmap, Readme.md:181);
+ * these entries let a host that cannot use torch.distributed (Common Lisp through CFFI) run the
+ * batch-sharded configurations: one process per GPU, contiguous slices of the batch per rank,
+ * weights replicated.  Sequences never interact (external/llm/layers.lisp:35-51), so the only
+ * collectives are the two below; both are NCCL calls queued on the context's stream.  NCCL is bound
+ * at run time (dlopen of libnccl.so.2); on a host without it only world == 1 works. */
+#define CATEN_B200_DIST_ID_BYTES 128
+/* Rank 0 creates the group id (an ncclUniqueId, 128 bytes) and hands it to the other ranks by any
+ * means the host has (a file, the environment, a socket). */
+int caten_b200_dist_unique_id(void *id128);
+/* Joins the group: collective over all `world` ranks.  world == 1 needs no id and no NCCL. */
+int caten_b200_dist_init(caten_b200_ctx *ctx, int rank, int world, const void *id128);
+int caten_b200_dist_finalize(caten_b200_ctx *ctx);
+int caten_b200_dist_rank(caten_b200_ctx *ctx);
+int caten_b200_dist_world(caten_b200_ctx *ctx);
+/* Contiguous slice [*first, *first + *count) of `batch` sequences owned by `rank`; earlier ranks take
+ * the remainder. */
+int caten_b200_dist_shard(int64_t batch, int world, int rank, int64_t *first, int64_t *count);
+/* Broadcasts `bytes` bytes at d_arena (the file's tensor data / the packed weight arena) from rank
+ * `root` to every rank, in place; each rank then calls caten_b200_weight_upload_device on its copy. */
+int caten_b200_dist_bcast_weights(caten_b200_ctx *ctx, void *d_arena, size_t bytes, int root);
+/* All-gather of next-token ids: every rank contributes n_per_rank int64 (slices padded to the largest),
+ * d_all receives [world, n_per_rank] in rank order on every rank. */
+int caten_b200_dist_gather_ids(caten_b200_ctx *ctx, const int64_t *d_local, int64_t n_per_rank, int64_t *d_all);
+
 /* ---- generic schedule item ------------------------------------------------------------------------
  * One fused element-wise (optionally reducing) kernel of the scheduler, i.e. what
  * source/byoc/clang.lisp:163-205 renders as one C function from a Schedule-Item's :EXPR nodes

@@ -84,3 +84,36 @@ def test_broadcast_and_gather_world_size_2(tmp_path):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=240)
     assert r.returncode == 0, r.stdout + r.stderr
     assert r.stdout.count("-ok") == 2, r.stdout
+
+
+def test_c_abi_shard_agrees_with_host_shard():
+    """`caten_b200_dist_shard` (what a Lisp host calls) cuts the batch exactly as `shard_batch`."""
+    import ctypes as C
+
+    from caten_b200 import _lib as L
+    lib = L.load()
+    for batch in (1, 7, 64, 256):
+        for world in (1, 2, 3, 8):
+            for r in range(world):
+                first, count = C.c_int64(), C.c_int64()
+                assert lib.caten_b200_dist_shard(batch, world, r, C.byref(first), C.byref(count)) == 0
+                assert (first.value, count.value) == D.shard_batch(batch, world, r)
+    assert lib.caten_b200_dist_shard(4, 2, 2, C.byref(first), C.byref(count)) == L.EINVAL
+    # group calls without a context are refused before anything touches a GPU or NCCL
+    assert lib.caten_b200_dist_init(None, 0, 2, None) == L.EINVAL
+    assert lib.caten_b200_dist_gather_ids(None, None, 0, None) == L.EINVAL
+    assert lib.caten_b200_dist_rank(None) == -1
+
+
+def test_assemble_gathered_undoes_the_padding():
+    batch, steps = 5, 3
+    want = np.arange(steps * batch).reshape(steps, batch)
+    for world in (1, 2, 3, 5):
+        nb_max = max(D.shard_batch(batch, world, r)[1] for r in range(world))
+        flat = np.full((world, steps * nb_max), -1, np.int64)
+        for r in range(world):
+            b0, nb = D.shard_batch(batch, world, r)
+            blk = np.full((steps, nb_max), -1, np.int64)
+            blk[:, :nb] = want[:, b0:b0 + nb]
+            flat[r] = blk.reshape(-1)
+        np.testing.assert_array_equal(D.assemble_gathered(flat, steps, batch, world), want)
