@@ -1,0 +1,120 @@
+// Per-format arithmetic of one 32-wide block of a weight row against 32 activations held in
+// registers: shared by the dequant-GEMV kernel and the single-kernel decode step.
+#pragma once
+#include "common.cuh"
+
+namespace cb {
+
+// ---- per-format block arithmetic -------------------------------------------------------------
+// A thread owns one 32-wide column block kb of x and walks down the rows of W.
+//
+// Q4_0.  A nibble masked in place inside its 32-bit word, `w & (0xF << p)`, reinterpreted as a
+// float, is the (sub)normal number nibble * 2^(p-149): the binary32 encoding is linear in its
+// integer bit pattern below 2^24.  So with x pre-multiplied by 2^(64-p) (a power of two: exact),
+// one AND plus one FMA accumulates x*nibble*2^-85 exactly as an fp32 FMA of x and nibble would,
+// with no shift, integer-to-float conversion or subtraction per weight.  The "-8" offset of
+// Q4_0 is folded into the accumulator's start value -8*sum(x)*2^-85, and 2^85 into the block
+// scale.  Nibbles of the top byte (bits 24..31 overlap the exponent field) are taken from
+// w >> 8.  Valid for |x| < 2^62; FMA with subnormal operands runs at full rate.
+struct BlkQ4 {
+  static constexpr int WORDS = 4;
+  float xs[32];
+  float c0;
+  __device__ __forceinline__ void prep(const float *xv) {
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) sum += xv[j];
+    c0 = sum * -0x1p-82f;  // -8 * 2^-85
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      xs[8 * i + 0] = xv[4 * i + 0] * 0x1p64f;        // byte 0 low  nibble, p = 0
+      xs[8 * i + 1] = xv[16 + 4 * i + 0] * 0x1p60f;   // byte 0 high nibble, p = 4
+      xs[8 * i + 2] = xv[4 * i + 1] * 0x1p56f;        // byte 1 low,  p = 8
+      xs[8 * i + 3] = xv[16 + 4 * i + 1] * 0x1p52f;   // byte 1 high, p = 12
+      xs[8 * i + 4] = xv[4 * i + 2] * 0x1p48f;        // byte 2 low,  p = 16
+      xs[8 * i + 5] = xv[16 + 4 * i + 2] * 0x1p44f;   // byte 2 high, p = 20
+      xs[8 * i + 6] = xv[4 * i + 3] * 0x1p48f;        // byte 3 low  (of w >> 8), p = 16
+      xs[8 * i + 7] = xv[16 + 4 * i + 3] * 0x1p44f;   // byte 3 high (of w >> 8), p = 20
+    }
+  }
+  __device__ __forceinline__ float dot(const uint32_t *w, float scale) const {
+    float a0 = c0, a1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t q = w[i], q8 = q >> 8;
+      a0 = fmaf(xs[8 * i + 0], __uint_as_float(q & 0x0000000Fu), a0);
+      a1 = fmaf(xs[8 * i + 1], __uint_as_float(q & 0x000000F0u), a1);
+      a0 = fmaf(xs[8 * i + 2], __uint_as_float(q & 0x00000F00u), a0);
+      a1 = fmaf(xs[8 * i + 3], __uint_as_float(q & 0x0000F000u), a1);
+      a0 = fmaf(xs[8 * i + 4], __uint_as_float(q & 0x000F0000u), a0);
+      a1 = fmaf(xs[8 * i + 5], __uint_as_float(q & 0x00F00000u), a1);
+      a0 = fmaf(xs[8 * i + 6], __uint_as_float(q8 & 0x000F0000u), a0);
+      a1 = fmaf(xs[8 * i + 7], __uint_as_float(q8 & 0x00F00000u), a1);
+    }
+    return (a0 + a1) * (scale * 0x1p85f);
+  }
+};
+
+// Q8_0: sign-extended byte -> float -> FMA; (float)q * scale is exact in fp32 (8 + 11 bits), so
+// scaling the 32-term sum once per block only changes where the roundings of the sum fall.
+struct BlkQ8 {
+  static constexpr int WORDS = 8;
+  float xs[32];
+  __device__ __forceinline__ void prep(const float *xv) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) xs[j] = xv[j];
+  }
+  __device__ __forceinline__ float dot(const uint32_t *w, float scale) const {
+    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t q = w[i];
+      a0 = fmaf(xs[4 * i + 0], (float)(int8_t)(q), a0);
+      a1 = fmaf(xs[4 * i + 1], (float)(int8_t)(q >> 8), a1);
+      a0 = fmaf(xs[4 * i + 2], (float)(int8_t)(q >> 16), a0);
+      a1 = fmaf(xs[4 * i + 3], (float)(int8_t)(q >> 24), a1);
+    }
+    return (a0 + a1) * scale;
+  }
+};
+
+// fp16 weights: 32 halves = 16 words
+struct BlkF16 {
+  static constexpr int WORDS = 16;
+  float xs[32];
+  __device__ __forceinline__ void prep(const float *xv) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) xs[j] = xv[j];
+  }
+  __device__ __forceinline__ float dot(const uint32_t *w, float) const {
+    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+      a0 = fmaf(xs[2 * i], f.x, a0);
+      a1 = fmaf(xs[2 * i + 1], f.y, a1);
+    }
+    return a0 + a1;
+  }
+};
+
+// fp32 weights: 32 floats = 32 words
+struct BlkF32 {
+  static constexpr int WORDS = 32;
+  float xs[32];
+  __device__ __forceinline__ void prep(const float *xv) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) xs[j] = xv[j];
+  }
+  __device__ __forceinline__ float dot(const uint32_t *w, float) const {
+    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      a0 = fmaf(xs[2 * i], __uint_as_float(w[2 * i]), a0);
+      a1 = fmaf(xs[2 * i + 1], __uint_as_float(w[2 * i + 1]), a1);
+    }
+    return a0 + a1;
+  }
+};
+
+}  // namespace cb
