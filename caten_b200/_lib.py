@@ -10,7 +10,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libcaten_b200.so")
+# CATEN_B200_LIB: load another build of the library (e.g. one with development instrumentation)
+LIB_PATH = os.environ.get("CATEN_B200_LIB") or os.path.join(HERE, "libcaten_b200.so")
 
 OK, EINVAL, ECUDA, EUNSUPPORTED, EDEVICE = 0, 1, 2, 3, 4
 F32, F16, Q4_0, Q8_0 = 0, 1, 2, 8
@@ -19,7 +20,7 @@ BLOCK_FORMATS = (Q4_0, Q8_0, Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K)
 ACT_NONE, ACT_GELU, ACT_RELU = 0, 1, 2
 PREC_FP32, PREC_BF16, PREC_BF16X3 = 0, 1, 2
 K_EMBED, K_LAYERNORM, K_GEMV, K_GEMM, K_ATTN_DECODE, K_ATTN_PREFILL, K_ARGMAX, K_COUNT = 0, 1, 2, 3, 4, 5, 6, 8
-KERNEL_CLASSES = ["embed", "layernorm", "gemv", "gemm", "attn_decode", "attn_prefill", "argmax", "other"]
+KERNEL_CLASSES = ["embed", "layernorm", "gemv", "gemm", "attn_decode", "attn_prefill", "argmax", "decode_step"]
 DIST_ID_BYTES = 128
 PRECISIONS = {"fp32": PREC_FP32, "bf16": PREC_BF16, "bf16x3": PREC_BF16X3}
 

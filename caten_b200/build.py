@@ -1,6 +1,10 @@
 """Builds ``libcaten_b200.so`` in-tree with nvcc for sm_100a (cross-compiles without a GPU).
 
-    python -m caten_b200.build [--force] [--verbose]
+    python -m caten_b200.build [--force] [--verbose] [--timing]
+
+``--timing`` builds a second library, ``libcaten_b200_timing.so``, whose single-kernel decode step
+records per-phase timestamps of CTA 0 (``-DDS_TIMING``; read by ``microbench.py decode_step``).
+It is a development aid: load it with ``CATEN_B200_LIB=caten_b200/libcaten_b200_timing.so``.
 
 ``-fmad=false``: multiply-add contraction is off so that element-wise formulas round exactly as
 written (they restate the reference's op-by-op definitions); hot loops call fmaf() explicitly.
@@ -18,7 +22,7 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libcaten_b200.so")
-SOURCES = ["capi.cu", "kernels_misc.cu", "gemv.cu", "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "attention_tc.cu", "gguf.cu", "expr.cu", "dequant_extra.cu", "sample.cu", "dist.cu"]
+SOURCES = ["capi.cu", "decode_small.cu", "kernels_misc.cu", "gemv.cu", "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "attention_tc.cu", "gguf.cu", "expr.cu", "dequant_extra.cu", "sample.cu", "dist.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-fmad=false", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 
@@ -37,19 +41,22 @@ def _deps():
     return out
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, timing: bool = False) -> str:
+    lib = LIB.replace(".so", "_timing.so") if timing else LIB
+    obj_dir = OBJ_DIR + ("_timing" if timing else "")
+    flags = NVCC_FLAGS + (["-DDS_TIMING", "-DDS_TIMING_CTA=0"] if timing else [])
     newest = max(os.path.getmtime(p) for p in _deps())
-    if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= newest:
-        return LIB
+    if not force and os.path.exists(lib) and os.path.getmtime(lib) >= newest:
+        return lib
     nvcc = _nvcc()
-    os.makedirs(OBJ_DIR, exist_ok=True)
+    os.makedirs(obj_dir, exist_ok=True)
     env = dict(os.environ)
     # use the system host compiler even when CC/CXX point elsewhere
     host = shutil.which("g++") or "g++"
 
     def compile_one(src):
-        obj = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
-        cmd = [nvcc, "-ccbin", host, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+        obj = os.path.join(obj_dir, src.replace(".cu", ".o"))
+        cmd = [nvcc, "-ccbin", host, *flags, "-c", os.path.join(CSRC, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True, env=env)
         return src, obj, r
 
@@ -61,15 +68,15 @@ def build(force: bool = False, verbose: bool = False) -> str:
             if r.returncode:
                 raise RuntimeError(f"nvcc failed on {src}")
             objs.append(obj)
-            with open(os.path.join(OBJ_DIR, src + ".ptxas.log"), "w") as f:
+            with open(os.path.join(obj_dir, src + ".ptxas.log"), "w") as f:
                 f.write(r.stderr)
-    link = [nvcc, "-ccbin", host, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs, "-ldl"]
+    link = [nvcc, "-ccbin", host, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", lib, *objs, "-ldl"]
     r = subprocess.run(link, capture_output=True, text=True, env=env)
     if r.returncode:
         sys.stderr.write(r.stdout + r.stderr)
         raise RuntimeError("link failed")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, timing="--timing" in sys.argv))

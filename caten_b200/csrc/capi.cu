@@ -43,6 +43,7 @@ static int check_status(caten_b200_ctx *ctx) {
   if (ctx->h_status[0] != DEV_OK) {
     const int code = ctx->h_status[0], where = ctx->h_status[1], detail = ctx->h_status[2];
     ctx->h_status[0] = 0;
+    ctx->device_failures++;
     cudaMemsetAsync(ctx->d_status, 0, 4 * sizeof(int), ctx->stream);
     return fail(ctx, CATEN_B200_EDEVICE, "kernel-side check failed: code %d (%s) at site %d, detail %d", code,
                 code == DEV_WAIT_TIMEOUT ? "bounded wait ran out" : "bad index", where, detail);
@@ -259,7 +260,9 @@ int caten_b200_weight_upload_device(caten_b200_ctx *ctx, int type, const void *d
     const int64_t nblocks = rows * w->nkb;
     const size_t qbytes = (size_t)nblocks * (type == CATEN_B200_Q4_0 ? 16 : 32);
     if ((e = cudaMalloc(&w->qs, qbytes)) != cudaSuccess) { delete w; return cuda_fail(ctx, e, "cudaMalloc(weight codes)"); }
-    if ((e = cudaMalloc((void **)&w->d, (size_t)nblocks * 2)) != cudaSuccess) { cudaFree(w->qs); delete w; return cuda_fail(ctx, e, "cudaMalloc(weight scales)"); }
+    // 16 spare bytes: the single-kernel decode step fetches scales in whole 16-byte pieces
+    if ((e = cudaMalloc((void **)&w->d, (size_t)nblocks * 2 + 16)) != cudaSuccess) { cudaFree(w->qs); delete w; return cuda_fail(ctx, e, "cudaMalloc(weight scales)"); }
+    cudaMemsetAsync((uint8_t *)w->d + (size_t)nblocks * 2, 0, 16, ctx->stream);
     if (int rc = launch_repack(ctx, type, (const uint8_t *)d_blocks, nblocks, w->qs, w->d)) { cudaFree(w->qs); cudaFree(w->d); delete w; return rc; }
   }
   ctx->weights_pending = true;  // the next kernel launch must not start reading weights early
@@ -457,6 +460,10 @@ struct caten_b200_gpt2 {
   cudaGraphExec_t graph = nullptr;
   void *graph_xbf = nullptr, *graph_wtmp = nullptr;  // scratch pointers baked into the graph
   int64_t launches_per_step = 0;
+  // 1..4 sequences: the whole single-token step is one kernel (decode_small.cu); CATEN_B200_PERSISTENT=0 keeps
+  // the kernel-per-operation path
+  cb::DecodeSmall *ds = nullptr;
+  int64_t ds_failures_seen = 0;
   bool defer_reduce = true;  // CATEN_B200_DEFER_REDUCE=0 keeps a reduction kernel behind every split-K linear
 };
 
@@ -544,6 +551,14 @@ int caten_b200_gpt2_create(caten_b200_ctx *ctx, const caten_b200_gpt2_desc *dsc,
   if (!rc && cudaMallocHost(&m->h_pos_pinned, sizeof(int)) != cudaSuccess) rc = fail(ctx, CATEN_B200_ECUDA, "cudaMallocHost(pos)");
   if (!rc && cudaMallocHost(&m->h_ids_pinned, (size_t)B * T * sizeof(float)) != cudaSuccess) rc = fail(ctx, CATEN_B200_ECUDA, "cudaMallocHost(ids)");
   if (!rc && cudaMallocHost(&m->h_out_pinned, (size_t)B * sizeof(int64_t)) != cudaSuccess) rc = fail(ctx, CATEN_B200_ECUDA, "cudaMallocHost(out ids)");
+  bool persistent = true;
+  if (const char *e = getenv("CATEN_B200_PERSISTENT")) persistent = atoi(e) != 0;
+  if (!rc && persistent && cb::decode_small_supported(m->desc, m->attn_w.data(), m->proj_w.data(), m->fc_w.data(), m->mproj_w.data())) {
+    const std::vector<const float *> vecs[8] = {m->ln1_g, m->ln1_b, m->attn_b, m->proj_b, m->ln2_g, m->ln2_b, m->fc_b, m->mproj_b};
+    rc = cb::decode_small_create(ctx, m->desc, m->attn_w, m->proj_w, m->fc_w, m->mproj_w, vecs, m->kc, m->vc, m->ids_io, m->out_ids,
+                                 m->ids_hist, m->d_pos, m->logits, &m->ds);
+    m->ds_failures_seen = ctx->device_failures;
+  }
   if (rc) { caten_b200_gpt2_destroy(m); return rc; }
   m->launches0 = ctx->launches;
   *out = m;
@@ -560,6 +575,7 @@ int caten_b200_gpt2_destroy(caten_b200_gpt2 *m) {
   float *bufs[] = {m->h, m->h2, m->xn, m->qkv, m->att, m->ff, m->last, m->logits, m->ids_f32};
   for (float *p : bufs) if (p) cudaFree(p);
   if (m->graph) cudaGraphExecDestroy(m->graph);
+  cb::decode_small_destroy(m->ds);
   if (m->bf_arena) cudaFree(m->bf_arena);
   if (m->out_ids) cudaFree(m->out_ids);
   if (m->ids_io) cudaFree(m->ids_io);
@@ -620,6 +636,8 @@ static int run_chunk(caten_b200_gpt2 *m, const float *ids_f32, const int64_t *id
   return layernorm(pend_h, m->h2, m->h, c.lnf_g, c.lnf_b, m->last + b0 * d, nb, s, lb);
 }
 
+static int decode_step_device_pos(caten_b200_gpt2 *m, int64_t n_host);
+
 int caten_b200_gpt2_step_device(caten_b200_gpt2 *m, const float *d_ids_f32, const int64_t *d_ids_i64, int64_t s, int64_t n,
                                 int64_t *d_out_ids) {
   if (!m) return fail(nullptr, CATEN_B200_EINVAL, "gpt2_step: model is NULL");
@@ -631,6 +649,14 @@ int caten_b200_gpt2_step_device(caten_b200_gpt2 *m, const float *d_ids_f32, cons
   if (s < 1 || n < 0 || n + s > c.max_seq_len)
     return fail(ctx, CATEN_B200_EINVAL, "gpt2_step: s=%lld n=%lld outside the cache (max_seq_len=%d)", (long long)s, (long long)n, c.max_seq_len);
   const int64_t B = c.batch;
+  if (s == 1 && m->ds) {
+    // single-token step of a few sequences: the one-kernel path, fed from the device-side state
+    if (int rc = launch_begin_steps(ctx, d_ids_f32, d_ids_i64, m->ids_io, m->d_pos, n, B)) return rc;
+    if (int rc = decode_step_device_pos(m, n)) return rc;
+    if (d_out_ids != m->out_ids)
+      CB_CUDA(ctx, cudaMemcpyAsync(d_out_ids, m->out_ids, (size_t)B * sizeof(int64_t), cudaMemcpyDeviceToDevice, ctx->stream));
+    return 0;
+  }
   int64_t per = m->max_rows / s;
   if (per < 1) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gpt2_step: s=%lld exceeds max_rows=%lld", (long long)s, (long long)m->max_rows);
   if (per > B) per = B;
@@ -676,6 +702,14 @@ int caten_b200_gpt2_step(caten_b200_gpt2 *m, const float *h_ids_f32, int64_t s, 
 static int decode_step_device_pos(caten_b200_gpt2 *m, int64_t n_host) {
   caten_b200_ctx *ctx = m->ctx;
   const caten_b200_gpt2_desc &c = m->desc;
+  if (m->ds) {
+    if (m->ds_failures_seen != ctx->device_failures) {   // an interrupted step left half-written exchange words
+      if (int rc = cb::decode_small_reset(ctx, m->ds)) return rc;
+      m->ds_failures_seen = ctx->device_failures;
+    }
+    ProfScope prof(ctx, CATEN_B200_K_DECODE_STEP);
+    return cb::decode_small_launch(ctx, m->ds);
+  }
   if (int rc = run_chunk(m, nullptr, m->ids_io, 0, c.batch, 1, n_host, m->d_pos)) return rc;
   if (int rc = model_linear(m, c.lm_head, m->last, m->last_bf, nullptr, nullptr, CATEN_B200_ACT_NONE, m->logits, cb::BfOut(), c.batch)) return rc;
   if (int rc = launch_argmax(ctx, m->logits, c.batch, c.vocab, m->out_ids)) return rc;
@@ -688,7 +722,8 @@ static int decode_run(caten_b200_gpt2 *m, int64_t n, int64_t steps) {
   caten_b200_ctx *ctx = m->ctx;
   const int64_t T = m->desc.max_seq_len;
   int64_t done = 0;
-  const bool use_graph = ctx->prof_mask == 0;  // event brackets cannot be placed inside a graph
+  // event brackets cannot be placed inside a graph; a step that is one kernel already gains nothing from one
+  const bool use_graph = ctx->prof_mask == 0 && !m->ds;
   if (use_graph && m->graph && (m->graph_xbf != ctx->xbf.ptr || m->graph_wtmp != ctx->wtmp.ptr)) {
     cudaGraphExecDestroy(m->graph);  // scratch was re-allocated since the capture: its pointers are stale
     m->graph = nullptr;

@@ -86,6 +86,7 @@ struct caten_b200_ctx {
   cb::Scratch wtmp;          // split-K partial tiles of the tensor-core GEMM
   void *encode_tiled = nullptr;  // cuTensorMapEncodeTiled, resolved at init
   int64_t launches = 0;
+  int64_t device_failures = 0;   // kernel-side check failures reported so far
   // split-K partial tiles: reduced by a second kernel through global scratch (default: it overlaps
   // with its neighbours under programmatic dependent launch and measured faster), or inside a
   // thread-block cluster through distributed shared memory (CATEN_B200_SPLITK_CLUSTER=1: every split-K
@@ -191,6 +192,21 @@ inline bool take_pdl(caten_b200_ctx *ctx) {
   ctx->weights_pending = false;
   return ok;
 }
+
+// Single-kernel decode step for 1..4 sequences (decode_small.cu)
+struct DecodeSmall;
+bool decode_small_supported(const caten_b200_gpt2_desc &c, const caten_b200_weight *const *attn, const caten_b200_weight *const *proj,
+                            const caten_b200_weight *const *fc, const caten_b200_weight *const *mproj);
+// vecs: eight per-layer tables in the order ln1_g, ln1_b, attn_b, proj_b, ln2_g, ln2_b, fc_b, mproj_b
+int decode_small_create(caten_b200_ctx *ctx, const caten_b200_gpt2_desc &c, const std::vector<const caten_b200_weight *> &attn,
+                        const std::vector<const caten_b200_weight *> &proj, const std::vector<const caten_b200_weight *> &fc,
+                        const std::vector<const caten_b200_weight *> &mproj, const std::vector<const float *> *vecs,
+                        const std::vector<float *> &kc, const std::vector<float *> &vc, int64_t *ids_io, int64_t *out_ids, int64_t *hist,
+                        int *d_pos, float *logits, DecodeSmall **out);
+void decode_small_destroy(DecodeSmall *s);
+int decode_small_launch(caten_b200_ctx *ctx, DecodeSmall *s);
+// after a kernel-side failure the exchange words of the interrupted step are stale: forget them
+int decode_small_reset(caten_b200_ctx *ctx, DecodeSmall *s);
 
 // Kernel launch with programmatic dependent launch allowed: the next kernel in the stream may be
 // scheduled (and run its prologue) while this one drains; every kernel launched this way calls

@@ -53,6 +53,12 @@ struct BlkQ4 {
     }
     return (a0 + a1) * (scale * 0x1p85f);
   }
+  // the block read from (shared) memory
+  __device__ __forceinline__ float dotp(const uint4 *src, float scale) const {
+    const uint4 v = src[0];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    return dot(w, scale);
+  }
 };
 
 // Q8_0: sign-extended byte -> float -> FMA; (float)q * scale is exact in fp32 (8 + 11 bits), so
@@ -76,6 +82,11 @@ struct BlkQ8 {
     }
     return (a0 + a1) * scale;
   }
+  __device__ __forceinline__ float dotp(const uint4 *src, float scale) const {
+    const uint4 u = src[0], v = src[1];
+    const uint32_t w[8] = {u.x, u.y, u.z, u.w, v.x, v.y, v.z, v.w};
+    return dot(w, scale);
+  }
 };
 
 // fp16 weights: 32 halves = 16 words
@@ -96,6 +107,21 @@ struct BlkF16 {
     }
     return a0 + a1;
   }
+  __device__ __forceinline__ float dotp(const uint4 *src, float) const {
+    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {   // one 16-byte piece (8 halves) at a time
+      const uint4 v = src[q];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+        a0 = fmaf(xs[8 * q + 2 * i], f.x, a0);
+        a1 = fmaf(xs[8 * q + 2 * i + 1], f.y, a1);
+      }
+    }
+    return a0 + a1;
+  }
 };
 
 // fp32 weights: 32 floats = 32 words
@@ -112,6 +138,18 @@ struct BlkF32 {
     for (int i = 0; i < 16; ++i) {
       a0 = fmaf(xs[2 * i], __uint_as_float(w[2 * i]), a0);
       a1 = fmaf(xs[2 * i + 1], __uint_as_float(w[2 * i + 1]), a1);
+    }
+    return a0 + a1;
+  }
+  __device__ __forceinline__ float dotp(const uint4 *src, float) const {
+    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {   // one 16-byte piece (4 floats) at a time
+      const float4 v = reinterpret_cast<const float4 *>(src)[q];
+      a0 = fmaf(xs[4 * q], v.x, a0);
+      a1 = fmaf(xs[4 * q + 1], v.y, a1);
+      a0 = fmaf(xs[4 * q + 2], v.z, a0);
+      a1 = fmaf(xs[4 * q + 3], v.w, a1);
     }
     return a0 + a1;
   }

@@ -345,7 +345,9 @@ int caten_b200_eval_expr(caten_b200_ctx *ctx, const caten_b200_expr *e);
  * bracketed with CUDA events on the context's stream, so asynchronous execution is kept. */
 enum {
   CATEN_B200_K_EMBED = 0, CATEN_B200_K_LAYERNORM = 1, CATEN_B200_K_GEMV = 2, CATEN_B200_K_GEMM = 3,
-  CATEN_B200_K_ATTN_DECODE = 4, CATEN_B200_K_ATTN_PREFILL = 5, CATEN_B200_K_ARGMAX = 6, CATEN_B200_K_COUNT = 8
+  CATEN_B200_K_ATTN_DECODE = 4, CATEN_B200_K_ATTN_PREFILL = 5, CATEN_B200_K_ARGMAX = 6,
+  CATEN_B200_K_DECODE_STEP = 7,   /* the whole single-token step of 1..4 sequences, which is one kernel */
+  CATEN_B200_K_COUNT = 8
 };
 /* Starts timing the classes whose bit (1 << class) is set in class_mask. */
 int caten_b200_profile_begin(caten_b200_ctx *ctx, unsigned class_mask);

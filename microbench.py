@@ -6,6 +6,7 @@
     python microbench.py gemm --rows 256 --n 1600 --k 6400 --wtype q4_0 --precision bf16x3
     python microbench.py relu_matmul --precision bf16x3
     python microbench.py expr --elements 67108864
+    python microbench.py decode_step --model gpt2-xl --wtype q4_0 --context 640 [--batch 1]
 
 Each prints one JSON line.  Operands are rotated over several copies larger in total than the
 126 MB L2, so every launch streams from HBM.  Events bracket each launch (the profile API of the
@@ -184,9 +185,52 @@ def expr(rt, a):
     return {"kernel": "expr_kernel", "elements": n, "cases": out}
 
 
+def decode_step(rt, a):
+    """The single-kernel decode step (1..4 sequences): time per step from the library's per-class events and, when the
+    loaded library is the timing build (`python -m caten_b200.build --timing`, CATEN_B200_LIB=...), the time CTA 0 spends
+    in every phase of a Transformer block, averaged over the layers of the last step."""
+    import ctypes as C
+    from caten_b200.gpt2 import GPT2
+    p = S.GPT2_SIZES[a.model]
+    B = min(a.batch, 4)
+    T = a.context + 40
+    sd = S.synth_state_dict(p, a.wtype, seed=0, max_seq_len=T)
+    m = GPT2(rt, p, sd, max_seq_len=T, batch=B)
+    prompt = S.synth_prompts(B, a.context, p.vocab_size, seed=0)
+    first = m.forward(prompt, a.context, 0)
+    m.decode_device(first, a.context, 4)
+    rt.profile_begin(["decode_step"])
+    m.decode_device(first, a.context, a.iters if a.iters <= 32 else 32)
+    prof = rt.profile_end()
+    ms, calls = prof.get("decode_step", (0.0, 0))
+    d, Ln, V = p.dim, p.n_layers, p.vocab_size
+    bpw = {"f32": 4.0, "q8_0": 34 / 32, "q4_0": 18 / 32}[a.wtype]
+    nbytes = (12 * d * d * Ln + V * d) * bpw + 4 * (13 * d * Ln + 2 * d) + B * (2 * d * 4 + Ln * 2 * (a.context + 1) * d * 4 + Ln * 2 * d * 4 + 8)
+    hbm, _ = _peak()
+    out = {"kernel": "decode_small_kernel", "model": a.model, "wtype": a.wtype, "batch": B, "context": a.context + 1,
+           "us_per_step": 1e3 * ms / calls if calls else None, "algorithmic_bytes": nbytes,
+           "frac_of_measured_hbm": (nbytes / (ms / calls / 1e3) / 1e9 / hbm) if calls else None}
+    lib = L.load()
+    if hasattr(lib, "cb_debug_ds_times"):
+        names = ["P1 poll h", "P1 ln_1", "P1 c_attn", "P2 attention chunk", "P3 combine", "P4 poll att", "-", "P4 attn.c_proj",
+                 "P5 poll h2", "P5 ln_2", "P5 c_fc+gelu", "P6 poll ff", "-", "P6 mlp.c_proj"]
+        n = 1 + Ln * len(names) + 3
+        buf = (C.c_ulonglong * n)()
+        lib.cb_debug_ds_times.argtypes = [C.c_void_p, C.c_int]
+        lib.cb_debug_ds_times(buf, n)
+        t = np.array(list(buf), dtype=np.float64)
+        per = np.diff(t[:1 + Ln * len(names)]).reshape(Ln, len(names)) / 1e3
+        out["phase_us_mean_over_layers_cta0"] = {nm: round(float(per[:, i].mean()), 2) for i, nm in enumerate(names) if nm != "-"}
+        k = Ln * len(names)
+        out["head_us"] = {"poll h": (t[k + 1] - t[k]) / 1e3, "ln_f": (t[k + 2] - t[k + 1]) / 1e3, "lm_head + arg-max candidates": (t[k + 3] - t[k + 2]) / 1e3}
+        out["step_us_cta0"] = (t[k + 3] - t[0]) / 1e3
+    m.close()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "gemv", "gemm", "relu_matmul", "expr"])
+    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "gemv", "gemm", "relu_matmul", "expr", "decode_step"])
     ap.add_argument("--elements", type=int, default=1 << 26)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--heads", type=int, default=25)
@@ -202,7 +246,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
     with B200Runtime(0) as rt:
-        print(json.dumps({"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemv": gemv, "gemm": gemm, "relu_matmul": relu_matmul, "expr": expr}[a.what](rt, a)))
+        print(json.dumps({"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemv": gemv, "gemm": gemm, "relu_matmul": relu_matmul, "expr": expr,
+                          "decode_step": decode_step}[a.what](rt, a)))
 
 
 if __name__ == "__main__":

@@ -137,10 +137,13 @@ def test_graph_replayed_decode_is_repeatable(rt, precision, batch):
     np.testing.assert_array_equal(first, want[:, 0])
     a = m.decode_device(first, 5, 11)          # eager first step + capture + replays
     b = m.decode_device(first, 5, 11)          # replays only
-    rt.profile_begin(["attn_decode"])
+    rt.profile_begin(["attn_decode", "decode_step"])
     c = m.decode_device(first, 5, 4)           # eager launches while timing is on
     prof = rt.profile_end()
-    assert prof["attn_decode"][1] == 4 * TINY.n_layers
+    if batch <= 4:   # a few sequences: the whole step is one kernel, timed as such
+        assert prof["decode_step"][1] == 4 and "attn_decode" not in prof
+    else:
+        assert prof["attn_decode"][1] == 4 * TINY.n_layers
     np.testing.assert_array_equal(a, want[:, 1:])
     np.testing.assert_array_equal(b, a)
     np.testing.assert_array_equal(c, a[:, :4])
@@ -239,3 +242,53 @@ def test_closing_after_the_runtime_is_gone_is_harmless():
     buf.close()
     g.close()
     del g
+
+
+@pytest.mark.parametrize("wtype,batch,params,head", [("q4_0", 1, TINY, None), ("q8_0", 3, TINY, None), ("q4_0", 4, WIDE, None),
+                                                     ("q8_0", 2, TINY, np.float32), ("q4_0", 1, WIDE, np.float16)])
+def test_single_kernel_decode_step_matches_kernel_per_operation_path(rt, oracle, monkeypatch, wtype, batch, params, head):
+    """With 1..4 sequences and block-quantised layers a single-token step is one kernel (weights streamed through shared memory,
+    activations exchanged as tagged words); CATEN_B200_PERSISTENT=0 keeps the kernel-per-operation
+    path.  Same inputs through both: logits within 1e-4, ids equal where the top-2 gap is decisive,
+    identical KV cache rows, and the strict-fp32 oracle within 1e-3 (the bar of every fp32 path)."""
+    T = 160
+    sd = S.synth_state_dict(params, wtype, seed=13, max_seq_len=T, trivial_affine=False, weight_std=0.08)
+    fsd = {k: (oracle.dequant(v.ggml_type, v.data, v.rows * v.cols).reshape(v.rows, v.cols) if isinstance(v, S.Packed) else v)
+           for k, v in sd.items()}
+    if head is not None:   # a dense output matrix (fp32 or fp16) behind quantised layers, as some GGUF files have
+        sd["lm_head.weight"] = fsd["lm_head.weight"].astype(head)
+        fsd["lm_head.weight"] = sd["lm_head.weight"].astype(np.float32)
+    prompt = S.synth_prompts(batch, 70, params.vocab_size, seed=3)   # long enough for several context chunks per head
+    monkeypatch.setenv("CATEN_B200_PERSISTENT", "0")
+    old = GPT2(rt, params, sd, max_seq_len=T, batch=batch)
+    monkeypatch.setenv("CATEN_B200_PERSISTENT", "1")
+    new = GPT2(rt, params, sd, max_seq_len=T, batch=batch)
+    ref = oracle.GPT2(params.n_layers, params.dim, params.n_heads, params.vocab_size, T, batch, fsd)
+    ids_ref, _ = ref.step(prompt, 0)
+    assert (old.forward(prompt, 70, 0) == new.forward(prompt, 70, 0)).all()   # the prompt runs the same kernels in both
+    tok, pos = ids_ref.reshape(-1, 1), 70
+    for step in range(12):
+        ids_ref, lg_ref = ref.step(tok, pos)
+        ia, ib = old.forward(tok, 1, pos), new.forward(tok, 1, pos)
+        la, lb = old.logits(), new.logits()
+        err = float(np.abs(la - lb).max())
+        assert err <= 1e-4, (step, err)
+        assert np.abs(lb - lg_ref).max() <= 1e-3
+        top2 = np.sort(lg_ref, axis=1)[:, -2:]
+        ok = (top2[:, 1] - top2[:, 0]) > 1e-3
+        np.testing.assert_array_equal(ib[ok], ids_ref[ok])
+        np.testing.assert_array_equal(ib[ok], ia[ok])
+        tok, pos = ids_ref.reshape(-1, 1), pos + 1
+    for layer in (0, params.n_layers - 1):
+        (ka, va), (kb, vb) = old.kv_cache(layer), new.kv_cache(layer)
+        np.testing.assert_allclose(kb[:, :, :pos], ka[:, :, :pos], atol=1e-4, rtol=0)
+        np.testing.assert_allclose(vb[:, :, :pos], va[:, :, :pos], atol=1e-4, rtol=0)
+        assert not kb[:, :, pos:].any() and not vb[:, :, pos:].any()
+    # device-resident decode (ids and position never leave the GPU) gives the host loop's ids
+    first = new.forward(prompt, 70, 0)
+    want = [first]
+    for i in range(5):
+        want.append(new.forward(want[-1].reshape(-1, 1), 1, 70 + i))
+    got = new.decode_device(first, 70, 5)
+    np.testing.assert_array_equal(got, np.stack(want[1:], axis=1))
+    old.close(); new.close(); ref.close()
