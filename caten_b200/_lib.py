@@ -103,6 +103,8 @@ SIGNATURES = {
     "caten_b200_attention": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64]),
     "caten_b200_attention_ex": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, C.c_int]),
     "caten_b200_argmax": (C.c_int, [_vp, _vp, _i64, _i64, _vp]),
+    "caten_b200_rmsnorm": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, C.c_float]),
+    "caten_b200_rope": (C.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, C.c_float, _i64]),
     "caten_b200_sample": (C.c_int, [_vp, _vp, _i64, _i64, C.c_float, C.c_int, _vp, _vp]),
     "caten_b200_gpt2_create": (C.c_int, [_vp, C.POINTER(GPT2Desc), _PFP]),
     "caten_b200_gpt2_destroy": (C.c_int, [_vp]),

@@ -200,6 +200,21 @@ class B200Runtime:
         L.check(self.ctx, self.lib.caten_b200_layernorm(self.ctx, x.ptr, gamma.ptr, beta.ptr, y.ptr, rows, d, eps))
         return y
 
+    def rmsnorm(self, x: B200Buffer, weight: Optional[B200Buffer] = None, eps: float = 1e-5) -> B200Buffer:
+        """`!rms-norm` (source/nn/normalization.lisp:70-85) over the last axis."""
+        d = x.shape[-1]
+        rows = int(np.prod(x.shape[:-1], dtype=np.int64))
+        y = self.open_buffer(x.shape, np.float32)
+        L.check(self.ctx, self.lib.caten_b200_rmsnorm(self.ctx, x.ptr, weight.ptr if weight else None, y.ptr, rows, d, eps))
+        return y
+
+    def rope(self, x: B200Buffer, base: float = 10000.0, pos0: int = 0) -> B200Buffer:
+        """`!rope` (source/nn/positional-encoding.lisp:3-56) on x [B, S, H, head_dim]."""
+        B, S_, H, hd = x.shape
+        y = self.open_buffer(x.shape, np.float32)
+        L.check(self.ctx, self.lib.caten_b200_rope(self.ctx, x.ptr, y.ptr, B, S_, H, hd, float(base), int(pos0)))
+        return y
+
     def embed(self, ids: B200Buffer, wte: B200Buffer, wpe: B200Buffer, n: int) -> B200Buffer:
         B, s = ids.shape
         V, d = wte.shape

@@ -210,6 +210,17 @@ int caten_b200_argmax(caten_b200_ctx *ctx, const float *d_x, int64_t rows, int64
 int caten_b200_sample(caten_b200_ctx *ctx, const float *d_logits, int64_t rows, int64_t V, float temperature,
                       int top_k, const float *d_uniform, int64_t *d_out);
 
+/* RMSNorm over the last axis (source/nn/normalization.lisp:70-85):
+ *   y = x * (1 / sqrt(eps + mean(x * x))) [* weight]; d_weight [d] or NULL.  x, y [rows, d]; d % 4 == 0, d <= 8192. */
+int caten_b200_rmsnorm(caten_b200_ctx *ctx, const float *d_x, const float *d_weight, float *d_y, int64_t rows,
+                       int64_t d, float eps);
+/* Rotary positional encoding (source/nn/positional-encoding.lisp:3-56, `(!rope x dim)` with dim = head_dim / 2):
+ * x, y [B, S, H, head_dim]; the pair (x[2i], x[2i+1]) is rotated by (pos0 + s) * base^(-2i / head_dim); an odd last
+ * element is copied.  The reference counts positions from 0 (pos0 = 0); pos0 > 0 serves a step that continues a
+ * KV-cached sequence.  In place (d_y == d_x) is allowed. */
+int caten_b200_rope(caten_b200_ctx *ctx, const float *d_x, float *d_y, int64_t B, int64_t S, int64_t H,
+                    int64_t head_dim, float base, int64_t pos0);
+
 /* ---- whole GPT-2 step ---------------------------------------------------------------------------
  * Replaces one `(forward runtime (x . tokens) (s . len) (n . start-pos))` of
  * apps/gpt2/gpt2.lisp:104 on the GraphRuntime built by make-gpt2 (gpt2.lisp:82-93): the whole

@@ -318,7 +318,7 @@ source/codegen/jit.lisp:118-120)."))
 (defun item-op-types (si) (map 'list #'node-type (getattr si :items)))
 
 (defun classify-item (si)
-  "-> one of :embedding :layernorm :linear :relu-matmul :argmax :expr.
+  "-> one of :embedding :layernorm :rmsnorm :linear :relu-matmul :argmax :expr.
 The four Linear-shaped kernels of a GPT-2 block, with what the scheduler fuses into them
 (source/test-suite/test-schedule.lisp:72-74,128-130):
   c_attn          MATMUL + LINEAR(bias)
@@ -329,6 +329,7 @@ The four Linear-shaped kernels of a GPT-2 block, with what the scheduler fuses i
   (cond
     ((item-has si "GRAPH/EMBEDDING") :embedding)
     ((item-has si "GRAPH/LAYERNORM") :layernorm)
+    ((item-has si "GRAPH/RMSNORM") :rmsnorm)   ; one kernel in the reference too (test-schedule.lisp:164-166)
     ((item-has si "GRAPH/ARGMAXNODE") :argmax)
     ((and (item-has si "GRAPH/MATMUL" "GRAPH/LINEAR")
           (find :WMMA (item-op-types si)))
@@ -375,6 +376,19 @@ The four Linear-shaped kernels of a GPT-2 block, with what the scheduler fuses i
   (check (foreign-funcall "caten_b200_layernorm" :pointer *ctx* :pointer (buffer-value x) :pointer (buffer-value gamma)
                           :pointer (buffer-value beta) :pointer (buffer-value out)
                           :int64 (rows-of x) :int64 (car (last (buffer-shape x))) :float eps :int)))
+
+(defun call-rmsnorm (out x weight eps)
+  "`!rms-norm` (source/nn/normalization.lisp:70-85); weight may be nil."
+  (check (foreign-funcall "caten_b200_rmsnorm" :pointer *ctx* :pointer (buffer-value x)
+                          :pointer (if weight (buffer-value weight) (null-pointer)) :pointer (buffer-value out)
+                          :int64 (rows-of x) :int64 (car (last (buffer-shape x))) :float eps :int)))
+
+(defun call-rope (out x base pos0)
+  "`!rope` (source/nn/positional-encoding.lisp:3-56) on x [B S H head-dim]; for hosts that call it as one module-level
+operation (the scheduler splits the reference's own lowering into several element-wise items, which run through call-expr)."
+  (destructuring-bind (b s h hd) (buffer-shape x)
+    (check (foreign-funcall "caten_b200_rope" :pointer *ctx* :pointer (buffer-value x) :pointer (buffer-value out)
+                            :int64 b :int64 s :int64 h :int64 hd :float (coerce base 'single-float) :int64 pos0 :int))))
 
 (defun call-linear (out x w bias residual act)
   "y = act(x.W^T + bias) + residual (source/nn/linear.lisp:12-17); the memory planner may have made `out` the
@@ -574,6 +588,7 @@ other WMMA operand; bias is rank-1 (broadcast along rows); the residual has the 
         ;; sources: token ids (float32, apps/gpt2/gpt2.lisp:95), wte, wpe; the start position is the dynamic shape n
         `(call-embedding ,dst ,(first srcs) ,(second srcs) ,(third srcs)
                          ,(or (find 'n (map 'list #'car (getattr si :dynamic-shapes)) :test #'string-equal :key #'symbol-name) 0)))
+       (:rmsnorm `(call-rmsnorm ,dst ,(first srcs) ,(second srcs) 1e-5))
        (:argmax `(call-argmax ,dst ,(first srcs)))
        (:expr (plan-expr si))))))
 

@@ -159,6 +159,25 @@ def attention(qkv, kc, vc, B, s, n, H, mode=STRICT_F32):
     return out
 
 
+def rmsnorm(x, weight=None, eps=1e-5, mode=STRICT_F32):
+    x = _f32(x)
+    weight = None if weight is None else _f32(weight)
+    rows, d = x.reshape(-1, x.shape[-1]).shape
+    y = np.empty_like(x)
+    lib().orc_rmsnorm(C.c_int(mode), _p(x), _p(weight), C.c_int64(rows), C.c_int64(d), C.c_float(eps), _p(y))
+    return y
+
+
+def rope(x, base=10000.0, pos0=0, mode=STRICT_F32):
+    """x [B, S, H, head_dim] -> rotated copy (`!rope x (head_dim / 2)`)."""
+    x = _f32(x)
+    B, S, H, hd = x.shape
+    y = np.empty_like(x)
+    lib().orc_rope(C.c_int(mode), _p(x), C.c_int64(B), C.c_int64(S), C.c_int64(H), C.c_int64(hd), C.c_float(base),
+                   C.c_int64(pos0), _p(y))
+    return y
+
+
 def argmax(x):
     x = _f32(x)
     rows, V = x.shape

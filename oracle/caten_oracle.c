@@ -294,6 +294,64 @@ void orc_attention(int mode, const float *qkv, float *kc, float *vc, int64_t B, 
   }
 }
 
+/* source/nn/normalization.lisp:70-85: norm = x * recip(sqrt(eps + mean(x * x))), then * weight.
+ * mode 0: every step in fp32 (sequential sum); mode 2: all in double. */
+void orc_rmsnorm(int mode, const float *x, const float *w, int64_t rows, int64_t d, float eps, float *y) {
+  for (int64_t r = 0; r < rows; ++r) {
+    const float *xr = x + r * d;
+    float *yr = y + r * d;
+    if (mode == 2) {
+      double sq = 0;
+      for (int64_t k = 0; k < d; ++k) sq += (double)xr[k] * (double)xr[k];
+      const double rs = 1.0 / sqrt((double)eps + sq / (double)d);
+      for (int64_t k = 0; k < d; ++k) yr[k] = (float)((double)xr[k] * rs * (w ? (double)w[k] : 1.0));
+    } else {
+      float sq = 0;
+      for (int64_t k = 0; k < d; ++k) sq = sq + xr[k] * xr[k];
+      const float mean = sq * (1.0f / (float)d);
+      const float rs = 1.0f / sqrtf(eps + mean);
+      for (int64_t k = 0; k < d; ++k) {
+        float v = xr[k] * rs;
+        if (w) v = v * w[k];
+        yr[k] = v;
+      }
+    }
+  }
+}
+
+/* source/nn/positional-encoding.lisp:3-56 on x [B, S, H, hd] with dim = hd / 2:
+ *   theta_i = exp(-((2 i) / hd) * log(base)); angle = (pos0 + s) * theta_i;
+ *   out[2i] = x[2i] * cos - x[2i+1] * sin; out[2i+1] = x[2i] * sin + x[2i+1] * cos; an odd last element is copied.
+ * exp = exp2(x * 1/ln2), log = log2(x) * ln2 (api/function.lisp:437-448), cos(a) = sin(a + pi/2)
+ * (api/high-level-ops.lisp:119-122); transcendentals are the double libm functions applied to floats, as the
+ * rendered C calls them (source/codegen/renderer.lisp:362-370).  mode 2: everything in double, cos as cos. */
+void orc_rope(int mode, const float *x, int64_t B, int64_t S, int64_t H, int64_t hd, float base, int64_t pos0, float *y) {
+  const int64_t half = hd / 2;
+  for (int64_t b = 0; b < B; ++b)
+    for (int64_t s = 0; s < S; ++s)
+      for (int64_t h = 0; h < H; ++h) {
+        const float *xp = x + ((b * S + s) * H + h) * hd;
+        float *yp = y + ((b * S + s) * H + h) * hd;
+        for (int64_t i = 0; i < half; ++i) {
+          if (mode == 2) {
+            const double theta = exp(-((double)(2 * i) / (double)hd) * log((double)base));
+            const double ang = (double)(pos0 + s) * theta;
+            yp[2 * i] = (float)((double)xp[2 * i] * cos(ang) - (double)xp[2 * i + 1] * sin(ang));
+            yp[2 * i + 1] = (float)((double)xp[2 * i] * sin(ang) + (double)xp[2 * i + 1] * cos(ang));
+          } else {
+            const float expo = (float)(2 * i) * (1.0f / (float)hd);
+            const float logb = (float)log2((double)base) * 0.6931472f;
+            const float theta = (float)exp2((double)(-(expo * logb)) * (double)(1.0f / 0.6931472f));
+            const float ang = (float)(pos0 + s) * theta;
+            const float sn = (float)sin((double)ang), cs = (float)sin((double)(ang + 1.5707964f));
+            yp[2 * i] = xp[2 * i] * cs + (-(xp[2 * i + 1] * sn));
+            yp[2 * i + 1] = xp[2 * i] * sn + xp[2 * i + 1] * cs;
+          }
+        }
+        if (hd & 1) yp[hd - 1] = xp[hd - 1];
+      }
+}
+
 void orc_argmax(const float *x, int64_t rows, int64_t V, int64_t *out) {
   for (int64_t r = 0; r < rows; ++r) out[r] = argmax_f32(x + r * V, V);
 }

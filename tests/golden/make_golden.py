@@ -113,6 +113,34 @@ def attn_block():
     np.savez_compressed(os.path.join(OUT, "attn_block.npz"), **out)
 
 
+def llama_ops():
+    """RMSNorm and RoPE against the functions the reference's tests import from torchtune's documentation
+    (source/test-suite/test-normalization.lisp:8-15, test-rope.lisp:38-56), restated; shapes of those tests
+    (30 x 40; 1 x 10 x 10 x 10) plus head dim 64 rows."""
+    def rms(x):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5)
+
+    def rope(x, base=10000):
+        dim = x.shape[-1]
+        theta = 1.0 / (base ** (torch.arange(0, dim, 2).float() / dim))
+        idx_theta = torch.einsum("i,j->ij", torch.arange(x.size(1), dtype=theta.dtype), theta)
+        cache = torch.stack([torch.cos(idx_theta), torch.sin(idx_theta)], dim=-1)
+        xs = x.float().reshape(*x.shape[:-1], -1, 2)
+        rc = cache.view(1, x.size(1), 1, xs.size(-2), 2)
+        out = torch.stack([xs[..., 0] * rc[..., 0] - xs[..., 1] * rc[..., 1], xs[..., 1] * rc[..., 0] + xs[..., 0] * rc[..., 1]], dim=-1)
+        return out.flatten(-2)
+
+    g = torch.Generator().manual_seed(29)
+    out = {}
+    for tag, shape in (("ref", (30, 40)), ("wide", (9, 1600))):
+        x = torch.rand(*shape, generator=g)
+        out[f"rms_{tag}_x"], out[f"rms_{tag}_y"] = x.numpy(), rms(x).numpy()
+    for tag, shape in (("ref", (1, 10, 10, 10)), ("hd64", (2, 33, 3, 64))):
+        x = torch.rand(*shape, generator=g)
+        out[f"rope_{tag}_x"], out[f"rope_{tag}_y"] = x.numpy(), rope(x).numpy()
+    np.savez_compressed(os.path.join(OUT, "llama_ops.npz"), **out)
+
+
 def torch_gpt2_f64(sd, tokens, p, n_new):
     """float64 GPT-2 (tanh GeLU, eps 1e-5, causal mask) recomputed from scratch for every new
     token: no KV cache, so it also checks the oracle's cache protocol."""
@@ -158,7 +186,7 @@ def gpt2_tiny():
 
 if __name__ == "__main__":
     only = sys.argv[1:]
-    for fn in (gguf_fixtures, torch_ops, gpt2_tiny, attn_block):
+    for fn in (gguf_fixtures, torch_ops, gpt2_tiny, attn_block, llama_ops):
         if not only or fn.__name__ in only:
             fn()
     print("wrote", sorted(f for f in os.listdir(OUT) if f.endswith(".npz")))

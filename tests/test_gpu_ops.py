@@ -462,3 +462,38 @@ def test_kv_cache_protocol(rt):
         np.testing.assert_array_equal(k[0, :, :start].transpose(1, 0, 2).reshape(start, d), np.concatenate(fed_k))
         np.testing.assert_array_equal(v[0, :, :start].transpose(1, 0, 2).reshape(start, d), np.concatenate(fed_v))
         assert not k[0, :, start:].any() and not v[0, :, start:].any()
+
+
+@pytest.mark.parametrize("rows,d", [(30, 40), (9, 1600), (3, 4096)])
+def test_rmsnorm(rt, oracle, golden, rows, d):
+    """`!rms-norm` (source/nn/normalization.lisp:70-85): the oracle within 1e-5, the torchtune function of
+    source/test-suite/test-normalization.lisp:57-63 at its tolerance, with and without a weight."""
+    g = golden["llama_ops"]
+    rng = np.random.Generator(np.random.PCG64(rows + d))
+    x = g["rms_ref_x"] if (rows, d) == (30, 40) else g["rms_wide_x"] if (rows, d) == (9, 1600) else rng.standard_normal((rows, d), dtype=np.float32) * 2
+    w = (rng.random(d, dtype=np.float32) + 0.5)
+    dx = rt.transfer_from_array(x)
+    got = rt.rmsnorm(dx).numpy()
+    np.testing.assert_allclose(got, oracle.rmsnorm(x), atol=1e-5, rtol=1e-5)
+    acc_check(got, oracle.rmsnorm(x), oracle.rmsnorm(x, mode=2))
+    if (rows, d) == (30, 40):
+        np.testing.assert_allclose(got, g["rms_ref_y"], atol=1e-3, rtol=1e-6)
+    np.testing.assert_allclose(rt.rmsnorm(dx, rt.transfer_from_array(w)).numpy(), oracle.rmsnorm(x, w), atol=1e-5, rtol=1e-5)
+    with pytest.raises(B200Error):
+        rt.rmsnorm(rt.open_buffer((2, 10)))    # d % 4 != 0
+
+
+@pytest.mark.parametrize("tag", ["ref", "hd64"])
+def test_rope(rt, oracle, golden, tag):
+    """`!rope` (source/nn/positional-encoding.lisp:3-56): bit-exact against the oracle (the same fp32 formula,
+    transcendentals through double), the torchtune function of source/test-suite/test-rope.lisp:60-66 at its
+    tolerance, and a continued sequence (pos0 > 0) equal to the tail of the full one."""
+    g = golden["llama_ops"]
+    x = g[f"rope_{tag}_x"]
+    got = rt.rope(rt.transfer_from_array(x)).numpy()
+    np.testing.assert_allclose(got, oracle.rope(x), atol=1e-6, rtol=1e-6)
+    np.testing.assert_allclose(got, g[f"rope_{tag}_y"], atol=1e-5, rtol=5e-4)
+    tail = rt.rope(rt.transfer_from_array(x[:, 4:]), pos0=4).numpy()
+    np.testing.assert_array_equal(tail, got[:, 4:])
+    odd = np.random.Generator(np.random.PCG64(1)).random((2, 5, 3, 7), dtype=np.float32)
+    np.testing.assert_allclose(rt.rope(rt.transfer_from_array(odd)).numpy(), oracle.rope(odd), atol=1e-6, rtol=1e-6)

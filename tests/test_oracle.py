@@ -198,3 +198,22 @@ def test_kv_cache_protocol(oracle):
         np.testing.assert_array_equal(kc[0, :start].reshape(start, d), np.concatenate(fed_k))
         np.testing.assert_array_equal(vc[0, :start].reshape(start, d), np.concatenate(fed_v))
         assert not kc[0, start:].any() and not vc[0, start:].any()
+
+
+@pytest.mark.parametrize("mode", [0, 2])
+def test_rmsnorm_and_rope_vs_torch(oracle, golden, mode):
+    """source/test-suite/test-normalization.lisp:57-63 (RMSNorm, atol 1e-3 / rtol 1e-6) and test-rope.lisp:60-66
+    (RoPE, atol 1e-5 / rtol 5e-4) against the torchtune functions those tests import."""
+    g = golden["llama_ops"]
+    for tag in ("ref", "wide"):
+        np.testing.assert_allclose(oracle.rmsnorm(g[f"rms_{tag}_x"], mode=mode), g[f"rms_{tag}_y"], atol=1e-5, rtol=1e-6)
+    for tag in ("ref", "hd64"):
+        np.testing.assert_allclose(oracle.rope(g[f"rope_{tag}_x"], mode=mode), g[f"rope_{tag}_y"], atol=1e-5, rtol=5e-4)
+    # a weight multiplies after the normalisation; an odd head dim keeps its last element
+    x = g["rms_ref_x"]
+    w = np.linspace(0.5, 1.5, x.shape[1]).astype(np.float32)
+    np.testing.assert_allclose(oracle.rmsnorm(x, w, mode=mode), g["rms_ref_y"] * w, atol=1e-5, rtol=1e-6)
+    odd = np.random.Generator(np.random.PCG64(1)).random((1, 4, 2, 7), dtype=np.float32)
+    out = oracle.rope(odd, mode=mode)
+    np.testing.assert_array_equal(out[..., 6], odd[..., 6])
+    np.testing.assert_array_equal(out[:, 0], odd[:, 0])   # position 0: no rotation
