@@ -61,6 +61,16 @@ def load_peaks():
         return 6650.0, "fallback (no MEASURED_PEAKS.json beside bench.py)"
 
 
+def load_tensor_peak():
+    """(burst, sustained) dense bf16 TFLOP/s of MEASURED_PEAKS.json, else the fallback pair."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            j = json.load(f)
+            return float(j["bf16_tflops"]), float(j["bf16_tflops_sustained"])
+    except Exception:
+        return 1590.0, 1400.0
+
+
 class ClockSampler:
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -435,8 +445,50 @@ def main():
         br = rt.profile_end()
         tot = sum(v[0] for v in br.values()) or 1.0
         extras["kernel_ms_share"] = {k: round(v[0] / tot, 4) for k, v in br.items()}
+        # prefill: the real one above (the precision of the run), plus one group of sequences (what one pass of the
+        # prefill processes at a time) in each tensor-core precision on rank 0, with the useful FLOP rate
+        # (2 x 12 d^2 L per token + causal attention 2 s d L per token + the last row's lm_head)
         extras["prefill"] = {"tokens_per_s": sum_over_ranks(nb * prompt_len) / (prefill_ms / 1e3), "ms": prefill_ms,
-                             "tokens": batch * prompt_len}
+                             "tokens": batch * prompt_len, "precision": args.precision}
+        if rank == 0 and world == 1 and args.precision != "fp32":
+            _, bf16_peak = load_tensor_peak()
+            gsz = max(1, min(nb, 8192 // prompt_len))
+            flop_per_tok = 2.0 * 12 * params.dim ** 2 * params.n_layers + 2.0 * prompt_len * params.dim * params.n_layers
+            for prec in ("bf16x3", "bf16"):
+                pm = GPT2(rt, params, sd, max_seq_len=prompt_len + 8, batch=gsz, precision=prec)
+                pin = rt.transfer_from_array(prompts[:gsz].astype(np.float32))
+                pout = rt.open_buffer((gsz,), np.int64)
+                pm.forward_device(pin, prompt_len, 0, pout); rt.sync()      # warm-up (allocations, attributes)
+                p0 = ev(); pm.forward_device(pin, prompt_len, 0, pout); p1 = ev(); rt.sync()
+                ms = p0.elapsed_time(p1)
+                tf = flop_per_tok * gsz * prompt_len / (ms / 1e3) / 1e12
+                extras["prefill"][f"group_{prec}"] = {"sequences": gsz, "tokens": gsz * prompt_len, "ms": ms, "tokens_per_s": gsz * prompt_len / (ms / 1e3),
+                                                       "useful_TFLOP/s": tf, "frac_of_sustained_bf16_peak": tf / bf16_peak,
+                                                       "issued_frac": tf * (3 if prec == "bf16x3" else 1) / bf16_peak}
+                pm.close(); pin.close(); pout.close()
+            # configuration 2 of the reference's benchmark list: relu(A[4096x768] . B[768x3072]), fp32 in and out
+            A_, B_ = S.synth_relu_gemm(seed=1)
+            da, db = rt.transfer_from_array(A_), rt.transfer_from_array(B_)
+            from caten_b200 import _lib as L_
+            dc = rt.open_buffer((4096, 3072))
+            rm = {}
+            for prec in ("bf16x3", "bf16", "fp32"):
+                pc = L_.PRECISIONS[prec]
+
+                def once():   # straight through the C ABI into a caller-owned output: no allocation inside the timed loop
+                    L_.check(rt.ctx, rt.lib.caten_b200_relu_matmul(rt.ctx, da.ptr, db.ptr, dc.ptr, 4096, 768, 3072, pc))
+                for _ in range(3):
+                    once()
+                rt.sync()
+                p0 = ev()
+                for _ in range(10):
+                    once()
+                p1 = ev(); rt.sync()
+                us = p0.elapsed_time(p1) / 10 * 1e3
+                tf = 2.0 * 4096 * 768 * 3072 / (us / 1e6) / 1e12
+                rm[prec] = {"us": us, "useful_TFLOP/s": tf, "frac_of_sustained_bf16_peak": tf / bf16_peak}
+            extras["relu_matmul_4096x768x3072"] = rm
+            da.close(); db.close(); dc.close()
         if rank == 0 and wtype != "f32":
             # dequant-GEMV on the model's own matrices, cycling over all layers so the weights
             # (hundreds of MB in total) do not stay in the 126 MB L2
