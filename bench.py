@@ -214,6 +214,9 @@ def main():
     ap.add_argument("--dist-plane", default="capi", choices=["capi", "torch"],
                     help="who moves the weights and the ids between GPUs: the library's own NCCL entry points "
                          "(caten_b200_dist_*, what a Lisp host would call) or torch.distributed")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="override the workload's total batch (e.g. 32 = what one of 8 GPUs holds in a strong-scaled xl-q4_0-b256 run); "
+                         "the batch that ran is the one config.workload names")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the short oracle check of the benchmarked model")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill/GEMV/kernel-breakdown side measurements")
@@ -223,6 +226,10 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     model_name, wtype, batch, prompt_len, decode_len = WORKLOADS[args.workload]
+    if args.batch is not None:
+        if args.batch < 1:
+            raise SystemExit("--batch must be at least 1")
+        batch = args.batch
     if args.scaling == "weak":
         batch *= world   # global batch; every rank keeps the workload's own batch
     W = max(0, args.warmup)

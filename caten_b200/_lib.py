@@ -15,7 +15,8 @@ LIB_PATH = os.environ.get("CATEN_B200_LIB") or os.path.join(HERE, "libcaten_b200
 
 OK, EINVAL, ECUDA, EUNSUPPORTED, EDEVICE = 0, 1, 2, 3, 4
 F32, F16, Q4_0, Q8_0 = 0, 1, 2, 8
-Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K = 3, 6, 7, 10, 11, 12, 13, 14   # expanded to fp32 at upload
+Q4_1, Q5_0, Q5_1 = 3, 6, 7                                # kept packed, like Q4_0 and Q8_0
+Q2_K, Q3_K, Q4_K, Q5_K, Q6_K = 10, 11, 12, 13, 14        # expanded to fp32 at upload
 BLOCK_FORMATS = (Q4_0, Q8_0, Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K)
 ACT_NONE, ACT_GELU, ACT_RELU = 0, 1, 2
 PREC_FP32, PREC_BF16, PREC_BF16X3 = 0, 1, 2
@@ -82,6 +83,7 @@ SIGNATURES = {
     "caten_b200_weight_upload_device": (C.c_int, [_vp, C.c_int, _vp, _i64, _i64, _PFP]),
     "caten_b200_weight_free": (C.c_int, [_vp, _vp]),
     "caten_b200_weight_nbytes": (_i64, [C.c_int, _i64, _i64]),
+    "caten_b200_weight_device_nbytes": (_i64, [_vp]),
     "caten_b200_weight_dequant": (C.c_int, [_vp, _vp, _vp]),
     "caten_b200_gguf_open": (C.c_int, [C.c_char_p, _PFP]),
     "caten_b200_gguf_close": (C.c_int, [_vp]),

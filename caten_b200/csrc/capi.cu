@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "blocks32.cuh"
 
 namespace cb {
 
@@ -226,8 +227,8 @@ int64_t caten_b200_weight_nbytes(int type, int64_t rows, int64_t cols) {
   switch (type) {
     case CATEN_B200_F32: return n * 4;
     case CATEN_B200_F16: return n * 2;
-    case CATEN_B200_Q4_0: return cols % 32 ? -1 : n / 32 * 18;
-    case CATEN_B200_Q8_0: return cols % 32 ? -1 : n / 32 * 34;
+    case CATEN_B200_Q4_0: case CATEN_B200_Q4_1: case CATEN_B200_Q5_0: case CATEN_B200_Q5_1: case CATEN_B200_Q8_0:
+      return cols % 32 ? -1 : n / 32 * cb::type_block_bytes(type);
   }
   return cb::extra_type_nbytes(type, n, cols);
 }
@@ -248,22 +249,35 @@ int caten_b200_weight_upload_device(caten_b200_ctx *ctx, int type, const void *d
   if (cb::extra_type_nbytes(type, rows * cols, cols) >= 0) {
     // a block format the kernels do not consume packed: expand to fp32 now, keep an fp32 weight
     w->type = CATEN_B200_F32;
+    w->device_bytes = rows * cols * (int64_t)sizeof(float);
     if ((e = cudaMalloc(&w->qs, (size_t)(rows * cols) * sizeof(float))) != cudaSuccess) { delete w; return cuda_fail(ctx, e, "cudaMalloc(weight)"); }
     if (int rc = launch_dequant_extra(ctx, type, (const uint8_t *)d_blocks, rows * cols, (float *)w->qs)) { cudaFree(w->qs); delete w; return rc; }
   } else if (type == CATEN_B200_F32 || type == CATEN_B200_F16) {
+    w->device_bytes = nbytes;
     if ((e = cudaMalloc(&w->qs, (size_t)nbytes)) != cudaSuccess) { delete w; return cuda_fail(ctx, e, "cudaMalloc(weight)"); }
     if ((e = cudaMemcpyAsync(w->qs, d_blocks, (size_t)nbytes, cudaMemcpyDeviceToDevice, ctx->stream)) != cudaSuccess) {
       cudaFree(w->qs); delete w; return cuda_fail(ctx, e, "cudaMemcpyAsync(weight)");
     }
   } else {
+    // the 32-weight block formats stay packed: codes, scales, minima and fifth bits as separate arrays
     w->nkb = cols / 32;
     const int64_t nblocks = rows * w->nkb;
-    const size_t qbytes = (size_t)nblocks * (type == CATEN_B200_Q4_0 ? 16 : 32);
-    if ((e = cudaMalloc(&w->qs, qbytes)) != cudaSuccess) { delete w; return cuda_fail(ctx, e, "cudaMalloc(weight codes)"); }
+    const size_t qbytes = (size_t)nblocks * cb::type_code_bytes(type);
+    auto drop = [&]() { cudaFree(w->qs); cudaFree(w->d); cudaFree(w->m); cudaFree(w->qh); delete w; };
+    if ((e = cudaMalloc(&w->qs, qbytes)) != cudaSuccess) { drop(); return cuda_fail(ctx, e, "cudaMalloc(weight codes)"); }
     // 16 spare bytes: the single-kernel decode step fetches scales in whole 16-byte pieces
-    if ((e = cudaMalloc((void **)&w->d, (size_t)nblocks * 2 + 16)) != cudaSuccess) { cudaFree(w->qs); delete w; return cuda_fail(ctx, e, "cudaMalloc(weight scales)"); }
+    if ((e = cudaMalloc((void **)&w->d, (size_t)nblocks * 2 + 16)) != cudaSuccess) { drop(); return cuda_fail(ctx, e, "cudaMalloc(weight scales)"); }
     cudaMemsetAsync((uint8_t *)w->d + (size_t)nblocks * 2, 0, 16, ctx->stream);
-    if (int rc = launch_repack(ctx, type, (const uint8_t *)d_blocks, nblocks, w->qs, w->d)) { cudaFree(w->qs); cudaFree(w->d); delete w; return rc; }
+    w->device_bytes = (int64_t)qbytes + nblocks * 2;
+    if (cb::type_has_min(type)) {
+      if ((e = cudaMalloc((void **)&w->m, (size_t)nblocks * 2)) != cudaSuccess) { drop(); return cuda_fail(ctx, e, "cudaMalloc(weight minima)"); }
+      w->device_bytes += nblocks * 2;
+    }
+    if (cb::type_has_qh(type)) {
+      if ((e = cudaMalloc((void **)&w->qh, (size_t)nblocks * 4)) != cudaSuccess) { drop(); return cuda_fail(ctx, e, "cudaMalloc(weight fifth bits)"); }
+      w->device_bytes += nblocks * 4;
+    }
+    if (int rc = launch_repack(ctx, type, (const uint8_t *)d_blocks, nblocks, w->qs, w->d, w->m, w->qh)) { drop(); return rc; }
   }
   ctx->weights_pending = true;  // the next kernel launch must not start reading weights early
   *out = w;
@@ -294,9 +308,13 @@ int caten_b200_weight_free(caten_b200_ctx *ctx, caten_b200_weight *w) {
   if (!w) return 0;
   if (w->qs) cudaFree(w->qs);
   if (w->d) cudaFree(w->d);
+  if (w->m) cudaFree(w->m);
+  if (w->qh) cudaFree(w->qh);
   delete w;
   return 0;
 }
+
+int64_t caten_b200_weight_device_nbytes(const caten_b200_weight *w) { return w ? w->device_bytes : -1; }
 
 int caten_b200_weight_dequant(caten_b200_ctx *ctx, const caten_b200_weight *w, float *d_out) {
   NEED_CTX(ctx);

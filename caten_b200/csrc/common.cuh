@@ -112,8 +112,11 @@ struct caten_b200_weight {
   int type = 0;
   int64_t rows = 0, cols = 0;
   int64_t nkb = 0;          // blocks of 32 per row (quantised types)
-  void *qs = nullptr;       // F32: float[rows*cols]; F16: half[rows*cols]; Q8_0: int8[rows*nkb*32]; Q4_0: u8[rows*nkb*16]
+  void *qs = nullptr;       // F32: float[rows*cols]; F16: half[rows*cols]; Q8_0: int8[rows*nkb*32]; Q4_x / Q5_x: u8[rows*nkb*16]
   __half *d = nullptr;      // per-block scales [rows*nkb] (quantised types)
+  __half *m = nullptr;      // per-block minima [rows*nkb] (Q4_1, Q5_1)
+  uint32_t *qh = nullptr;   // per-block fifth code bits [rows*nkb] (Q5_0, Q5_1)
+  int64_t device_bytes = 0; // what the arrays above occupy
   caten_b200_ctx *ctx = nullptr;
 };
 
@@ -136,7 +139,7 @@ int scratch_reserve(caten_b200_ctx *ctx, Scratch *s, size_t bytes);
   } while (0)
 
 // ---- launchers (each returns a status code; all asynchronous on ctx->stream) ----
-int launch_repack(caten_b200_ctx *ctx, int type, const uint8_t *d_blocks, int64_t nblocks, void *qs, __half *d);
+int launch_repack(caten_b200_ctx *ctx, int type, const uint8_t *d_blocks, int64_t nblocks, void *qs, __half *d, __half *m, uint32_t *qh);
 int launch_dequant(caten_b200_ctx *ctx, const caten_b200_weight *w, float *out);
 // block formats that are expanded to fp32 at upload (dequant_extra.cu)
 int64_t extra_type_nbytes(int type, int64_t n, int64_t cols);

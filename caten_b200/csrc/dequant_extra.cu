@@ -1,5 +1,5 @@
-// GGUF block formats beyond the two the kernels consume packed (Q4_0, Q8_0): Q4_1, Q5_0, Q5_1
-// and the 256-element "K" formats Q2_K, Q3_K, Q4_K, Q5_K, Q6_K.  The reference lists these type ids but
+// GGUF block formats beyond those the kernels consume packed (Q4_0, Q4_1, Q5_0, Q5_1, Q8_0): the
+// 256-element "K" formats Q2_K, Q3_K, Q4_K, Q5_K, Q6_K.  The reference lists these type ids but
 // implements none of them (external/gguf/tensor-info.lisp:3-34, 36-41); what it does for the
 // types it knows is dequantise to fp32 at load (external/gguf/dequantize.lisp:14-53), and that is
 // what happens here for these formats: the raw blocks are expanded once, on the device, into an
@@ -12,31 +12,6 @@ namespace cb {
 
 __device__ __forceinline__ float h2f(const uint8_t *p) {
   return __half2float(__ushort_as_half((unsigned short)(p[0] | (p[1] << 8))));
-}
-
-// legacy formats: 32 weights per block; one thread per weight
-__global__ void dequant_block32_kernel(int type, const uint8_t *__restrict__ blocks, float *__restrict__ out, int64_t n) {
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  const int64_t blk = i >> 5;
-  const int e = (int)(i & 31), j = e & 15, hi = e >> 4;  // byte j holds elements j (low nibble) and j + 16 (high nibble)
-  float w;
-  if (type == CATEN_B200_Q4_1) {  // d, m, qs[16]
-    const uint8_t *b = blocks + blk * 20;
-    const int q = hi ? b[4 + j] >> 4 : b[4 + j] & 15;
-    w = (float)q * h2f(b) + h2f(b + 2);
-  } else if (type == CATEN_B200_Q5_0) {  // d, qh[4], qs[16]
-    const uint8_t *b = blocks + blk * 22;
-    const uint32_t qh = b[2] | (b[3] << 8) | (b[4] << 16) | ((uint32_t)b[5] << 24);
-    const int q = ((hi ? b[6 + j] >> 4 : b[6 + j] & 15) | (((qh >> e) & 1u) << 4)) - 16;
-    w = h2f(b) * (float)q;
-  } else {  // Q5_1: d, m, qh[4], qs[16]
-    const uint8_t *b = blocks + blk * 24;
-    const uint32_t qh = b[4] | (b[5] << 8) | (b[6] << 16) | ((uint32_t)b[7] << 24);
-    const int q = (hi ? b[8 + j] >> 4 : b[8 + j] & 15) | (((qh >> e) & 1u) << 4);
-    w = (float)q * h2f(b) + h2f(b + 2);
-  }
-  out[i] = w;
 }
 
 // 6-bit scale and minimum of sub-block j (0..7) from the 12 packed bytes of a Q4_K / Q5_K block
@@ -105,9 +80,6 @@ __global__ void dequant_block256_kernel(int type, const uint8_t *__restrict__ bl
 // bytes of `n` weights in block format `type`, or -1 when the format is not one of this file's
 int64_t extra_type_nbytes(int type, int64_t n, int64_t cols) {
   switch (type) {
-    case CATEN_B200_Q4_1: return cols % 32 ? -1 : n / 32 * 20;
-    case CATEN_B200_Q5_0: return cols % 32 ? -1 : n / 32 * 22;
-    case CATEN_B200_Q5_1: return cols % 32 ? -1 : n / 32 * 24;
     case CATEN_B200_Q2_K: return cols % 256 ? -1 : n / 256 * 84;
     case CATEN_B200_Q3_K: return cols % 256 ? -1 : n / 256 * 110;
     case CATEN_B200_Q4_K: return cols % 256 ? -1 : n / 256 * 144;
@@ -121,10 +93,7 @@ int launch_dequant_extra(caten_b200_ctx *ctx, int type, const uint8_t *d_blocks,
   if (n <= 0) return 0;
   const int64_t grid = (n + 255) / 256;
   if (grid > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "dequant: tensor too large");
-  if (type == CATEN_B200_Q4_1 || type == CATEN_B200_Q5_0 || type == CATEN_B200_Q5_1)
-    dequant_block32_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(type, d_blocks, out, n);
-  else
-    dequant_block256_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(type, d_blocks, out, n);
+  dequant_block256_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(type, d_blocks, out, n);
   CB_LAUNCH_CHECK(ctx, "dequant_extra");
   return 0;
 }

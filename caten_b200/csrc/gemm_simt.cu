@@ -5,6 +5,7 @@
 // order and roundings as the C loop BACKEND=CLANG renders for !matmul (source/byoc/clang.lisp:58-111,
 // api/high-level-ops.lisp:85-86) when gcc targets baseline x86-64 (no FMA contraction).
 #include "common.cuh"
+#include "blocks32.cuh"
 
 namespace cb {
 
@@ -13,8 +14,8 @@ constexpr int WT_F32_T = 100;  // fp32 operand given as [K, N] row-major (relu_m
 constexpr int SG_BM = 64, SG_BN = 64, SG_BK = 32, SG_LD = 68;
 
 template <int WT>
-__device__ __forceinline__ void load_w8(const void *qs, const __half *d, int64_t row, int64_t N, int64_t K,
-                                        int64_t nkb, int kb, int part, float *o) {
+__device__ __forceinline__ void load_w8(const void *qs, const __half *d, const __half *mins, const uint32_t *qh5, int64_t row,
+                                        int64_t N, int64_t K, int64_t nkb, int kb, int part, float *o) {
   if (row >= N) {
 #pragma unroll
     for (int e = 0; e < 8; ++e) o[e] = 0.0f;
@@ -36,23 +37,26 @@ __device__ __forceinline__ void load_w8(const void *qs, const __half *d, int64_t
     const int8_t *q = reinterpret_cast<const int8_t *>(&v);
 #pragma unroll
     for (int e = 0; e < 8; ++e) o[e] = (float)q[e] * sc;
-  } else if (WT == CATEN_B200_Q4_0) {
+  } else if (type_is_nibble(WT)) {
     // elements part*8 .. part*8+7 of the block: parts 0,1 are the low nibbles of bytes 0-7, 8-15;
-    // parts 2,3 the high nibbles of the same bytes
+    // parts 2,3 the high nibbles of the same bytes; the 5-bit formats take bit 4 from qh
     const int64_t bi = row * nkb + kb;
     const uint2 v = *reinterpret_cast<const uint2 *>((const uint8_t *)qs + bi * 16 + (part & 1) * 8);
     const float sc = __half2float(d[bi]);
+    const float mn = type_has_min(WT) ? __half2float(mins[bi]) : 0.0f;
+    const uint32_t hb = type_has_qh(WT) ? qh5[bi] >> (part * 8) : 0u;
     const uint8_t *q = reinterpret_cast<const uint8_t *>(&v);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       const int nib = part < 2 ? (q[e] & 0x0F) : (q[e] >> 4);
-      o[e] = (float)(nib - 8) * sc;
+      o[e] = nibble_value<WT>(nib | (int)(((hb >> e) & 1u) << 4), sc, mn);
     }
   }
 }
 
 template <int WT>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const void *__restrict__ qs, const __half *__restrict__ d,
+                                                        const __half *__restrict__ mins, const uint32_t *__restrict__ qh5,
                                                         const float *__restrict__ x, const float *__restrict__ bias,
                                                         const float *res, float *y, int act, int64_t M, int64_t N,
                                                         int64_t K, int64_t nkb) {
@@ -83,7 +87,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const void *__restrict__
       for (int e = 0; e < 8; ++e)
         wv[e] = n0 + lrow < N ? ((const float *)qs)[((int64_t)kb * 32 + part * 8 + e) * N + n0 + lrow] : 0.0f;
     } else {
-      load_w8<WT>(qs, d, n0 + lrow, N, K, nkb, kb, part, wv);
+      load_w8<WT>(qs, d, mins, qh5, n0 + lrow, N, K, nkb, kb, part, wv);
     }
     __syncthreads();
 #pragma unroll
@@ -121,12 +125,12 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const void *__restrict__
 }
 
 template <int WT>
-static int launch_simt(caten_b200_ctx *ctx, const void *qs, const __half *d, const float *x, const float *bias,
-                       const float *res, int act, float *y, int64_t M, int64_t N, int64_t K) {
+static int launch_simt(caten_b200_ctx *ctx, const void *qs, const __half *d, const __half *mins, const uint32_t *qh5, const float *x,
+                       const float *bias, const float *res, int act, float *y, int64_t M, int64_t N, int64_t K) {
   if (K % 32) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm: inner dimension %lld is not a multiple of 32", (long long)K);
   const int64_t gx = (N + SG_BN - 1) / SG_BN, gy = (M + SG_BM - 1) / SG_BM;
   if (gy > 65535) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm: too many rows for one launch (%lld)", (long long)M);
-  launch_k(ctx, gemm_simt_kernel<WT>, dim3((unsigned)gx, (unsigned)gy), dim3(256), 0, qs, d, x, bias, res, y, act, M, N, K, K / 32);
+  launch_k(ctx, gemm_simt_kernel<WT>, dim3((unsigned)gx, (unsigned)gy), dim3(256), 0, qs, d, mins, qh5, x, bias, res, y, act, M, N, K, K / 32);
   CB_LAUNCH_CHECK(ctx, "gemm_simt_kernel");
   return 0;
 }
@@ -134,18 +138,24 @@ static int launch_simt(caten_b200_ctx *ctx, const void *qs, const __half *d, con
 int launch_gemm_simt(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
                      const float *res, int act, float *y, int64_t M) {
   if (M <= 0) return 0;
+#define SIMT_CASE(T) \
+  case T: return launch_simt<T>(ctx, w->qs, w->d, w->m, w->qh, x, bias, res, act, y, M, w->rows, w->cols)
   switch (w->type) {
-    case CATEN_B200_F32: return launch_simt<CATEN_B200_F32>(ctx, w->qs, w->d, x, bias, res, act, y, M, w->rows, w->cols);
-    case CATEN_B200_F16: return launch_simt<CATEN_B200_F16>(ctx, w->qs, w->d, x, bias, res, act, y, M, w->rows, w->cols);
-    case CATEN_B200_Q8_0: return launch_simt<CATEN_B200_Q8_0>(ctx, w->qs, w->d, x, bias, res, act, y, M, w->rows, w->cols);
-    case CATEN_B200_Q4_0: return launch_simt<CATEN_B200_Q4_0>(ctx, w->qs, w->d, x, bias, res, act, y, M, w->rows, w->cols);
+    SIMT_CASE(CATEN_B200_F32);
+    SIMT_CASE(CATEN_B200_F16);
+    SIMT_CASE(CATEN_B200_Q8_0);
+    SIMT_CASE(CATEN_B200_Q4_0);
+    SIMT_CASE(CATEN_B200_Q4_1);
+    SIMT_CASE(CATEN_B200_Q5_0);
+    SIMT_CASE(CATEN_B200_Q5_1);
   }
+#undef SIMT_CASE
   return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm: weight type %d", w->type);
 }
 
 int launch_relu_matmul_simt(caten_b200_ctx *ctx, const float *a, const float *b, float *c, int64_t M, int64_t K, int64_t N) {
   if (M <= 0 || N <= 0) return 0;
-  return launch_simt<WT_F32_T>(ctx, b, nullptr, a, nullptr, nullptr, CATEN_B200_ACT_RELU, c, M, N, K);
+  return launch_simt<WT_F32_T>(ctx, b, nullptr, nullptr, nullptr, a, nullptr, nullptr, CATEN_B200_ACT_RELU, c, M, N, K);
 }
 
 }  // namespace cb

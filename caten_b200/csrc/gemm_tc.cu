@@ -30,6 +30,7 @@
 #include <atomic>
 
 #include "common.cuh"
+#include "blocks32.cuh"
 #include "tcgen05.cuh"
 
 namespace cb {
@@ -41,7 +42,8 @@ constexpr int TC_BK = 64;       // k per stage: 64 bf16 = one 128-byte swizzle r
 
 struct TcArgs {
   const void *qs;
-  const __half *d;
+  const __half *d, *m;   // per-block scales; minima (Q4_1, Q5_1)
+  const uint32_t *qh;    // per-block fifth code bits (Q5_0, Q5_1)
   const float *bias, *res;
   float *y;
   int *status;
@@ -146,6 +148,58 @@ template <> struct WRow<CATEN_B200_Q4_0> {
     }
   }
 };
+
+// Q4_1, Q5_0, Q5_1: each weight is formed in fp32 exactly as the dequantiser forms it (code
+// product, then the minimum), then split into bf16 terms.
+template <int WT> struct WRowNibble {
+  static constexpr int DEPTH = 2, GROUPS = 4;
+  uint4 q[2];       // the chunk's two blocks of nibbles
+  uint32_t sc2;     // their fp16 scales
+  uint32_t mn2;     // their fp16 minima (the _1 formats)
+  uint32_t hb[2];   // their fifth code bits (the 5-bit formats)
+  __device__ __forceinline__ void load(const TcArgs &a, int64_t row, bool ok, int kc) {
+    if (ok) {
+      const int64_t bi = row * a.nkb + (int64_t)kc * 2;  // even: the pairs below are naturally aligned
+      q[0] = __ldcs(reinterpret_cast<const uint4 *>(a.qs) + bi);
+      q[1] = __ldcs(reinterpret_cast<const uint4 *>(a.qs) + bi + 1);
+      sc2 = *reinterpret_cast<const uint32_t *>(a.d + bi);
+      mn2 = type_has_min(WT) ? *reinterpret_cast<const uint32_t *>(a.m + bi) : 0u;
+      if (type_has_qh(WT)) {
+        const uint2 h = *reinterpret_cast<const uint2 *>(a.qh + bi);
+        hb[0] = h.x; hb[1] = h.y;
+      } else {
+        hb[0] = hb[1] = 0u;
+      }
+    } else {
+      // codes that dequantise to zero with scale and minimum zero
+      q[0] = q[1] = make_uint4(0u, 0u, 0u, 0u);
+      sc2 = mn2 = 0u;
+      hb[0] = hb[1] = 0u;
+    }
+  }
+  template <int NSPLIT> __device__ __forceinline__ void store(uint32_t t_hi) const {
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      const float d = __half2float(__ushort_as_half((unsigned short)(b ? sc2 >> 16 : sc2 & 0xFFFFu)));
+      const float mn = __half2float(__ushort_as_half((unsigned short)(b ? mn2 >> 16 : mn2 & 0xFFFFu)));
+      const uint32_t wd[4] = {q[b].x, q[b].y, q[b].z, q[b].w};
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {  // elements 0..15: low nibbles of the 16 bytes; 16..31: high nibbles
+        float w[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const int nib = (int)((wd[e >> 2] >> (8 * (e & 3) + 4 * half)) & 15u);
+          const int code = nib | (int)(((hb[b] >> (16 * half + e)) & 1u) << 4);
+          w[e] = nibble_value<WT>(code, d, mn);
+        }
+        emit16<NSPLIT>(t_hi, 16 * b + 8 * half, w);
+      }
+    }
+  }
+};
+template <> struct WRow<CATEN_B200_Q4_1> : WRowNibble<CATEN_B200_Q4_1> {};
+template <> struct WRow<CATEN_B200_Q5_0> : WRowNibble<CATEN_B200_Q5_0> {};
+template <> struct WRow<CATEN_B200_Q5_1> : WRowNibble<CATEN_B200_Q5_1> {};
 
 template <> struct WRow<CATEN_B200_Q8_0> {
   static constexpr int DEPTH = 2, GROUPS = 4;
@@ -646,6 +700,9 @@ static int launch_tc(caten_b200_ctx *ctx, int wt, int nsplit, const CUtensorMap 
     TC_CASE(CATEN_B200_F32);
     TC_CASE(CATEN_B200_F16);
     TC_CASE(CATEN_B200_Q4_0);
+    TC_CASE(CATEN_B200_Q4_1);
+    TC_CASE(CATEN_B200_Q5_0);
+    TC_CASE(CATEN_B200_Q5_1);
     TC_CASE(CATEN_B200_Q8_0);
     TC_CASE(WT_F32_T);
     default: return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_tc: weight type %d", wt);
@@ -681,7 +738,7 @@ static int tc_plan(caten_b200_ctx *ctx, const char *who, int64_t M, int64_t N, i
   const int num_k = (int)(K / TC_BK);
   int splits = 1;
   if (p->tiles < ctx->sm_count) {
-    const int by_work = num_k / 4 > 0 ? num_k / 4 : 1;        // at least 4 chunks per CTA
+    const int by_work = num_k / 4 > 0 ? num_k / 4 : 1;        // at least 4 chunks per CTA (2 or 1 measured no faster)
     const int by_fill = (int)(ctx->sm_count / p->tiles);      // one wave: every CTA resident at once
     splits = by_work < by_fill ? by_work : by_fill;
     if (splits > split_cap) splits = split_cap;
@@ -697,7 +754,16 @@ static int tc_plan(caten_b200_ctx *ctx, const char *who, int64_t M, int64_t N, i
   return 0;
 }
 
-static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, int64_t nkb, const float *x,
+// where a weight operand lives
+struct WSrc {
+  const void *qs;
+  const __half *d, *m;
+  const uint32_t *qh;
+  int64_t nkb;
+};
+static WSrc wsrc_of(const caten_b200_weight *w) { return WSrc{w->qs, w->d, w->m, w->qh, w->nkb}; }
+
+static int run_tc(caten_b200_ctx *ctx, int wt, const WSrc &ws, const float *x,
                   const float *bias, const float *res, int act, float *y, int64_t M, int64_t N, int64_t K, int nsplit,
                   const __nv_bfloat16 *xhi_pre = nullptr, const __nv_bfloat16 *xlo_pre = nullptr, BfOut ybf = BfOut(),
                   PartIn *defer = nullptr) {
@@ -731,9 +797,9 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const void *qs, const __half *d, 
   if (int rc = make_x_map(ctx, &ml, nsplit == 3 ? xlo : xhi, M, K, p.bnx)) return rc;
 
   TcArgs a;
-  a.qs = qs; a.d = d; a.bias = bias; a.res = res; a.y = y; a.status = ctx->d_status; a.act = act;
+  a.qs = ws.qs; a.d = ws.d; a.m = ws.m; a.qh = ws.qh; a.bias = bias; a.res = res; a.y = y; a.status = ctx->d_status; a.act = act;
   a.yhi = ybf.hi; a.ylo = ybf.lo;
-  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.nkb = (int)nkb; a.bnx = p.bnx;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.nkb = (int)ws.nkb; a.bnx = p.bnx;
   a.stages = p.stages; a.idesc = p.idesc; a.concat = p.concat;
   a.splits = p.splits; a.cps = p.cps; a.part = nullptr;
   a.cluster = (p.splits > 1 && want_cluster) ? 1 : 0;
@@ -815,7 +881,7 @@ int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, cons
   if (int rc = make_x_map(ctx, &ml, nsplit == 3 ? xlo : xhi, M, K, p.bnx)) return rc;
 
   TcArgs a;
-  a.qs = w->qs; a.d = w->d; a.bias = bias; a.res = res; a.y = y; a.status = ctx->d_status; a.act = act;
+  a.qs = w->qs; a.d = w->d; a.m = w->m; a.qh = w->qh; a.bias = bias; a.res = res; a.y = y; a.status = ctx->d_status; a.act = act;
   a.yhi = nullptr; a.ylo = nullptr;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.nkb = (int)w->nkb; a.bnx = p.bnx;
   a.stages = p.stages; a.idesc = p.idesc; a.concat = p.concat;
@@ -834,17 +900,17 @@ int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, cons
 
 int launch_gemm_tc(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const float *bias,
                    const float *res, int act, float *y, int64_t M, int nsplit) {
-  return run_tc(ctx, w->type, w->qs, w->d, w->nkb, x, bias, res, act, y, M, w->rows, w->cols, nsplit);
+  return run_tc(ctx, w->type, wsrc_of(w), x, bias, res, act, y, M, w->rows, w->cols, nsplit);
 }
 
 int launch_gemm_tc_ex(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x, const __nv_bfloat16 *xhi,
                       const __nv_bfloat16 *xlo, const float *bias, const float *res, int act, float *y, BfOut ybf, int64_t M,
                       int nsplit, PartIn *defer) {
-  return run_tc(ctx, w->type, w->qs, w->d, w->nkb, x, bias, res, act, y, M, w->rows, w->cols, nsplit, xhi, xlo, ybf, defer);
+  return run_tc(ctx, w->type, wsrc_of(w), x, bias, res, act, y, M, w->rows, w->cols, nsplit, xhi, xlo, ybf, defer);
 }
 
 int launch_relu_matmul_tc(caten_b200_ctx *ctx, const float *a, const float *b, float *c, int64_t M, int64_t K, int64_t N, int nsplit) {
-  return run_tc(ctx, WT_F32_T, b, nullptr, 0, a, nullptr, nullptr, CATEN_B200_ACT_RELU, c, M, N, K, nsplit);
+  return run_tc(ctx, WT_F32_T, WSrc{b, nullptr, nullptr, nullptr, 0}, a, nullptr, nullptr, CATEN_B200_ACT_RELU, c, M, N, K, nsplit);
 }
 
 }  // namespace cb

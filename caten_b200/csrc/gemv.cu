@@ -3,13 +3,15 @@
 // with 128-bit loads and unpacked in registers; x lives in registers (quantised types) or
 // shared memory (fp32/fp16 weights).  fp32 accumulation throughout.
 #include "common.cuh"
+#include "blocks32.cuh"
 #include "gemv_blocks.cuh"
 
 namespace cb {
 
 struct GemvArgs {
   const void *qs;
-  const __half *d;
+  const __half *d, *m;   // scales; minima (Q4_1, Q5_1)
+  const uint32_t *qh;    // fifth code bits (Q5_0, Q5_1)
   const float *x, *bias, *res;
   float *y;
   int act, N, nkb, G;
@@ -42,7 +44,8 @@ __global__ void __launch_bounds__(GEMV_MAX_THREADS) gemv_blocked_kernel(GemvArgs
   // alternate between two shared-memory buffers, so there is one barrier per iteration and the
   // packed stream stays in flight across it.
   uint32_t qn[RI][W];
-  float scn[RI];
+  float scn[RI], mnn[RI];
+  uint32_t qhn[RI];
   auto load = [&](int64_t base) {
 #pragma unroll
     for (int i = 0; i < RI; ++i) {
@@ -55,6 +58,8 @@ __global__ void __launch_bounds__(GEMV_MAX_THREADS) gemv_blocked_kernel(GemvArgs
         qn[i][4 * j] = v.x; qn[i][4 * j + 1] = v.y; qn[i][4 * j + 2] = v.z; qn[i][4 * j + 3] = v.w;
       }
       scn[i] = ok ? __half2float(a.d[bidx]) : 0.0f;
+      if (BLK::HAS_M) mnn[i] = ok ? __half2float(a.m[bidx]) : 0.0f;
+      if (BLK::HAS_QH) qhn[i] = ok ? a.qh[bidx] : 0u;
     }
   };
   int64_t base = (int64_t)blockIdx.x * rows_per_iter;
@@ -73,11 +78,13 @@ __global__ void __launch_bounds__(GEMV_MAX_THREADS) gemv_blocked_kernel(GemvArgs
   }
   int buf = 0;
   for (; base < a.N; base += stride) {
-    uint32_t q[RI][W];
-    float sc[RI];
+    uint32_t q[RI][W], qhc[RI];
+    float sc[RI], mn[RI];
 #pragma unroll
     for (int i = 0; i < RI; ++i) {
       sc[i] = scn[i];
+      mn[i] = BLK::HAS_M ? mnn[i] : 0.0f;
+      qhc[i] = BLK::HAS_QH ? qhn[i] : 0u;
 #pragma unroll
       for (int j = 0; j < W; ++j) q[i][j] = qn[i][j];
     }
@@ -85,7 +92,12 @@ __global__ void __launch_bounds__(GEMV_MAX_THREADS) gemv_blocked_kernel(GemvArgs
     float *rb = red + buf * rows_per_iter * nkb;
     if (active) {
 #pragma unroll
-      for (int i = 0; i < RI; ++i) rb[(i * G + ro) * nkb + kb] = blk.dot(q[i], sc[i]);
+      for (int i = 0; i < RI; ++i) {
+        float r;
+        if constexpr (BLK::HAS_M || BLK::HAS_QH) r = blk.dotx(q[i], sc[i], mn[i], qhc[i]);
+        else r = blk.dot(q[i], sc[i]);
+        rb[(i * G + ro) * nkb + kb] = r;
+      }
     }
     __syncthreads();
     for (int r = warp; r < rows_per_iter; r += nwarps) {
@@ -225,16 +237,21 @@ int launch_gemv(caten_b200_ctx *ctx, const caten_b200_weight *w, const float *x,
                 const float *res, int act, float *y) {
   if (w->rows > 0x7fffffff || w->cols > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv: dimension too large");
   const int N = (int)w->rows, K = (int)w->cols;
-  if (w->type == CATEN_B200_Q4_0 || w->type == CATEN_B200_Q8_0) {
+  if (type_is_packed(w->type)) {
     GemvArgs a;
-    a.qs = w->qs; a.d = w->d; a.x = x; a.bias = bias; a.res = res; a.y = y; a.act = act; a.N = N;
+    a.qs = w->qs; a.d = w->d; a.m = w->m; a.qh = w->qh; a.x = x; a.bias = bias; a.res = res; a.y = y; a.act = act; a.N = N;
     a.nkb = (int)w->nkb;
     if (a.nkb > GEMV_MAX_THREADS) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv: cols=%d too wide (max %d)", K, GEMV_MAX_THREADS * 32);
     a.G = GEMV_MAX_THREADS / a.nkb;
     // few rows: keep every SM busy with single-row-group iterations; many rows: 4 loads in flight
     const bool deep = (int64_t)N >= (int64_t)a.G * 4 * ctx->sm_count;
-    if (w->type == CATEN_B200_Q4_0) return deep ? launch_blocked<BlkQ4, 4>(ctx, a) : launch_blocked<BlkQ4, 1>(ctx, a);
-    return deep ? launch_blocked<BlkQ8, 4>(ctx, a) : launch_blocked<BlkQ8, 1>(ctx, a);
+    switch (w->type) {
+      case CATEN_B200_Q4_0: return deep ? launch_blocked<BlkQ4, 4>(ctx, a) : launch_blocked<BlkQ4, 1>(ctx, a);
+      case CATEN_B200_Q4_1: return deep ? launch_blocked<BlkQ41, 4>(ctx, a) : launch_blocked<BlkQ41, 1>(ctx, a);
+      case CATEN_B200_Q5_0: return deep ? launch_blocked<BlkQ5<false>, 4>(ctx, a) : launch_blocked<BlkQ5<false>, 1>(ctx, a);
+      case CATEN_B200_Q5_1: return deep ? launch_blocked<BlkQ5<true>, 4>(ctx, a) : launch_blocked<BlkQ5<true>, 1>(ctx, a);
+      default: return deep ? launch_blocked<BlkQ8, 4>(ctx, a) : launch_blocked<BlkQ8, 1>(ctx, a);
+    }
   }
   const size_t smem = (size_t)K * sizeof(float);
   if (smem > 160 * 1024) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemv: cols=%d too wide", K);

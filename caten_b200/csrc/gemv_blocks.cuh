@@ -17,6 +17,7 @@ namespace cb {
 // scale.  Nibbles of the top byte (bits 24..31 overlap the exponent field) are taken from
 // w >> 8.  Valid for |x| < 2^62; FMA with subnormal operands runs at full rate.
 struct BlkQ4 {
+  static constexpr bool HAS_M = false, HAS_QH = false;
   static constexpr int WORDS = 4;
   float xs[32];
   float c0;
@@ -64,6 +65,7 @@ struct BlkQ4 {
 // Q8_0: sign-extended byte -> float -> FMA; (float)q * scale is exact in fp32 (8 + 11 bits), so
 // scaling the 32-term sum once per block only changes where the roundings of the sum fall.
 struct BlkQ8 {
+  static constexpr bool HAS_M = false, HAS_QH = false;
   static constexpr int WORDS = 8;
   float xs[32];
   __device__ __forceinline__ void prep(const float *xv) {
@@ -89,8 +91,65 @@ struct BlkQ8 {
   }
 };
 
+// Q4_1: w = q * d + m.  The nibble arithmetic of BlkQ4 without the -8 offset; the minimum enters
+// once per block as m * sum(x).
+struct BlkQ41 {
+  static constexpr bool HAS_M = true, HAS_QH = false;
+  static constexpr int WORDS = 4;
+  BlkQ4 nib;
+  float sumx;
+  __device__ __forceinline__ void prep(const float *xv) {
+    nib.prep(xv);
+    nib.c0 = 0.0f;
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) sum += xv[j];
+    sumx = sum;
+  }
+  __device__ __forceinline__ float dotx(const uint32_t *w, float scale, float mn, uint32_t) const {
+    return nib.dot(w, scale) + mn * sumx;
+  }
+};
+
+// Q5_0 (w = (q - 16) * d) and Q5_1 (w = q * d + m): code = nibble | bit e of qh << 4, converted
+// with an integer-to-float instruction per weight.
+template <bool WITH_MIN>
+struct BlkQ5 {
+  static constexpr bool HAS_M = WITH_MIN, HAS_QH = true;
+  static constexpr int WORDS = 4;
+  float xs[32];
+  float sumx;
+  __device__ __forceinline__ void prep(const float *xv) {
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      xs[j] = xv[j];
+      sum += xv[j];
+    }
+    sumx = sum;
+  }
+  __device__ __forceinline__ float dotx(const uint32_t *w, float scale, float mn, uint32_t qh) const {
+    constexpr int OFF = WITH_MIN ? 0 : 16;
+    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int j = 4 * i + b;  // byte j: elements j and j + 16
+        const int lo = (int)((w[i] >> (8 * b)) & 15u) | (int)(((qh >> j) & 1u) << 4);
+        const int hi = (int)((w[i] >> (8 * b + 4)) & 15u) | (int)(((qh >> (j + 16)) & 1u) << 4);
+        a0 = fmaf(xs[j], (float)(lo - OFF), a0);
+        a1 = fmaf(xs[j + 16], (float)(hi - OFF), a1);
+      }
+    }
+    const float r = (a0 + a1) * scale;
+    return WITH_MIN ? r + mn * sumx : r;
+  }
+};
+
 // fp16 weights: 32 halves = 16 words
 struct BlkF16 {
+  static constexpr bool HAS_M = false, HAS_QH = false;
   static constexpr int WORDS = 16;
   float xs[32];
   __device__ __forceinline__ void prep(const float *xv) {
@@ -126,6 +185,7 @@ struct BlkF16 {
 
 // fp32 weights: 32 floats = 32 words
 struct BlkF32 {
+  static constexpr bool HAS_M = false, HAS_QH = false;
   static constexpr int WORDS = 32;
   float xs[32];
   __device__ __forceinline__ void prep(const float *xv) {

@@ -1,47 +1,67 @@
 // Small HBM-bound kernels of the GPT-2 graph: weight re-layout and dequantisation, LayerNorm,
 // token+position embedding gather, arg-max.
 #include "common.cuh"
+#include "blocks32.cuh"
 
 namespace cb {
 
 // ---------------------------------------------------------------------------------------------
-// GGUF blocks -> (codes, scales) arrays.  Q8_0 block = fp16 scale + 32 int8 (34 B); Q4_0 block =
-// fp16 scale + 16 bytes of nibbles (18 B) (external/gguf/dequantize.lisp:40-53 reads the same
-// fields in the same order).  The bytes are copied unchanged; only their placement differs.
+// GGUF blocks -> separate arrays of codes, scales, minima and fifth bits.  A block in the file is
+// [fp16 d][fp16 m (Q4_1, Q5_1)][u32 qh (Q5_0, Q5_1)][codes: 32 int8 (Q8_0) or 16 bytes of nibbles]
+// (external/gguf/dequantize.lisp:40-53 reads the Q8_0 fields in the same order).  The bytes are
+// copied unchanged; only their placement differs.
 // ---------------------------------------------------------------------------------------------
-template <int QBYTES>
+template <int TYPE>
 __global__ void repack_kernel(const uint8_t *__restrict__ src, int64_t nblocks, uint8_t *__restrict__ qs,
-                              __half *__restrict__ d) {
+                              __half *__restrict__ d, __half *__restrict__ m, uint32_t *__restrict__ qh) {
+  constexpr int QBYTES = type_code_bytes(TYPE);
   const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= nblocks) return;
-  const uint8_t *p = src + b * (QBYTES + 2);
-  const uint16_t hs = (uint16_t)p[0] | ((uint16_t)p[1] << 8);
-  d[b] = __ushort_as_half(hs);
+  const uint8_t *p = src + b * type_block_bytes(TYPE);
+  d[b] = __ushort_as_half((uint16_t)((uint16_t)p[0] | ((uint16_t)p[1] << 8)));
+  p += 2;
+  if (type_has_min(TYPE)) {
+    m[b] = __ushort_as_half((uint16_t)((uint16_t)p[0] | ((uint16_t)p[1] << 8)));
+    p += 2;
+  }
+  if (type_has_qh(TYPE)) {
+    qh[b] = (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
+    p += 4;
+  }
   uint32_t w[QBYTES / 4];
 #pragma unroll
   for (int i = 0; i < QBYTES / 4; ++i)
-    w[i] = (uint32_t)p[2 + 4 * i] | ((uint32_t)p[3 + 4 * i] << 8) | ((uint32_t)p[4 + 4 * i] << 16) |
-           ((uint32_t)p[5 + 4 * i] << 24);
+    w[i] = (uint32_t)p[4 * i] | ((uint32_t)p[4 * i + 1] << 8) | ((uint32_t)p[4 * i + 2] << 16) | ((uint32_t)p[4 * i + 3] << 24);
   uint4 *o = reinterpret_cast<uint4 *>(qs + b * QBYTES);
 #pragma unroll
   for (int i = 0; i < QBYTES / 16; ++i) o[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
 }
 
-int launch_repack(caten_b200_ctx *ctx, int type, const uint8_t *d_blocks, int64_t nblocks, void *qs, __half *d) {
+int launch_repack(caten_b200_ctx *ctx, int type, const uint8_t *d_blocks, int64_t nblocks, void *qs, __half *d, __half *m,
+                  uint32_t *qh) {
   const int threads = 256;
   const int64_t grid = (nblocks + threads - 1) / threads;
   if (grid > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "repack: too many blocks");
-  if (type == CATEN_B200_Q4_0)
-    repack_kernel<16><<<(unsigned)grid, threads, 0, ctx->stream>>>(d_blocks, nblocks, (uint8_t *)qs, d);
-  else
-    repack_kernel<32><<<(unsigned)grid, threads, 0, ctx->stream>>>(d_blocks, nblocks, (uint8_t *)qs, d);
+#define REPACK_CASE(T) \
+  case T: repack_kernel<T><<<(unsigned)grid, threads, 0, ctx->stream>>>(d_blocks, nblocks, (uint8_t *)qs, d, m, qh); break
+  switch (type) {
+    REPACK_CASE(CATEN_B200_Q4_0);
+    REPACK_CASE(CATEN_B200_Q4_1);
+    REPACK_CASE(CATEN_B200_Q5_0);
+    REPACK_CASE(CATEN_B200_Q5_1);
+    REPACK_CASE(CATEN_B200_Q8_0);
+    default: return fail(ctx, CATEN_B200_EUNSUPPORTED, "repack: type %d", type);
+  }
+#undef REPACK_CASE
   CB_LAUNCH_CHECK(ctx, "repack_kernel");
   return 0;
 }
 
-// w = (float)code * (float)scale, one rounded fp32 multiply (external/gguf/dequantize.lisp:51).
+// Q8_0: w = (float)code * (float)scale, one rounded fp32 multiply (external/gguf/dequantize.lisp:51);
+// the nibble formats: the formulas of blocks32.cuh.
 __global__ void dequant_kernel(int type, const void *__restrict__ qs, const __half *__restrict__ d,
-                               int64_t n, float *__restrict__ out) {
+                               const __half *__restrict__ m, const uint32_t *__restrict__ qh, int64_t n,
+                               float *__restrict__ out) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int64_t blk = i >> 5;
@@ -55,8 +75,9 @@ __global__ void dequant_kernel(int type, const void *__restrict__ qs, const __ha
     out[i] = (float)q * __half2float(d[blk]);
   } else {
     const uint8_t byte = ((const uint8_t *)qs)[blk * 16 + (j & 15)];
-    const int q = (j < 16 ? (byte & 0x0F) : (byte >> 4)) - 8;
-    out[i] = (float)q * __half2float(d[blk]);
+    int q = j < 16 ? (byte & 0x0F) : (byte >> 4);
+    if (type_has_qh(type)) q |= (int)((qh[blk] >> j) & 1u) << 4;
+    out[i] = nibble_value_rt(type, q, __half2float(d[blk]), type_has_min(type) ? __half2float(m[blk]) : 0.0f);
   }
 }
 
@@ -65,7 +86,7 @@ int launch_dequant(caten_b200_ctx *ctx, const caten_b200_weight *w, float *out) 
   const int threads = 256;
   const int64_t grid = (n + threads - 1) / threads;
   if (grid > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "dequant: tensor too large");
-  dequant_kernel<<<(unsigned)grid, threads, 0, ctx->stream>>>(w->type, w->qs, w->d, n, out);
+  dequant_kernel<<<(unsigned)grid, threads, 0, ctx->stream>>>(w->type, w->qs, w->d, w->m, w->qh, n, out);
   CB_LAUNCH_CHECK(ctx, "dequant_kernel");
   return 0;
 }

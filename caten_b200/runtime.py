@@ -51,6 +51,11 @@ class B200Weight:
     def packed_nbytes(self) -> int:
         return int(L.load().caten_b200_weight_nbytes(self.ggml_type, self.rows, self.cols))
 
+    @property
+    def device_nbytes(self) -> int:
+        """Bytes held in device memory: ``packed_nbytes`` when the kernels read the format packed."""
+        return int(L.load().caten_b200_weight_device_nbytes(self.handle))
+
     def dequantize(self) -> np.ndarray:
         """fp32 [rows, cols], the values external/gguf/dequantize.lisp:14-53 would produce."""
         rt = self.runtime

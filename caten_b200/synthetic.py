@@ -14,9 +14,10 @@ from dataclasses import dataclass
 
 import numpy as np
 
-GGML_F32, GGML_F16, GGML_Q4_0, GGML_Q8_0 = 0, 1, 2, 8
-BLOCK_BYTES = {GGML_Q4_0: 18, GGML_Q8_0: 34}
-TYPE_IDS = {"f32": GGML_F32, "f16": GGML_F16, "q4_0": GGML_Q4_0, "q8_0": GGML_Q8_0}
+GGML_F32, GGML_F16, GGML_Q4_0, GGML_Q4_1, GGML_Q5_0, GGML_Q5_1, GGML_Q8_0 = 0, 1, 2, 3, 6, 7, 8
+BLOCK_BYTES = {GGML_Q4_0: 18, GGML_Q4_1: 20, GGML_Q5_0: 22, GGML_Q5_1: 24, GGML_Q8_0: 34}
+TYPE_IDS = {"f32": GGML_F32, "f16": GGML_F16, "q4_0": GGML_Q4_0, "q4_1": GGML_Q4_1, "q5_0": GGML_Q5_0, "q5_1": GGML_Q5_1,
+            "q8_0": GGML_Q8_0}
 
 
 @dataclass(frozen=True)
@@ -87,6 +88,18 @@ def _rand_packed(rng: np.random.Generator, rows: int, cols: int, wtype: str, std
         scales = (np.abs(rng.standard_normal(nb, dtype=np.float32)) * np.float32(std / 8)).astype("<f2")
         out[:, 0:2] = scales.reshape(nb, 1).view(np.uint8)
         return Packed(GGML_Q4_0, rows, cols, out.reshape(-1))
+    if wtype in ("q4_1", "q5_0", "q5_1"):
+        # uniform code bytes (and fifth bits); scale = |N(0, std)| / half the code range; the _1
+        # formats get a minimum that centres the codes: m = -(range / 2) * d + N(0, std / 16)
+        t = TYPE_IDS[wtype]
+        levels = 16 if wtype == "q4_1" else 32
+        out = rng.integers(0, 256, size=(nb, BLOCK_BYTES[t]), dtype=np.uint8)
+        d = (np.abs(rng.standard_normal(nb, dtype=np.float32)) * np.float32(std / (levels / 2))).astype("<f2")
+        out[:, 0:2] = d.reshape(nb, 1).view(np.uint8)
+        if wtype != "q5_0":
+            m = (-(levels / 2) * d.astype(np.float32) + rng.standard_normal(nb, dtype=np.float32) * np.float32(std / 16)).astype("<f2")
+            out[:, 2:4] = m.reshape(nb, 1).view(np.uint8)
+        return Packed(t, rows, cols, out.reshape(-1))
     raise ValueError(wtype)
 
 
@@ -95,7 +108,7 @@ def synth_state_dict(p: GPT2Params, wtype: str = "f32", seed: int = 0, max_seq_l
     """Draw order (fixed): wte, wpe, then per layer c_attn, attn.c_proj, mlp.c_fc, mlp.c_proj
     (weight, then bias/affine extras when ``trivial_affine`` is False), then lm_head.
 
-    wtype "f32": every matrix ~ N(0, 0.02).  "q8_0"/"q4_0": the five kinds of Linear weight are
+    wtype "f32": every matrix ~ N(0, 0.02).  "q8_0"/"q4_0"/"q4_1"/"q5_0"/"q5_1": the five kinds of Linear weight are
     packed blocks; embeddings, LayerNorm parameters and biases stay fp32.
     ``trivial_affine``: biases 0, LayerNorm gamma 1 / beta 0 (the benchmark configurations);
     False draws them at random so tests exercise those terms.  ``weight_std`` scales the fp32

@@ -90,10 +90,11 @@ void *caten_b200_stream(caten_b200_ctx *ctx);
 /* ---- weights ----------------------------------------------------------------------------------
  * Replaces external/gguf/tensor-info.lisp:71-77,104-120 + external/gguf/dequantize.lisp:14-53,
  * which dequantise every tensor to a fp32 Lisp array at load: here the raw GGUF blocks are
- * uploaded as they are in the file and stay packed in HBM (Q8_0: 34-byte blocks, Q4_0: 18-byte
- * blocks; on the device codes and fp16 scales are kept in two arrays so code loads are 16-byte
- * aligned — same bytes, same values). `cols` (the `in` dimension) must be a multiple of 32 for
- * the quantised types. */
+ * uploaded as they are in the file and stay packed in HBM (Q8_0: 34-byte blocks, Q4_0: 18, Q4_1:
+ * 20, Q5_0: 22, Q5_1: 24; on the device codes, fp16 scales, fp16 minima and fifth code bits are
+ * kept in separate arrays so code loads are 16-byte aligned — same bytes, same values). The
+ * 256-weight K formats are expanded to fp32 at upload. `cols` (the `in` dimension) must be a
+ * multiple of the block size (32; 256 for the K formats). */
 int caten_b200_weight_upload(caten_b200_ctx *ctx, int ggml_type, const void *h_blocks, int64_t rows,
                              int64_t cols, caten_b200_weight **w);
 /* Same, from raw blocks already in device memory (e.g. after an NCCL broadcast of the file's
@@ -104,8 +105,12 @@ int caten_b200_weight_upload_device(caten_b200_ctx *ctx, int ggml_type, const vo
 int caten_b200_weight_free(caten_b200_ctx *ctx, caten_b200_weight *w);
 /* Number of bytes of a rows x cols tensor in GGUF block form; -1 for an unknown type. */
 int64_t caten_b200_weight_nbytes(int ggml_type, int64_t rows, int64_t cols);
+/* Bytes the uploaded weight occupies in device memory: the file's bytes for the formats the
+ * kernels read packed, rows*cols*4 for a format expanded at upload; -1 for a NULL handle. */
+int64_t caten_b200_weight_device_nbytes(const caten_b200_weight *w);
 /* dequantize (external/gguf/dequantize.lisp:8): writes rows*cols fp32 values, bit-identical to
- * (float)code * (float)scale, to d_out. */
+ * (float)code * (float)scale (Q8_0, Q4_0; the other block formats: to the Python `gguf` package's
+ * dequantiser), to d_out. */
 int caten_b200_weight_dequant(caten_b200_ctx *ctx, const caten_b200_weight *w, float *d_out);
 
 /* ---- GGUF files ------------------------------------------------------------------------------------

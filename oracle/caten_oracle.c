@@ -169,13 +169,17 @@ float orc_half_to_float(uint16_t h) {
 }
 
 /* ggml type ids as stored in GGUF tensor infos (external/gguf/tensor-info.lisp:3-34). */
-enum { ORC_F32 = 0, ORC_F16 = 1, ORC_Q4_0 = 2, ORC_Q8_0 = 8 };
+enum { ORC_F32 = 0, ORC_F16 = 1, ORC_Q4_0 = 2, ORC_Q4_1 = 3, ORC_Q5_0 = 6, ORC_Q5_1 = 7, ORC_Q8_0 = 8 };
 
 /* external/gguf/dequantize.lisp:14-53.  Q8_0: 34-byte blocks = fp16 scale + 32 int8,
  * w = (float)q * (float)scale.  Q4_0 is not implemented by the reference
  * (tensor-info.lisp:41 signals "Not ready"); layout per ggml: 18-byte blocks = fp16 scale +
  * 16 bytes, byte j holds element j in its low nibble and element j+16 in its high nibble,
- * w = (float)(nibble - 8) * (float)scale.  n = number of elements (multiple of 32 for Q*). */
+ * w = (float)(nibble - 8) * (float)scale.  Q4_1 (d, m, 16 bytes: w = q*d + m), Q5_0 (d, 4 bytes
+ * of fifth bits, 16 bytes: w = (q - 16)*d) and Q5_1 (d, m, fifth bits, 16 bytes: w = q*d + m)
+ * are ggml's other 32-weight formats, which the reference lists (tensor-info.lisp:3-34) but does
+ * not implement; each value is a rounded product followed by a rounded sum, as the Python `gguf`
+ * package computes it.  n = number of elements (multiple of 32 for Q*). */
 int orc_dequant(int ggml_type, const uint8_t *src, int64_t n, float *out) {
   if (ggml_type == ORC_F32) {
     memcpy(out, src, (size_t)n * 4);
@@ -197,6 +201,29 @@ int orc_dequant(int ggml_type, const uint8_t *src, int64_t n, float *out) {
       for (int i = 0; i < 16; ++i) {
         out[b * 32 + i] = (float)((int)(blk[2 + i] & 0x0F) - 8) * sc;
         out[b * 32 + i + 16] = (float)((int)(blk[2 + i] >> 4) - 8) * sc;
+      }
+    }
+  } else if (ggml_type == ORC_Q4_1 || ggml_type == ORC_Q5_0 || ggml_type == ORC_Q5_1) {
+    if (n % 32) return 2;
+    const int has_m = ggml_type != ORC_Q5_0, has_h = ggml_type != ORC_Q4_1;
+    const int head = 2 + 2 * has_m + 4 * has_h;
+    for (int64_t b = 0; b < n / 32; ++b) {
+      const uint8_t *blk = src + b * (head + 16);
+      const float sc = orc_half_to_float((uint16_t)(blk[0] | blk[1] << 8));
+      const float mn = has_m ? orc_half_to_float((uint16_t)(blk[2] | blk[3] << 8)) : 0.0f;
+      const uint8_t *h = blk + 2 + 2 * has_m;
+      const uint32_t qh = has_h ? ((uint32_t)h[0] | (uint32_t)h[1] << 8 | (uint32_t)h[2] << 16 | (uint32_t)h[3] << 24) : 0u;
+      const uint8_t *qs = blk + head;
+      for (int e = 0; e < 32; ++e) {
+        const int nib = e < 16 ? (qs[e] & 0x0F) : (qs[e - 16] >> 4);
+        const int q = nib | (int)((qh >> e) & 1u) << 4;
+        volatile float prod;  /* keeps the product and the sum separately rounded at any -O level */
+        if (has_m) {
+          prod = (float)q * sc;
+          out[b * 32 + e] = prod + mn;
+        } else {
+          out[b * 32 + e] = (float)(q - 16) * sc;
+        }
       }
     }
   } else {

@@ -57,6 +57,29 @@ def gguf_fixtures():
     np.savez_compressed(os.path.join(OUT, "gguf_dequant.npz"), **out)
 
 
+def gguf_nibble_formats():
+    """Q4_1, Q5_0 and Q5_1 blocks (formats the reference lists, external/gguf/tensor-info.lisp:3-34,
+    without implementing them) dequantised by the Python `gguf` package: random blocks, and blocks
+    whose scale / minimum run through the fp16 classes (zero, subnormal, normal, negative, largest)."""
+    from gguf import GGMLQuantizationType as GT
+    from gguf.quants import dequantize
+
+    rng = np.random.Generator(np.random.PCG64(11))
+    out = {}
+    for name, gt in (("q4_1", GT.Q4_1), ("q5_0", GT.Q5_0), ("q5_1", GT.Q5_1)):
+        bb = S.BLOCK_BYTES[S.TYPE_IDS[name]]
+        p = S._rand_packed(rng, 6, 96, name)
+        out[f"rand_{name}_raw"] = p.data
+        out[f"rand_{name}"] = dequantize(p.data.reshape(-1, bb), gt).astype(np.float32).reshape(6, 96)
+        raw = rng.integers(0, 256, size=(6, bb), dtype=np.uint8)
+        raw[:, 0:2] = np.array([0.0, 6e-8, 3e-5, 1.0, -2.5, 2047.0], dtype="<f2").reshape(6, 1).view(np.uint8)
+        if name != "q5_0":
+            raw[:, 2:4] = np.array([1.5, -6e-8, 0.0, -3e-5, 65504.0, -100.0], dtype="<f2").reshape(6, 1).view(np.uint8)
+        out[f"edge_{name}_raw"] = raw.reshape(-1)
+        out[f"edge_{name}"] = dequantize(raw, gt).astype(np.float32).reshape(6, 32)
+    np.savez_compressed(os.path.join(OUT, "gguf_dequant_nibble.npz"), **out)
+
+
 def torch_ops():
     g = torch.Generator().manual_seed(11)
     out = {}
@@ -186,7 +209,7 @@ def gpt2_tiny():
 
 if __name__ == "__main__":
     only = sys.argv[1:]
-    for fn in (gguf_fixtures, torch_ops, gpt2_tiny, attn_block, llama_ops):
+    for fn in (gguf_fixtures, gguf_nibble_formats, torch_ops, gpt2_tiny, attn_block, llama_ops):
         if not only or fn.__name__ in only:
             fn()
     print("wrote", sorted(f for f in os.listdir(OUT) if f.endswith(".npz")))

@@ -87,6 +87,15 @@ def test_tiny_bf16_parity(rt, oracle, wtype):
     run_parity(rt, oracle, TINY, wtype, "bf16", B=6, prompt_len=9, steps=4, T=48, logit_tol=2e-2, rel=True)
 
 
+@pytest.mark.parametrize("wtype", ["q4_1", "q5_0", "q5_1"])
+def test_tiny_other_packed_formats(rt, oracle, wtype):
+    """The other 32-weight GGUF formats are consumed packed by the same kernels: one sequence (GEMV, one
+    kernel per operation), the exact fp32 GEMM, and the tensor-core GEMM."""
+    run_parity(rt, oracle, TINY, wtype, "fp32", B=1, prompt_len=3, steps=5, T=32, logit_tol=1e-3)
+    run_parity(rt, oracle, TINY, wtype, "fp32", B=5, prompt_len=7, steps=3, T=32, logit_tol=1e-3)
+    run_parity(rt, oracle, TINY, wtype, "bf16x3", B=6, prompt_len=9, steps=4, T=48, logit_tol=1e-3)
+
+
 def test_gpt2_small_width_one_layer(rt, oracle):
     """Real GPT-2 small widths (d=768, 12 heads, d_ff=3072), one layer, reduced vocabulary."""
     p = S.GPT2Params(n_layers=1, n_heads=12, dim=768, vocab_size=4099)

@@ -1,8 +1,9 @@
-"""GPU tests of the GGUF block formats that are expanded to fp32 at upload (Q4_1, Q5_0, Q5_1, Q2_K,
-Q3_K, Q4_K, Q5_K, Q6_K): the device expansion must give, bit for bit, what the Python `gguf` package's
+"""GPU tests of the GGUF block formats beyond Q4_0 / Q8_0: Q4_1, Q5_0 and Q5_1 stay packed in device
+memory and are unpacked inside the GEMV / GEMM kernels; Q2_K, Q3_K, Q4_K, Q5_K and Q6_K are expanded to
+fp32 at upload.  Either way the weight's values must be, bit for bit, what the Python `gguf` package's
 dequantiser gives (the library the reference's own GGUF tests use as their oracle,
 source/test-suite/external/test-gguf.lisp:53-75), and a Linear over such a weight must match the
-product with those values."""
+product with those values on every kernel path."""
 import numpy as np
 import pytest
 
@@ -44,6 +45,8 @@ def test_expansion_matches_gguf_package_bit_for_bit(rt, t):
     got = w.dequantize()
     np.testing.assert_array_equal(got.view(np.uint32), want.reshape(rows, cols).view(np.uint32))
     assert w.packed_nbytes == raw.size
+    # the 32-weight formats keep the file's bytes on the device, the K formats hold fp32
+    assert w.device_nbytes == (raw.size if per == 32 else rows * cols * 4)
     # one sequence (fp32 GEMV) and a small batch (tensor cores, split bf16)
     x1 = rng.standard_normal((1, cols), dtype=np.float32)
     y1 = rt.linear(w, rt.transfer_from_array(x1)).numpy()
@@ -53,6 +56,58 @@ def test_expansion_matches_gguf_package_bit_for_bit(rt, t):
     y8 = rt.linear(w, rt.transfer_from_array(x8), precision=L.PREC_BF16X3).numpy()
     ref8 = x8.astype(np.float64) @ want.reshape(rows, cols).T.astype(np.float64)
     np.testing.assert_allclose(y8, ref8, atol=5e-5 * np.abs(ref8).max() + 1e-5, rtol=0)   # split bf16: about 2^-16 of the operands' scale
+    w.close()
+
+
+PACKED = {"q4_1": L.Q4_1, "q5_0": L.Q5_0, "q5_1": L.Q5_1}
+
+
+@pytest.mark.parametrize("name", sorted(PACKED))
+def test_packed_nibble_formats_golden_and_edge_scales(rt, golden, name):
+    """Committed `gguf`-package vectors, including scales / minima from every fp16 class."""
+    g = golden["gguf_dequant_nibble"]
+    for kind in ("rand", "edge"):
+        want = g[f"{kind}_{name}"]
+        w = rt.upload_weight(S.Packed(PACKED[name], want.shape[0], want.shape[1], g[f"{kind}_{name}_raw"]))
+        np.testing.assert_array_equal(w.dequantize().view(np.uint32), want.view(np.uint32))
+        w.close()
+
+
+@pytest.mark.parametrize("name", sorted(PACKED))
+@pytest.mark.parametrize("rows,cols", [(37, 512), (1600, 1600), (130, 6400)])
+def test_packed_nibble_formats_on_every_linear_path(rt, oracle, name, rows, cols):
+    """GEMV (1 and 3 rows), the exact fp32 GEMM, and the tensor-core GEMM in both precisions with row counts
+    that give one narrow tile, a ragged tile and several tiles; weight rows not a multiple of the 128-row tile."""
+    rng = np.random.Generator(np.random.PCG64(rows + cols))
+    p = S._rand_packed(rng, rows, cols, name, 0.05)
+    wf = oracle.dequant(p.ggml_type, p.data, rows * cols).reshape(rows, cols)
+    w = rt.upload_weight(p)
+    assert w.device_nbytes == p.data.size
+    np.testing.assert_array_equal(w.dequantize().view(np.uint32), wf.view(np.uint32))
+    bias = rng.standard_normal(rows, dtype=np.float32)
+    d_bias = rt.transfer_from_array(bias)
+    w64 = wf.T.astype(np.float64)
+    for M in (1, 3):
+        x = rng.standard_normal((M, cols), dtype=np.float32)
+        y = rt.linear(w, rt.transfer_from_array(x), d_bias).numpy()
+        ref = x.astype(np.float64) @ w64 + bias
+        np.testing.assert_allclose(y, ref, atol=3e-6 * np.abs(ref).max() + 1e-5, rtol=0)
+    for M in (8, 70):
+        x = rng.standard_normal((M, cols), dtype=np.float32)
+        d_x = rt.transfer_from_array(x)
+        ref = x.astype(np.float64) @ w64 + bias
+        y32 = rt.linear(w, d_x, d_bias, precision=L.PREC_FP32).numpy()
+        # the exact path: the oracle's own accumulation order over the same dequantised values
+        np.testing.assert_array_equal(y32.view(np.uint32), oracle.linear(x, wf, bias).view(np.uint32))
+        y3 = rt.linear(w, d_x, d_bias, precision=L.PREC_BF16X3).numpy()
+        np.testing.assert_allclose(y3, ref, atol=5e-5 * np.abs(ref).max() + 1e-5, rtol=0)
+        y1 = rt.linear(w, d_x, d_bias, precision=L.PREC_BF16).numpy()
+        np.testing.assert_allclose(y1, ref, atol=2e-2 * np.abs(ref).max(), rtol=0)
+    if cols <= 1600:
+        x = rng.standard_normal((300, cols), dtype=np.float32)
+        ref = x.astype(np.float64) @ w64 + bias
+        y3 = rt.linear(w, rt.transfer_from_array(x), d_bias, precision=L.PREC_BF16X3).numpy()
+        np.testing.assert_allclose(y3, ref, atol=5e-5 * np.abs(ref).max() + 1e-5, rtol=0)
     w.close()
 
 

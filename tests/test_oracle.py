@@ -29,6 +29,16 @@ def test_dequant_q4_0_scale_edge_cases(oracle, golden):
     np.testing.assert_array_equal(got.view(np.uint32), g["edge_q4_0"].view(np.uint32))
 
 
+@pytest.mark.parametrize("name,t", [("q4_1", 3), ("q5_0", 6), ("q5_1", 7)])
+def test_dequant_other_nibble_formats_bit_exact(oracle, golden, name, t):
+    """Q4_1 / Q5_0 / Q5_1 against the Python `gguf` package: random blocks and the fp16 edge classes."""
+    g = golden["gguf_dequant_nibble"]
+    for kind in ("rand", "edge"):
+        want = g[f"{kind}_{name}"]
+        got = oracle.dequant(t, g[f"{kind}_{name}_raw"], want.size).reshape(want.shape)
+        np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
 def test_half_to_float_all_bit_patterns(oracle):
     h = np.arange(65536, dtype=np.uint16)
     want = h.view(np.float16).astype(np.float32)
