@@ -22,7 +22,7 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libcaten_b200.so")
-SOURCES = ["capi.cu", "decode_small.cu", "kernels_misc.cu", "gemv.cu", "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "attention_tc.cu", "gguf.cu", "expr.cu", "dequant_extra.cu", "sample.cu", "dist.cu", "llama_ops.cu"]
+SOURCES = ["capi.cu", "decode_small.cu", "kernels_misc.cu", "gemv.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_dense.cu", "attention.cu", "attention_tc.cu", "gguf.cu", "expr.cu", "dequant_extra.cu", "sample.cu", "dist.cu", "llama_ops.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-fmad=false", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

@@ -110,6 +110,7 @@ int caten_b200_init(int device, caten_b200_ctx **out) {
   ctx->sm_count = prop.multiProcessorCount;
   if (const char *e = getenv("CATEN_B200_PDL")) ctx->use_pdl = atoi(e) != 0;
   if (const char *e = getenv("CATEN_B200_SPLITK_CLUSTER")) ctx->splitk_cluster = atoi(e);
+  if (const char *e = getenv("CATEN_B200_DENSE_GEMM")) ctx->dense_gemm = atoi(e) != 0;
   if (const char *e = getenv("CATEN_B200_ATTN_TC")) ctx->attn_tc = atoi(e);
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaStreamCreate"); }
   if ((e = cudaMalloc(&ctx->d_status, 4 * sizeof(int))) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaMalloc"); }
@@ -135,6 +136,7 @@ int caten_b200_destroy(caten_b200_ctx *ctx) {
   for (auto e : ctx->prof_pool) cudaEventDestroy(e);
   if (ctx->xbf.ptr) cudaFree(ctx->xbf.ptr);
   if (ctx->wtmp.ptr) cudaFree(ctx->wtmp.ptr);
+  if (ctx->wbf.ptr) cudaFree(ctx->wbf.ptr);
   cudaFree(ctx->d_status);
   cudaFreeHost(ctx->h_status);
   cudaStreamDestroy(ctx->stream);

@@ -84,6 +84,8 @@ struct caten_b200_ctx {
   int *h_status = nullptr;   // pinned mirror
   cb::Scratch xbf;           // bf16 copy (hi, lo) of the activation operand of the tensor-core GEMM
   cb::Scratch wtmp;          // split-K partial tiles of the tensor-core GEMM
+  cb::Scratch wbf;           // bf16 copy (hi, lo) of the weight operand of the many-row GEMM
+  bool dense_gemm = true;    // many-row linears expand the weights once and run the TMA-fed GEMM (CATEN_B200_DENSE_GEMM=0: off)
   void *encode_tiled = nullptr;  // cuTensorMapEncodeTiled, resolved at init
   int64_t launches = 0;
   int64_t device_failures = 0;   // kernel-side check failures reported so far
@@ -188,6 +190,19 @@ int launch_gemm_tc_noalloc(caten_b200_ctx *ctx, const caten_b200_weight *w, cons
 int launch_relu_matmul_simt(caten_b200_ctx *ctx, const float *a, const float *b, float *c, int64_t M, int64_t K, int64_t N);
 int launch_relu_matmul_tc(caten_b200_ctx *ctx, const float *a, const float *b, float *c, int64_t M, int64_t K,
                           int64_t N, int nsplit);
+
+// where a weight operand lives
+struct WSrc {
+  const void *qs;
+  const __half *d, *m;
+  const uint32_t *qh;
+  int64_t nkb;
+};
+constexpr int WT_F32_T = 100;  // pseudo weight type: fp32 operand given as [K, N] row-major (relu_matmul's b)
+// many-row GEMM with both operands from shared memory (gemm_dense.cu)
+bool gemm_dense_applies(const caten_b200_ctx *ctx, int64_t M, int64_t N, int64_t K);
+int launch_gemm_dense(caten_b200_ctx *ctx, int wt, const WSrc &ws, const float *x, const __nv_bfloat16 *xhi, const __nv_bfloat16 *xlo,
+                      const float *bias, const float *res, int act, float *y, BfOut ybf, int64_t M, int64_t N, int64_t K, int nsplit);
 
 // Whether the next launch may be a programmatic dependent launch; clears the pending-upload mark.
 inline bool take_pdl(caten_b200_ctx *ctx) {

@@ -9,50 +9,8 @@
 
 namespace cb {
 
-constexpr int WT_F32_T = 100;  // fp32 operand given as [K, N] row-major (relu_matmul's b)
 
 constexpr int SG_BM = 64, SG_BN = 64, SG_BK = 32, SG_LD = 68;
-
-template <int WT>
-__device__ __forceinline__ void load_w8(const void *qs, const __half *d, const __half *mins, const uint32_t *qh5, int64_t row,
-                                        int64_t N, int64_t K, int64_t nkb, int kb, int part, float *o) {
-  if (row >= N) {
-#pragma unroll
-    for (int e = 0; e < 8; ++e) o[e] = 0.0f;
-    return;
-  }
-  if (WT == CATEN_B200_F32) {
-    const float4 *p = reinterpret_cast<const float4 *>((const float *)qs + row * K + (int64_t)kb * 32 + part * 8);
-    const float4 a = p[0], b = p[1];
-    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
-  } else if (WT == CATEN_B200_F16) {
-    const uint4 v = *reinterpret_cast<const uint4 *>((const __half *)qs + row * K + (int64_t)kb * 32 + part * 8);
-    const __half *h = reinterpret_cast<const __half *>(&v);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) o[e] = __half2float(h[e]);
-  } else if (WT == CATEN_B200_Q8_0) {
-    const int64_t bi = row * nkb + kb;
-    const uint2 v = *reinterpret_cast<const uint2 *>((const int8_t *)qs + bi * 32 + part * 8);
-    const float sc = __half2float(d[bi]);
-    const int8_t *q = reinterpret_cast<const int8_t *>(&v);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) o[e] = (float)q[e] * sc;
-  } else if (type_is_nibble(WT)) {
-    // elements part*8 .. part*8+7 of the block: parts 0,1 are the low nibbles of bytes 0-7, 8-15;
-    // parts 2,3 the high nibbles of the same bytes; the 5-bit formats take bit 4 from qh
-    const int64_t bi = row * nkb + kb;
-    const uint2 v = *reinterpret_cast<const uint2 *>((const uint8_t *)qs + bi * 16 + (part & 1) * 8);
-    const float sc = __half2float(d[bi]);
-    const float mn = type_has_min(WT) ? __half2float(mins[bi]) : 0.0f;
-    const uint32_t hb = type_has_qh(WT) ? qh5[bi] >> (part * 8) : 0u;
-    const uint8_t *q = reinterpret_cast<const uint8_t *>(&v);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int nib = part < 2 ? (q[e] & 0x0F) : (q[e] >> 4);
-      o[e] = nibble_value<WT>(nib | (int)(((hb >> e) & 1u) << 4), sc, mn);
-    }
-  }
-}
 
 template <int WT>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const void *__restrict__ qs, const __half *__restrict__ d,

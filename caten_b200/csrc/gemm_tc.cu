@@ -35,7 +35,6 @@
 
 namespace cb {
 
-constexpr int WT_F32_T = 100;  // fp32 operand given as [K, N] row-major (relu_matmul's b)
 
 constexpr int TC_BM = 128;      // weight rows per CTA (MMA M)
 constexpr int TC_BK = 64;       // k per stage: 64 bf16 = one 128-byte swizzle row
@@ -754,13 +753,6 @@ static int tc_plan(caten_b200_ctx *ctx, const char *who, int64_t M, int64_t N, i
   return 0;
 }
 
-// where a weight operand lives
-struct WSrc {
-  const void *qs;
-  const __half *d, *m;
-  const uint32_t *qh;
-  int64_t nkb;
-};
 static WSrc wsrc_of(const caten_b200_weight *w) { return WSrc{w->qs, w->d, w->m, w->qh, w->nkb}; }
 
 static int run_tc(caten_b200_ctx *ctx, int wt, const WSrc &ws, const float *x,
@@ -769,6 +761,10 @@ static int run_tc(caten_b200_ctx *ctx, int wt, const WSrc &ws, const float *x,
                   PartIn *defer = nullptr) {
   if (defer) *defer = PartIn();
   if (M <= 0 || N <= 0) return 0;
+  // thousands of rows (prefill): expand the weights once, both operands through TMA
+  // (its epilogue moves 16 bytes at a time: bias, residual and outputs must be aligned for that)
+  const uintptr_t align_bits = (uintptr_t)bias | (uintptr_t)res | (uintptr_t)y | (uintptr_t)ybf.hi | (uintptr_t)ybf.lo;
+  if (gemm_dense_applies(ctx, M, N, K) && !(align_bits & 15)) return launch_gemm_dense(ctx, wt, ws, x, xhi_pre, xlo_pre, bias, res, act, y, ybf, M, N, K, nsplit);
   TcPlan p;
   // reduce inside a cluster: always (mode 1) or only when this launch needs its own epilogue (mode 2)
   const bool own_epilogue = !(defer && act == CATEN_B200_ACT_NONE && !ybf.hi && N % 4 == 0);

@@ -221,6 +221,64 @@ def test_gemm_tensor_core(rt, oracle, wtype, M, N, K, prec):
     w.close()
 
 
+# thousands of rows: the weights are expanded to bf16 once and both operands reach the tensor cores through TMA
+# (persistent kernel, two accumulators).  Ragged rows and features, every weight format, both precisions.
+MANY_ROW_CASES = [("q4_0", 2048, 2560, 1600), ("q4_0", 2000, 2500, 768), ("q8_0", 1100, 4800, 128), ("q5_1", 1500, 3200, 256),
+                  ("f32", 1024, 4864, 192), ("f16", 4100, 1200, 64)]
+
+
+@pytest.mark.parametrize("wtype,M,N,K", MANY_ROW_CASES)
+@pytest.mark.parametrize("prec", ["bf16", "bf16x3"])
+def test_gemm_tensor_core_many_rows(rt, oracle, wtype, M, N, K, prec):
+    rng = np.random.Generator(np.random.PCG64(M + 7 * N + K))
+    up, t, raw = make_weight(rng, N, K, wtype)
+    Wf = oracle.dequant(t, raw, N * K).reshape(N, K)
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    bias = rng.standard_normal(N, dtype=np.float32) * 0.1
+    res = rng.standard_normal((M, N), dtype=np.float32) * 0.1
+    w = rt.upload_weight(up)
+    dx, db, dr = rt.transfer_from_array(x), rt.transfer_from_array(bias), rt.transfer_from_array(res)
+    ref_lin = (x.astype(np.float64) @ Wf.T.astype(np.float64))
+    got_lin = rt.linear(w, dx, None, None, L.ACT_NONE, L.PRECISIONS[prec]).numpy()
+    got = rt.linear(w, dx, db, dr, L.ACT_GELU, L.PRECISIONS[prec]).numpy()
+    rt.sync()
+    tol = 2e-2 if prec == "bf16" else 1e-4   # relative to the largest output
+    assert np.abs(got_lin - ref_lin).max() <= tol * np.abs(ref_lin).max()
+    # bias, GELU (as the reference composes it) and residual on a sample of rows through the oracle
+    rows = np.unique(np.concatenate([np.arange(0, 8), np.arange(M - 8, M), rng.integers(0, M, 48)]))
+    ref = oracle.linear(x[rows], Wf, bias, res[rows], 1, mode=0)
+    assert np.abs(got[rows] - ref).max() <= tol * max(1.0, np.abs(ref).max())
+    # and everywhere against the kernel's own un-fused result
+    z = got_lin + bias
+    full = res + 0.5 * z * (1.0 + np.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+    assert np.abs(got - full).max() <= 1e-4 * max(1.0, np.abs(full).max())
+    w.close()
+
+
+def test_gemm_many_rows_matches_the_tile_per_cta_kernel(oracle, monkeypatch):
+    """CATEN_B200_DENSE_GEMM=0 sends many-row linears through the decode GEMM (weights dequantised inside the
+    kernel): the two kernels must agree to split-bf16 accuracy, and relu(matmul) likewise."""
+    from caten_b200.runtime import B200Runtime
+    rng = np.random.Generator(np.random.PCG64(91))
+    up, _, _ = make_weight(rng, 2560, 1600, "q4_0")
+    x = rng.standard_normal((2048, 1600), dtype=np.float32)
+    a, b = S.synth_relu_gemm(seed=1, M=4096, K=768, N=3072)
+    outs = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("CATEN_B200_DENSE_GEMM", flag)
+        with B200Runtime(0) as r2:
+            w = r2.upload_weight(up)
+            y = r2.linear(w, r2.transfer_from_array(x), None, None, L.ACT_NONE, L.PREC_BF16X3).numpy()
+            c = r2.relu_matmul(r2.transfer_from_array(a), r2.transfer_from_array(b), L.PREC_BF16X3).numpy()
+            r2.sync()
+            outs.append((y, c))
+            w.close()
+    assert np.abs(outs[0][0] - outs[1][0]).max() <= 1e-4 * np.abs(outs[1][0]).max()
+    assert np.abs(outs[0][1] - outs[1][1]).max() <= 1e-4 * np.abs(outs[1][1]).max()
+    ref = np.maximum(a[:64].astype(np.float64) @ b.astype(np.float64), 0.0)
+    np.testing.assert_allclose(outs[0][1][:64], ref, atol=1e-5, rtol=1e-5)   # test-gemm.lisp:3-22
+
+
 def test_gemm_tensor_core_split_k_is_deterministic(rt):
     """Few output tiles and a long inner dimension: several CTAs share a tile (split-K) and the
     last one to finish adds the partial tiles in a fixed order, so repeated runs give equal bits."""
