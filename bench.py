@@ -469,9 +469,11 @@ def main():
                 p0 = ev(); pm.forward_device(pin, prompt_len, 0, pout); p1 = ev(); rt.sync()
                 ms = p0.elapsed_time(p1)
                 tf = flop_per_tok * gsz * prompt_len / (ms / 1e3) / 1e12
+                rt.profile_begin(); pm.forward_device(pin, prompt_len, 0, pout); by_class = rt.profile_end()   # a third pass, kernel classes bracketed by events
                 extras["prefill"][f"group_{prec}"] = {"sequences": gsz, "tokens": gsz * prompt_len, "ms": ms, "tokens_per_s": gsz * prompt_len / (ms / 1e3),
                                                        "useful_TFLOP/s": tf, "frac_of_sustained_bf16_peak": tf / bf16_peak,
-                                                       "issued_frac": tf * (3 if prec == "bf16x3" else 1) / bf16_peak}
+                                                       "issued_frac": tf * (3 if prec == "bf16x3" else 1) / bf16_peak,
+                                                       "ms_by_kernel_class": {k: round(v[0], 3) for k, v in by_class.items()}}
                 pm.close(); pin.close(); pout.close()
             # configuration 2 of the reference's benchmark list: relu(A[4096x768] . B[768x3072]), fp32 in and out
             A_, B_ = S.synth_relu_gemm(seed=1)

@@ -396,6 +396,7 @@ int caten_b200_layernorm(caten_b200_ctx *ctx, const float *d_x, const float *d_g
   NEED_CTX(ctx);
   if (!d_x || !d_gamma || !d_beta || !d_y) return fail(ctx, CATEN_B200_EINVAL, "layernorm: NULL argument");
   if (rows < 0 || d <= 0) return fail(ctx, CATEN_B200_EINVAL, "layernorm: bad shape");
+  ProfScope prof(ctx, CATEN_B200_K_LAYERNORM);
   return launch_layernorm(ctx, d_x, d_gamma, d_beta, d_y, rows, d, eps);
 }
 
@@ -531,6 +532,8 @@ int caten_b200_gpt2_create(caten_b200_ctx *ctx, const caten_b200_gpt2_desc *dsc,
     m->attn_w.push_back(ws[0]); m->proj_w.push_back(ws[1]); m->fc_w.push_back(ws[2]); m->mproj_w.push_back(ws[3]);
   }
   int64_t max_rows = dsc->max_rows > 0 ? dsc->max_rows : 8192;
+  if (dsc->max_rows <= 0)
+    if (const char *e = getenv("CATEN_B200_MAX_ROWS")) { const long v = atol(e); if (v >= 1 && v <= (1 << 20)) max_rows = v; }
   if (max_rows < B) max_rows = B;  // a decode step processes the whole batch at once
   m->max_rows = max_rows;
   auto alloc = [&](float **p, int64_t n) { return caten_b200_malloc(ctx, (size_t)n * sizeof(float), (void **)p); };

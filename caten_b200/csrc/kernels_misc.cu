@@ -109,6 +109,9 @@ __device__ __forceinline__ float ln_block_sum(float v, float *red) {
   return t;
 }
 
+// PARTS: the row is residual + a pending split-K linear output (the batched partial-tile loads take ~64 more
+// registers, which only the few-row decode launches can afford: without them 8 CTAs share an SM instead of 2).
+template <bool PARTS>
 __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__restrict__ x, const float *__restrict__ g,
                                                                const float *__restrict__ b, float *__restrict__ y,
                                                                int d4, float invd, float eps, int64_t src_stride,
@@ -121,7 +124,7 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__re
   const float4 *xr = reinterpret_cast<const float4 *>(x) + src_row * d4;
   float4 v[LN_MAXV];
   float sum = 0.0f;
-  if (pin.splits > 0) {
+  if (PARTS && pin.splits > 0) {
     // x is the residual input; the row normalised is residual + the pending linear output, which
     // also becomes the new residual stream.  The partial tiles of all the thread's columns are
     // fetched together, eight splits at a time (the kernel is latency-bound: 256 CTAs, a few
@@ -213,7 +216,7 @@ int launch_layernorm_strided(caten_b200_ctx *ctx, const float *x, const float *g
   if (rows <= 0) return 0;
   if (d % 4 || d > 4 * LN_THREADS * LN_MAXV) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: d=%lld (need d%%4==0, d<=2048)", (long long)d);
   if (rows > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: too many rows");
-  launch_k(ctx, layernorm_kernel, dim3((unsigned)rows), dim3(LN_THREADS), 0, x, g, b, y, (int)(d / 4), 1.0f / (float)d, eps, src_stride,
+  launch_k(ctx, layernorm_kernel<false>, dim3((unsigned)rows), dim3(LN_THREADS), 0, x, g, b, y, (int)(d / 4), 1.0f / (float)d, eps, src_stride,
                                                                    (uint2 *)bf.hi, (uint2 *)bf.lo, PartIn(), (float *)nullptr);
   CB_LAUNCH_CHECK(ctx, "layernorm_kernel");
   return 0;
@@ -225,7 +228,7 @@ int launch_layernorm_pending(caten_b200_ctx *ctx, const PartIn &pin, const float
   if (pin.splits <= 0 || !res || !xout) return fail(ctx, CATEN_B200_EINVAL, "layernorm: no pending linear output");
   if (d % 4 || d > 4 * LN_THREADS * LN_MAXV) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: d=%lld (need d%%4==0, d<=2048)", (long long)d);
   if (rows > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "layernorm: too many rows");
-  launch_k(ctx, layernorm_kernel, dim3((unsigned)rows), dim3(LN_THREADS), 0, res, g, b, y, (int)(d / 4), 1.0f / (float)d, eps, src_stride,
+  launch_k(ctx, layernorm_kernel<true>, dim3((unsigned)rows), dim3(LN_THREADS), 0, res, g, b, y, (int)(d / 4), 1.0f / (float)d, eps, src_stride,
                                                                    (uint2 *)bf.hi, (uint2 *)bf.lo, pin, xout);
   CB_LAUNCH_CHECK(ctx, "layernorm_kernel");
   return 0;

@@ -7,6 +7,7 @@
     python microbench.py relu_matmul --precision bf16x3
     python microbench.py expr --elements 67108864
     python microbench.py decode_step --model gpt2-xl --wtype q4_0 --context 640 [--batch 1]
+    python microbench.py layernorm --rows 8192 --n 1600
 
 Each prints one JSON line.  Operands are rotated over several copies larger in total than the
 126 MB L2, so every launch streams from HBM.  Events bracket each launch (the profile API of the
@@ -185,6 +186,30 @@ def expr(rt, a):
     return {"kernel": "expr_kernel", "elements": n, "cases": out}
 
 
+def layernorm(rt, a):
+    """LayerNorm over --rows rows of width --n through `caten_b200_layernorm` (fp32 in, fp32 out)."""
+    rows, d = a.rows, a.n
+    copies = max(2, int(np.ceil(300e6 / (rows * d * 8))))
+    rng = np.random.Generator(np.random.PCG64(0))
+    xs = [rt.transfer_from_array(rng.standard_normal((rows, d), dtype=np.float32)) for _ in range(copies)]
+    ys = [rt.open_buffer((rows, d)) for _ in range(copies)]
+    g = rt.transfer_from_array(np.ones(d, np.float32))
+    b = rt.transfer_from_array(np.zeros(d, np.float32))
+
+    def once(i):
+        L.check(rt.ctx, rt.lib.caten_b200_layernorm(rt.ctx, xs[i % copies].ptr, g.ptr, b.ptr, ys[i % copies].ptr, rows, d, 1e-5))
+    for i in range(a.warmup):
+        once(i)
+    rt.profile_begin(["layernorm"])
+    for i in range(a.iters):
+        once(i)
+    ms, calls = rt.profile_end()["layernorm"]
+    nbytes = rows * d * 8.0
+    hbm, _ = _peak()
+    return {"kernel": "layernorm_kernel", "rows": rows, "d": d, "us": 1e3 * ms / calls, "algorithmic_bytes": nbytes,
+            "GB/s": nbytes / (ms / calls / 1e3) / 1e9, "frac_of_measured_hbm": nbytes / (ms / calls / 1e3) / 1e9 / hbm}
+
+
 def decode_step(rt, a):
     """The single-kernel decode step (1..4 sequences): time per step from the library's per-class events and, when the
     loaded library is the timing build (`python -m caten_b200.build --timing`, CATEN_B200_LIB=...), the time CTA 0 spends
@@ -230,7 +255,7 @@ def decode_step(rt, a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "gemv", "gemm", "relu_matmul", "expr", "decode_step"])
+    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "gemv", "gemm", "relu_matmul", "expr", "decode_step", "layernorm"])
     ap.add_argument("--elements", type=int, default=1 << 26)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--heads", type=int, default=25)
@@ -247,7 +272,7 @@ def main():
     a = ap.parse_args()
     with B200Runtime(0) as rt:
         print(json.dumps({"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemv": gemv, "gemm": gemm, "relu_matmul": relu_matmul, "expr": expr,
-                          "decode_step": decode_step}[a.what](rt, a)))
+                          "decode_step": decode_step, "layernorm": layernorm}[a.what](rt, a)))
 
 
 if __name__ == "__main__":
