@@ -24,7 +24,32 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float *__restric
                                                           float *__restrict__ vc, float *__restrict__ out, int H,
                                                           int T, int n, const int *__restrict__ d_n,
                                                           __nv_bfloat16 *__restrict__ ohi, __nv_bfloat16 *__restrict__ olo,
-                                                          const PartIn pin) {
+                                                          const PartIn pin, long long prefetch_bytes) {
+  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  float *kb = kc + ((int64_t)b * H + h) * T * 64;
+  float *vb = vc + ((int64_t)b * H + h) * T * 64;
+  // Under programmatic dependent launch the first CTAs of this grid become resident while the kernels before it
+  // (LayerNorm, the qkv linear) still run, and would idle in the wait below.  The history of this head, rows [0, n)
+  // of K and V, was written by earlier steps and depends on nothing in flight, so those CTAs ask for it to be
+  // brought into L2 meanwhile (HBM is nearly idle during the linears): one bulk L2 prefetch of up to 32 KB per
+  // participating thread.  Only a hint: L2 is coherent, nothing reads through it, and a stale position only changes
+  // how much is asked for.  Limited to the streams that together fit `prefetch_bytes` of the 126 MB L2 (measured:
+  // 2-5 % of a step; asking for more than ~100 MB, or asking a layer ahead from the LayerNorm kernels, which
+  // delays the linears' own weight loads behind the prefetch, made steps slower).
+  {
+    constexpr long long PIECE = 32 << 10;
+    int np = d_n ? *d_n : n;
+    np = np < 0 ? 0 : (np > T - 1 ? T - 1 : np);
+    const long long stream_bytes = 256ll * np;
+    const int pieces = (int)((stream_bytes + PIECE - 1) / PIECE);
+    if (tid < 2 * pieces && ((long long)b * H + h + 1) * 2 * stream_bytes <= prefetch_bytes) {
+      const int which = tid >= pieces ? 1 : 0, i = tid - which * pieces;
+      const char *src = reinterpret_cast<const char *>(which ? vb : kb) + (long long)i * PIECE;
+      const long long left = stream_bytes - (long long)i * PIECE;
+      const unsigned bytes = (unsigned)(left < PIECE ? left : PIECE);
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+    }
+  }
   pdl_enter();
   if (d_n) n = *d_n;  // position kept on the device (decode replayed from a CUDA graph)
   extern __shared__ float smem[];
@@ -32,11 +57,8 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float *__restric
   float *part = smem + 64;    // 16 x 64
   float *red = part + 1024;   // 32
   float *sc = red + 32;       // t
-  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
   const int d = H * 64, t = n + 1;
   const float *row = qkv + (int64_t)b * 3 * d;
-  float *kb = kc + ((int64_t)b * H + h) * T * 64;
-  float *vb = vc + ((int64_t)b * H + h) * T * 64;
   if (pin.splits > 0) {
     // the qkv linear left split-K partial tiles: sum this head's q, k, v entries here
     if (tid < 192) {
@@ -318,7 +340,7 @@ int launch_attention(caten_b200_ctx *ctx, const float *qkv, float *kc, float *vc
     if (smem > 48 * 1024)
       CB_CUDA(ctx, cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     launch_k(ctx, attn_decode_kernel, dim3((unsigned)H, (unsigned)B), dim3(256), smem, qkv, kc, vc, out, (int)H, (int)T, (int)n, d_n, bf.hi, bf.lo,
-             pending_qkv ? *pending_qkv : PartIn());
+             pending_qkv ? *pending_qkv : PartIn(), ctx->attn_prefetch_bytes);
     CB_LAUNCH_CHECK(ctx, "attn_decode_kernel");
     return 0;
   }

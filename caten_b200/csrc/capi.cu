@@ -111,6 +111,7 @@ int caten_b200_init(int device, caten_b200_ctx **out) {
   if (const char *e = getenv("CATEN_B200_PDL")) ctx->use_pdl = atoi(e) != 0;
   if (const char *e = getenv("CATEN_B200_SPLITK_CLUSTER")) ctx->splitk_cluster = atoi(e);
   if (const char *e = getenv("CATEN_B200_DENSE_GEMM")) ctx->dense_gemm = atoi(e) != 0;
+  if (const char *e = getenv("CATEN_B200_ATTN_PREFETCH_MB")) ctx->attn_prefetch_bytes = (long long)atoi(e) << 20;
   if (const char *e = getenv("CATEN_B200_ATTN_TC")) ctx->attn_tc = atoi(e);
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaStreamCreate"); }
   if ((e = cudaMalloc(&ctx->d_status, 4 * sizeof(int))) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaMalloc"); }
