@@ -8,6 +8,8 @@
     python microbench.py expr --elements 67108864
     python microbench.py decode_step --model gpt2-xl --wtype q4_0 --context 640 [--batch 1]
     python microbench.py layernorm --rows 8192 --n 1600
+    python microbench.py gguf_load --model gpt2-xl --wtype q4_0
+    python microbench.py sample --batch 256
 
 Each prints one JSON line.  Operands are rotated over several copies larger in total than the
 126 MB L2, so every launch streams from HBM.  Events bracket each launch (the profile API of the
@@ -210,6 +212,81 @@ def layernorm(rt, a):
             "GB/s": nbytes / (ms / calls / 1e3) / 1e9, "frac_of_measured_hbm": nbytes / (ms / calls / 1e3) / 1e9 / hbm}
 
 
+def gguf_load(rt, a):
+    """File -> device: writes a synthetic GPT-2 GGUF file (--model, --wtype) with the Python `gguf` package, then
+    times opening / parsing it in the library (mmap, header, metadata, tensor table) and building the model from
+    it (every tensor uploaded straight from the mapping, quantised ones kept packed)."""
+    import tempfile
+    import time
+    from gguf import GGMLQuantizationType as GT, GGUFWriter
+    from caten_b200.gguf import REMAP, load_gguf, remap_key
+    from caten_b200.gpt2 import make_gpt2_from_gguf
+
+    def file_name(key):   # inverse of the reference's key remapping (apps/gpt2/gpt2.lisp:52-75)
+        for before, after in reversed(REMAP):
+            key = key.replace(after, before)
+        return key
+    p = S.GPT2_SIZES[a.model]
+    T = 1024
+    sd = S.synth_state_dict(p, a.wtype, seed=0, max_seq_len=T)
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "model.gguf")
+        w = GGUFWriter(path, "gpt2")
+        w.add_uint32("gpt2.block_count", p.n_layers)
+        w.add_uint32("gpt2.embedding_length", p.dim)
+        w.add_uint32("gpt2.attention.head_count", p.n_heads)
+        w.add_uint32("gpt2.context_length", T)
+        for k, v in sd.items():
+            assert remap_key(file_name(k)) == k
+            if isinstance(v, S.Packed):
+                w.add_tensor(file_name(k), v.data.reshape(v.rows, v.cols // 32 * S.BLOCK_BYTES[v.ggml_type]), raw_dtype=GT(v.ggml_type))
+            else:
+                w.add_tensor(file_name(k), v)
+        w.write_header_to_file(); w.write_kv_data_to_file(); w.write_tensors_to_file(); w.close()
+        size = os.path.getsize(path)
+        del sd
+        t0 = time.perf_counter()
+        g = load_gguf(path)
+        t_open = time.perf_counter() - t0
+        n_tensors = len(g.tensors)
+        g.close()
+        best = None
+        for _ in range(max(1, min(a.iters, 3))):   # the first pass also pages the file in
+            t0 = time.perf_counter()
+            m = make_gpt2_from_gguf(path, runtime=rt, batch=1, max_seq_len=64)
+            rt.sync()
+            dt = time.perf_counter() - t0
+            m.close()
+            best = dt if best is None else min(best, dt)
+    return {"what": "gguf file -> model on the device", "model": a.model, "wtype": a.wtype, "file_bytes": size, "tensors": n_tensors,
+            "open_parse_ms": 1e3 * t_open, "load_s": best, "GB/s": size / best / 1e9}
+
+
+def sample(rt, a):
+    """`caten_b200_sample`: temperature / top-k sampling of one id per row of [--batch, 50257] logits."""
+    rows, V = a.batch, 50257
+    rng = np.random.Generator(np.random.PCG64(0))
+    copies = 4
+    lg = [rt.transfer_from_array(rng.standard_normal((rows, V), dtype=np.float32) * 3) for _ in range(copies)]
+    u = rt.transfer_from_array(rng.random(rows, dtype=np.float32))
+    out = {}
+    import torch
+    for name, (temp, k) in {"temperature": (0.8, 0), "top_k_40": (0.8, 40)}.items():
+        for i in range(a.warmup):
+            rt.sample(lg[i % copies], u, temp, k).close()
+        rt.sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        st = torch.cuda.ExternalStream(rt.stream)
+        e0.record(st)
+        for i in range(a.iters):
+            rt.sample(lg[i % copies], u, temp, k).close()
+        e1.record(st)
+        rt.sync()
+        us = 1e3 * e0.elapsed_time(e1) / a.iters
+        out[name] = {"us": us, "GB/s": rows * V * 4 / (us / 1e6) / 1e9}
+    return {"kernel": "sample", "rows": rows, "vocab": V, **out}
+
+
 def decode_step(rt, a):
     """The single-kernel decode step (1..4 sequences): time per step from the library's per-class events and, when the
     loaded library is the timing build (`python -m caten_b200.build --timing`, CATEN_B200_LIB=...), the time CTA 0 spends
@@ -255,7 +332,7 @@ def decode_step(rt, a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "gemv", "gemm", "relu_matmul", "expr", "decode_step", "layernorm"])
+    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "gemv", "gemm", "relu_matmul", "expr", "decode_step", "layernorm", "gguf_load", "sample"])
     ap.add_argument("--elements", type=int, default=1 << 26)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--heads", type=int, default=25)
@@ -272,7 +349,7 @@ def main():
     a = ap.parse_args()
     with B200Runtime(0) as rt:
         print(json.dumps({"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemv": gemv, "gemm": gemm, "relu_matmul": relu_matmul, "expr": expr,
-                          "decode_step": decode_step, "layernorm": layernorm}[a.what](rt, a)))
+                          "decode_step": decode_step, "layernorm": layernorm, "gguf_load": gguf_load, "sample": sample}[a.what](rt, a)))
 
 
 if __name__ == "__main__":
