@@ -3,6 +3,7 @@
 #include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include <new>
 #include <vector>
@@ -138,6 +139,11 @@ int caten_b200_destroy(caten_b200_ctx *ctx) {
   if (ctx->xbf.ptr) cudaFree(ctx->xbf.ptr);
   if (ctx->wtmp.ptr) cudaFree(ctx->wtmp.ptr);
   if (ctx->wbf.ptr) cudaFree(ctx->wbf.ptr);
+  if (ctx->upload_stage.ptr) cudaFree(ctx->upload_stage.ptr);
+  for (int k = 0; k < 2; ++k) {
+    if (ctx->pin[k]) cudaFreeHost(ctx->pin[k]);
+    if (ctx->pin_ev[k]) cudaEventDestroy(ctx->pin_ev[k]);
+  }
   cudaFree(ctx->d_status);
   cudaFreeHost(ctx->h_status);
   cudaStreamDestroy(ctx->stream);
@@ -163,10 +169,38 @@ int caten_b200_free(caten_b200_ctx *ctx, void *d_ptr) {
   return 0;
 }
 
+// Host -> device copy queued on the context's stream.  Large sources (a memory-mapped model file, a numpy array) are
+// pageable memory, which the driver copies through its own small staging area at a few GB/s; here they go through two
+// 16 MiB pinned buffers of the context in alternation, so that the CPU fills one while the DMA engine drains the other.
+// On return the source has been read completely (the copies themselves may still be in flight on the stream).
+static constexpr size_t PIN_BYTES = (size_t)16 << 20;
+static int h2d_staged(caten_b200_ctx *ctx, void *d_dst, const void *h_src, size_t bytes) {
+  if (bytes < ((size_t)4 << 20)) {
+    CB_CUDA(ctx, cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    CB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // a pageable source may still be read after the call returns otherwise
+    return 0;
+  }
+  for (int k = 0; k < 2; ++k)
+    if (!ctx->pin[k]) {
+      CB_CUDA(ctx, cudaHostAlloc(&ctx->pin[k], PIN_BYTES, cudaHostAllocDefault));
+      CB_CUDA(ctx, cudaEventCreateWithFlags(&ctx->pin_ev[k], cudaEventDisableTiming));
+    }
+  int k = 0;
+  for (size_t off = 0; off < bytes; off += PIN_BYTES, k ^= 1) {
+    const size_t n = bytes - off < PIN_BYTES ? bytes - off : PIN_BYTES;
+    if (ctx->pin_busy[k]) CB_CUDA(ctx, cudaEventSynchronize(ctx->pin_ev[k]));  // its previous copy has left the buffer
+    memcpy(ctx->pin[k], (const char *)h_src + off, n);
+    CB_CUDA(ctx, cudaMemcpyAsync((char *)d_dst + off, ctx->pin[k], n, cudaMemcpyHostToDevice, ctx->stream));
+    CB_CUDA(ctx, cudaEventRecord(ctx->pin_ev[k], ctx->stream));
+    ctx->pin_busy[k] = true;
+  }
+  return 0;
+}
+
 int caten_b200_h2d(caten_b200_ctx *ctx, void *d_dst, const void *h_src, size_t bytes) {
   NEED_CTX(ctx);
   if (bytes && (!d_dst || !h_src)) return fail(ctx, CATEN_B200_EINVAL, "h2d: NULL pointer");
-  CB_CUDA(ctx, cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  if (int rc = h2d_staged(ctx, d_dst, h_src, bytes)) return rc;
   CB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return 0;
 }
@@ -296,13 +330,16 @@ int caten_b200_weight_upload(caten_b200_ctx *ctx, int type, const void *h_blocks
   const int64_t nbytes = caten_b200_weight_nbytes(type, rows, cols);
   if (nbytes < 0)
     return fail(ctx, CATEN_B200_EUNSUPPORTED, "weight_upload: ggml type %d with cols=%lld (types: F32=0 F16=1 Q4_0=2 Q4_1=3 Q5_0=6 Q5_1=7 Q8_0=8 Q2_K=10 Q3_K=11 Q4_K=12 Q5_K=13 Q6_K=14; cols a multiple of the block size)", type, (long long)cols);
-  void *staging = nullptr;
-  CB_CUDA(ctx, cudaMalloc(&staging, (size_t)nbytes));
-  cudaError_t e = cudaMemcpyAsync(staging, h_blocks, (size_t)nbytes, cudaMemcpyHostToDevice, ctx->stream);
-  if (e != cudaSuccess) { cudaFree(staging); return cuda_fail(ctx, e, "cudaMemcpyAsync(weight H2D)"); }
-  const int rc = caten_b200_weight_upload_device(ctx, type, staging, rows, cols, out);
+  // file / host bytes -> pinned bounce buffers -> a staging area on the device (kept by the context and reused by
+  // the next upload: work on the stream is ordered, so the re-layout kernel has read it before it is overwritten)
+  if (int rc = scratch_reserve(ctx, &ctx->upload_stage, (size_t)nbytes)) return rc;
+  if (int rc = h2d_staged(ctx, ctx->upload_stage.ptr, h_blocks, (size_t)nbytes)) return rc;
+  const int rc = caten_b200_weight_upload_device(ctx, type, ctx->upload_stage.ptr, rows, cols, out);
   cudaStreamSynchronize(ctx->stream);
-  cudaFree(staging);
+  if (ctx->upload_stage.bytes > ((size_t)128 << 20)) {  // a large dense tensor went through: do not keep that much
+    cudaFree(ctx->upload_stage.ptr);
+    ctx->upload_stage = cb::Scratch();
+  }
   return rc;
 }
 

@@ -85,6 +85,10 @@ struct caten_b200_ctx {
   cb::Scratch xbf;           // bf16 copy (hi, lo) of the activation operand of the tensor-core GEMM
   cb::Scratch wtmp;          // split-K partial tiles of the tensor-core GEMM
   cb::Scratch wbf;           // bf16 copy (hi, lo) of the weight operand of the many-row GEMM
+  cb::Scratch upload_stage;  // raw blocks of the weight being uploaded, before their re-layout
+  void *pin[2] = {nullptr, nullptr};          // pinned bounce buffers for large copies from pageable host memory
+  cudaEvent_t pin_ev[2] = {nullptr, nullptr};
+  bool pin_busy[2] = {false, false};
   long long attn_prefetch_bytes = 64ll << 20;  // L2 budget of the decode attention's K / V history hint (CATEN_B200_ATTN_PREFETCH_MB; 0 = off)
   bool dense_gemm = true;    // many-row linears expand the weights once and run the TMA-fed GEMM (CATEN_B200_DENSE_GEMM=0: off)
   void *encode_tiled = nullptr;  // cuTensorMapEncodeTiled, resolved at init
