@@ -455,6 +455,22 @@ def test_open_buffer_is_zero_filled_and_roundtrips(rt):
     assert e.numpy().size == 0
 
 
+def test_large_copies_through_the_pinned_bounce_buffers(rt, oracle):
+    """Copies of 4 MiB and more from pageable host memory are cut into 16 MiB pieces that alternate between two
+    pinned buffers: sizes around the piece boundaries, and a packed weight larger than one piece."""
+    rng = np.random.Generator(np.random.PCG64(5))
+    for n in ((4 << 20) // 4, (16 << 20) // 4 + 3, (40 << 20) // 4 + 1):
+        a = rng.integers(0, 2 ** 31, n, dtype=np.int64).astype(np.float32)
+        buf = rt.transfer_from_array(a)
+        np.testing.assert_array_equal(buf.numpy().view(np.uint32), a.view(np.uint32))
+        buf.close()
+    p = S._rand_packed(rng, 4100, 4096, "q8_0")      # 17.8 MB of blocks
+    w = rt.upload_weight(p)
+    want = oracle.dequant(p.ggml_type, p.data, p.rows * p.cols).reshape(p.rows, p.cols)
+    np.testing.assert_array_equal(w.dequantize().view(np.uint32), want.view(np.uint32))
+    w.close()
+
+
 def test_gemm_split_k_cluster_reduction_matches_global_reduction(oracle, monkeypatch):
     """CATEN_B200_SPLITK_CLUSTER=1 reduces split-K partial tiles inside a thread-block cluster
     (distributed shared memory) instead of a second kernel: same splits order, same epilogue."""
