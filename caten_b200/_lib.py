@@ -79,6 +79,7 @@ SIGNATURES = {
     "caten_b200_memset": (C.c_int, [_vp, _vp, C.c_int, C.c_size_t]),
     "caten_b200_sync": (C.c_int, [_vp]),
     "caten_b200_stream": (_vp, [_vp]),
+    "caten_b200_set_stream": (C.c_int, [_vp, _vp]),
     "caten_b200_weight_upload": (C.c_int, [_vp, C.c_int, _vp, _i64, _i64, _PFP]),
     "caten_b200_weight_upload_device": (C.c_int, [_vp, C.c_int, _vp, _i64, _i64, _PFP]),
     "caten_b200_weight_free": (C.c_int, [_vp, _vp]),

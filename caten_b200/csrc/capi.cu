@@ -115,6 +115,7 @@ int caten_b200_init(int device, caten_b200_ctx **out) {
   if (const char *e = getenv("CATEN_B200_ATTN_PREFETCH_MB")) ctx->attn_prefetch_bytes = (long long)atoi(e) << 20;
   if (const char *e = getenv("CATEN_B200_ATTN_TC")) ctx->attn_tc = atoi(e);
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaStreamCreate"); }
+  ctx->own_stream = ctx->stream;
   if ((e = cudaMalloc(&ctx->d_status, 4 * sizeof(int))) != cudaSuccess) { delete ctx; return cuda_fail(nullptr, e, "cudaMalloc"); }
   cudaMemset(ctx->d_status, 0, 4 * sizeof(int));
 
@@ -146,12 +147,19 @@ int caten_b200_destroy(caten_b200_ctx *ctx) {
   }
   cudaFree(ctx->d_status);
   cudaFreeHost(ctx->h_status);
-  cudaStreamDestroy(ctx->stream);
+  cudaStreamDestroy(ctx->own_stream);
   delete ctx;
   return 0;
 }
 
 void *caten_b200_stream(caten_b200_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
+
+int caten_b200_set_stream(caten_b200_ctx *ctx, void *stream) {
+  NEED_CTX(ctx);
+  CB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  ctx->stream = stream ? (cudaStream_t)stream : ctx->own_stream;
+  return 0;
+}
 
 int caten_b200_malloc(caten_b200_ctx *ctx, size_t bytes, void **d_ptr) {
   NEED_CTX(ctx);

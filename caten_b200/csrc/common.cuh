@@ -78,7 +78,8 @@ struct Scratch {
 struct caten_b200_ctx {
   int device = 0;
   int sm_count = 148;
-  cudaStream_t stream = nullptr;
+  cudaStream_t stream = nullptr;       // where work is queued: own_stream unless the caller supplied one
+  cudaStream_t own_stream = nullptr;
   std::string err;
   int *d_status = nullptr;   // device status word written by kernels whose bounded waits run out
   int *h_status = nullptr;   // pinned mirror

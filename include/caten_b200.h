@@ -86,6 +86,11 @@ int caten_b200_memset(caten_b200_ctx *ctx, void *d_dst, int byte, size_t bytes);
 int caten_b200_sync(caten_b200_ctx *ctx);
 /* The context's cudaStream_t, for callers that time or order work themselves. */
 void *caten_b200_stream(caten_b200_ctx *ctx);
+/* Makes the context queue its work on a stream the caller owns (a cudaStream_t / CUstream of the same device:
+ * the host framework's stream, or one bound to a green context, i.e. to a subset of the SMs); NULL returns to
+ * the context's own stream. Work already queued is waited for first. The caller keeps the stream alive until
+ * the context is destroyed or pointed elsewhere. */
+int caten_b200_set_stream(caten_b200_ctx *ctx, void *stream);
 
 /* ---- weights ----------------------------------------------------------------------------------
  * Replaces external/gguf/tensor-info.lisp:71-77,104-120 + external/gguf/dequantize.lisp:14-53,

@@ -455,6 +455,32 @@ def test_open_buffer_is_zero_filled_and_roundtrips(rt):
     assert e.numpy().size == 0
 
 
+def test_work_can_be_queued_on_a_stream_of_the_caller(oracle):
+    """caten_b200_set_stream: the context queues its kernels on a stream the host owns (here a torch stream), then
+    returns to its own."""
+    torch = pytest.importorskip("torch")
+    from caten_b200.runtime import B200Runtime
+    rng = np.random.Generator(np.random.PCG64(9))
+    up, t, raw = make_weight(rng, 384, 256, "q4_0")
+    Wf = oracle.dequant(t, raw, 384 * 256).reshape(384, 256)
+    x = rng.standard_normal((3, 256), dtype=np.float32)
+    ref = oracle.linear(x, Wf, mode=0)
+    with B200Runtime(0) as r2:
+        own = r2.stream
+        w = r2.upload_weight(up)
+        dx = r2.transfer_from_array(x)
+        host_stream = torch.cuda.Stream()
+        L.check(r2.ctx, r2.lib.caten_b200_set_stream(r2.ctx, host_stream.cuda_stream))
+        assert r2.stream == host_stream.cuda_stream
+        y1 = r2.linear(w, dx).numpy()
+        L.check(r2.ctx, r2.lib.caten_b200_set_stream(r2.ctx, None))
+        assert r2.stream == own
+        y2 = r2.linear(w, dx).numpy()
+        w.close()
+    np.testing.assert_array_equal(y1.view(np.uint32), y2.view(np.uint32))
+    np.testing.assert_allclose(y1, ref, atol=1e-5, rtol=1e-5)
+
+
 def test_large_copies_through_the_pinned_bounce_buffers(rt, oracle):
     """Copies of 4 MiB and more from pageable host memory are cut into 16 MiB pieces that alternate between two
     pinned buffers: sizes around the piece boundaries, and a packed weight larger than one piece."""
