@@ -9,7 +9,7 @@
 //               into one of TWO accumulators in tensor memory (2 x 256 columns)
 //   warps 2..9  epilogue: read the other accumulator with tcgen05.ld, add bias, apply the
 //               activation and the residual, store — while the next tile's MMAs run
-// Tile = 128 output features (TMEM lanes) x 256 rows (TMEM columns) x 64 k per stage.
+// Tile = 128 output features (TMEM lanes) x 256 rows (TMEM columns); a stage holds 64 k (bf16) or 32 k (split bf16).
 // Split-bf16 (NSPLIT = 3) issues W_hi.x_hi + W_lo.x_hi + W_hi.x_lo per k-step, as the decode GEMM.
 // Every mbarrier wait is bounded: when one runs out the role records it in the status word,
 // every role leaves its loop, copies in flight are awaited, tensor memory is freed.
@@ -21,7 +21,10 @@ namespace cb {
 
 constexpr int GD_BM = 128;   // output features per tile (MMA M, TMEM lanes)
 constexpr int GD_BN = 256;   // activation rows per tile (MMA N, TMEM columns)
-constexpr int GD_BK = 64;    // k per stage: 128 bytes of bf16, one swizzle atom
+constexpr int GD_BK = 64;    // k granularity of the operands (K % 64 == 0)
+// k per stage: 64 (128-byte rows, 128-byte swizzle) in bf16; 32 (64-byte rows, 64-byte swizzle) in split bf16, where a
+// 64-k stage of hi and lo tiles is 96 KB and only two would fit: four 48 KB stages keep three loads in flight
+template <int NSPLIT> struct GdStage { static constexpr int BK = NSPLIT == 3 ? 32 : 64; };
 constexpr int GD_EPI_WARPS = 8;
 constexpr int GD_THREADS = (2 + GD_EPI_WARPS) * 32;
 
@@ -150,11 +153,26 @@ __device__ __forceinline__ void gd_store_block(const GdArgs &a, const float *stg
   }
 }
 
+// K-major operand tile whose rows are BK bf16 wide: 128-byte rows with the 128-byte swizzle (8-row groups 1024 bytes
+// apart) or 64-byte rows with the 64-byte swizzle (8-row groups 512 bytes apart)
+template <int BK>
+__device__ __forceinline__ uint64_t gd_desc(uint32_t saddr) {
+  if (BK == 64) return umma_desc(saddr);
+  uint64_t d = (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)4 << 61;  // SWIZZLE_64B
+  return d;
+}
+
 template <int NSPLIT>
 __global__ void __launch_bounds__(GD_THREADS, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tw_hi, const __grid_constant__ CUtensorMap tw_lo,
                   const __grid_constant__ CUtensorMap tx_hi, const __grid_constant__ CUtensorMap tx_lo, const GdArgs a) {
-  constexpr uint32_t W_BYTES = GD_BM * 128u, X_BYTES = GD_BN * 128u;
+  constexpr int BK = GdStage<NSPLIT>::BK;
+  constexpr uint32_t ROW_BYTES = BK * 2u;
+  constexpr uint32_t W_BYTES = GD_BM * ROW_BYTES, X_BYTES = GD_BN * ROW_BYTES;
   constexpr uint32_t STAGE_BYTES = (W_BYTES + X_BYTES) * (NSPLIT == 3 ? 2u : 1u);
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -177,7 +195,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tw_hi, const __grid_consta
   auto st_xlo = [&](int s) { return st_xhi(s) + X_BYTES; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int num_k = a.K / GD_BK;
+  const int num_k = a.K / BK;
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -219,10 +237,10 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tw_hi, const __grid_consta
             break;
           }
           mbar_expect_tx(full(s), STAGE_BYTES);
-          tma_load_2d(st_whi(s), &tw_hi, full(s), kc * GD_BK, f0);
-          if (NSPLIT == 3) tma_load_2d(st_wlo(s), &tw_lo, full(s), kc * GD_BK, f0);
-          tma_load_2d(st_xhi(s), &tx_hi, full(s), kc * GD_BK, m0);
-          if (NSPLIT == 3) tma_load_2d(st_xlo(s), &tx_lo, full(s), kc * GD_BK, m0);
+          tma_load_2d(st_whi(s), &tw_hi, full(s), kc * BK, f0);
+          if (NSPLIT == 3) tma_load_2d(st_wlo(s), &tw_lo, full(s), kc * BK, f0);
+          tma_load_2d(st_xhi(s), &tx_hi, full(s), kc * BK, m0);
+          if (NSPLIT == 3) tma_load_2d(st_xlo(s), &tx_lo, full(s), kc * BK, m0);
           ++issued;
           if (++s == S) { s = 0; ph ^= 1u; }
         }
@@ -254,11 +272,11 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tw_hi, const __grid_consta
           break;
         }
         tc_fence_after();
-        const uint64_t dwh = umma_desc(st_whi(s)), dwl = umma_desc(st_wlo(s));
-        const uint64_t dxh = umma_desc(st_xhi(s)), dxl = umma_desc(st_xlo(s));
+        const uint64_t dwh = gd_desc<BK>(st_whi(s)), dwl = gd_desc<BK>(st_wlo(s));
+        const uint64_t dxh = gd_desc<BK>(st_xhi(s)), dxl = gd_desc<BK>(st_xlo(s));
         if (elect_one()) {
 #pragma unroll
-          for (int k4 = 0; k4 < GD_BK / 16; ++k4) {
+          for (int k4 = 0; k4 < BK / 16; ++k4) {
             const uint64_t adv = (uint64_t)(k4 * 2);  // 16 bf16 = 32 bytes = 2 descriptor units
             umma_bf16(acc, dwh + adv, dxh + adv, a.idesc, (kc > 0 || k4 > 0) ? 1u : 0u);
             if (NSPLIT == 3) {
@@ -330,14 +348,15 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// rows x K bf16, K contiguous; a box is `box_rows` rows of 64 k (128 bytes), 128-byte swizzle, zero fill outside
-static int make_map(caten_b200_ctx *ctx, CUtensorMap *map, const void *base, int64_t rows, int64_t K, int box_rows) {
+// rows x K bf16, K contiguous; a box is `box_rows` rows of `bk` k (128 bytes with the 128-byte swizzle, or 64 with
+// the 64-byte one), zero fill outside
+static int make_map(caten_b200_ctx *ctx, CUtensorMap *map, const void *base, int64_t rows, int64_t K, int box_rows, int bk) {
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)GD_BK, (cuuint32_t)box_rows};
+  const cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = ((EncodeTiledFn)ctx->encode_tiled)(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box,
-                                                       estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                       estr, CU_TENSOR_MAP_INTERLEAVE_NONE, bk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                                                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(ctx, CATEN_B200_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
   return 0;
@@ -399,10 +418,11 @@ int launch_gemm_dense(caten_b200_ctx *ctx, int wt, const WSrc &ws, const float *
   if (((uintptr_t)xhi | (uintptr_t)xlo) & 15) return fail(ctx, CATEN_B200_EINVAL, "gemm_dense: bf16 operand must be 16-byte aligned");
 
   CUtensorMap twh, twl, txh, txl;
-  if ((rc = make_map(ctx, &twh, whi, N, K, GD_BM))) return rc;
-  if ((rc = make_map(ctx, &twl, wlo ? wlo : whi, N, K, GD_BM))) return rc;
-  if ((rc = make_map(ctx, &txh, xhi, M, K, GD_BN))) return rc;
-  if ((rc = make_map(ctx, &txl, nsplit == 3 ? xlo : xhi, M, K, GD_BN))) return rc;
+  const int bk = nsplit == 3 ? GdStage<3>::BK : GdStage<1>::BK;
+  if ((rc = make_map(ctx, &twh, whi, N, K, GD_BM, bk))) return rc;
+  if ((rc = make_map(ctx, &twl, wlo ? wlo : whi, N, K, GD_BM, bk))) return rc;
+  if ((rc = make_map(ctx, &txh, xhi, M, K, GD_BN, bk))) return rc;
+  if ((rc = make_map(ctx, &txl, nsplit == 3 ? xlo : xhi, M, K, GD_BN, bk))) return rc;
 
   GdArgs a;
   a.bias = bias; a.res = res; a.y = y; a.yhi = ybf.hi; a.ylo = ybf.lo; a.status = ctx->d_status;
@@ -411,7 +431,7 @@ int launch_gemm_dense(caten_b200_ctx *ctx, int wt, const WSrc &ws, const float *
   const int64_t tiles = (int64_t)a.tiles_f * ((M + GD_BN - 1) / GD_BN);
   if (tiles > 0x7fffffff) return fail(ctx, CATEN_B200_EUNSUPPORTED, "gemm_dense: too many tiles");
   a.tiles = (int)tiles;
-  const size_t stage = (size_t)(GD_BM + GD_BN) * 128 * parts;
+  const size_t stage = (size_t)(GD_BM + GD_BN) * (size_t)bk * 2 * parts;
   int stages = (int)((200 * 1024) / stage);  // 1 KB slack + 1 KB barriers + stages + 16 KB of epilogue staging fit 227 KB
   if (stages > 6) stages = 6;
   a.stages = stages;
