@@ -59,6 +59,16 @@ struct TcArgs {
 };
 
 
+// Optional timestamps of CTA (0,0,0) (development builds only: -DDS_TIMING), one stream of (tag, SM cycle) pairs per role:
+// 0 = first producer warp, 1 = activation TMA lane, 2 = MMA warp; read back with cb_debug_tc_marks().
+#ifdef DS_TIMING
+__device__ long long g_tc_marks[3][256][2];
+__device__ int g_tc_marks_n[3];
+#define TC_MARK(role, tag, k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (k) < 256) { g_tc_marks[role][k][0] = (tag); g_tc_marks[role][k][1] = clock64(); g_tc_marks_n[role] = ++(k); } } while (0)
+#else
+#define TC_MARK(role, tag, k) do { } while (0)
+#endif
+
 // ---- weight rows: global memory -> registers -> bf16 in tensor memory -----------------------------
 //
 // The weight tile is the MMA's A operand and lives in tensor memory, not in shared memory: TMEM
@@ -322,11 +332,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
   smem += 1024;
   const uint32_t bar0 = smem_u32(bars);
-  auto full_w = [&](int s) { return bar0 + 8u * s; };
-  auto full_x = [&](int s) { return bar0 + 8u * (S + s); };
-  auto empty = [&](int s) { return bar0 + 8u * (2 * S + s); };
-  const uint32_t accum_bar = bar0 + 8u * (3 * S);
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
+  // full(s): both operands of the stage are in place (one arrival per warp of the producer group that wrote the
+  // weight stage, plus the TMA lane's arrive.expect_tx for the activation tile): the MMA warp's loop is a chain of
+  // waits and issues in one thread, and a second barrier per chunk cost it a quarter of its time with few rows
+  auto full = [&](int s) { return bar0 + 8u * s; };
+  auto empty = [&](int s) { return bar0 + 8u * (S + s); };
+  const uint32_t accum_bar = bar0 + 8u * (2 * S);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * S + 1);
   // [0] some role gave up a wait; [1] never set (for waits that must not be cut short);
   // [3] thread 0's verdict for the producer warps: accumulator ready
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -340,8 +352,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(full_w(s), 4);  // one arrival per warp of the producer group that filled the stage
-      mbar_init(full_x(s), 1);
+      mbar_init(full(s), 5);
       mbar_init(empty(s), 1);
     }
     mbar_init(accum_bar, 1);
@@ -368,7 +379,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
     // ---------------- weight producers ----------------
     // Warps run independently.  For its chunk a warp's lane 0 polls the stage's `empty` mbarrier,
     // the warp converts its 32 rows and writes them to the stage's TMEM columns, and lane 0
-    // arrives on `full_w`.  A group that is ahead starts on its next stage while the MMAs of
+    // arrives on `full`.  A group that is ahead starts on its next stage while the MMAs of
     // earlier chunks run, so conversion, barrier latency and the MMAs overlap.
     const int g = warp >> 2, quad = warp & 3;
     const int64_t row = (int64_t)n0 + quad * 32 + lane;
@@ -390,6 +401,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
     // (a few register moves) and the new load goes to the last slot, so the conversion code
     // exists once in the kernel instead of once per slot (a launch starts with a cold
     // instruction cache, and this loop is most of the kernel's code).
+    int pmk = 0;
+    (void)pmk;
     for (int kc = g; kc < num_k && alive; kc += ga) {
       int got = 0;
       if (lane == 0) {
@@ -401,11 +414,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
         alive = false;
       } else {
         tc_fence_after();  // the MMAs that read this stage are complete (their commit fired `empty`)
+        if (warp == 0 && lane == 0) TC_MARK(0, 10, pmk);
         ring[0].template store<NSPLIT>(t_quad + (uint32_t)s * WCOLS);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(full_w(s));
+        if (warp == 0 && lane == 0) TC_MARK(0, 11, pmk);
+        if (lane == 0) mbar_arrive(full(s));
 #pragma unroll
         for (int j = 0; j + 1 < DEPTH; ++j) ring[j] = ring[j + 1];
         if (kc + DEPTH * ga < num_k) ring[DEPTH - 1].load(a, row, row_ok, kc0 + kc + DEPTH * ga);
@@ -476,16 +491,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
           if (!*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 3; a.status[2] = kc; }
           break;
         }
-        mbar_expect_tx(full_x(s), stage_bytes);
-        tma_load_2d(smem_u32(stage_xhi(s)), &tm_hi, full_x(s), (kc0 + kc) * TC_BK, m0);
-        if (NSPLIT == 3) tma_load_2d(smem_u32(stage_xlo(s)), &tm_lo, full_x(s), (kc0 + kc) * TC_BK, m0);
+        mbar_expect_tx(full(s), stage_bytes);
+        tma_load_2d(smem_u32(stage_xhi(s)), &tm_hi, full(s), (kc0 + kc) * TC_BK, m0);
+        if (NSPLIT == 3) tma_load_2d(smem_u32(stage_xlo(s)), &tm_lo, full(s), (kc0 + kc) * TC_BK, m0);
         issued = kc + 1;
         if (++s == S) { s = 0; ph ^= 1u; }
       }
       if (*abort_flag) {
         // let the copies this thread started land before the CTA's shared memory is released
         for (int kc = issued > S ? issued - S : 0; kc < issued; ++kc)
-          mbar_wait(full_x(kc % S), (uint32_t)(kc / S) & 1u, abort_flag + 1);
+          mbar_wait(full(kc % S), (uint32_t)(kc / S) & 1u, abort_flag + 1);
       }
     }
   } else {
@@ -499,8 +514,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
     const uint32_t t_w0 = tmem_base + (uint32_t)TC_WCOL0;
     const uint64_t dx0 = umma_desc(smem_u32(smem));  // descriptor of stage 0's x_hi tile
     const uint32_t stage16 = stage_bytes >> 4, xlo16 = xbytes >> 4;  // in descriptor address units
+    // With few activation rows an MMA is short and this loop — one thread's chain of a barrier test, eight issues and
+    // a commit, ~600 cycles per chunk — sets the pace of the K loop (the producers are 1.5-2 k cycles ahead); with 256
+    // rows a chunk's twelve MMAs take 1.54 k cycles on the tensor pipe and hide it.
+    int mk = 0;
+    (void)mk;
+    if (lane == 0) TC_MARK(2, 1, mk);
     for (int kc = 0; kc < num_k; ++kc) {
-      ok = mbar_wait(full_w(s), ph, abort_flag) && mbar_wait(full_x(s), ph, abort_flag);
+      ok = mbar_wait(full(s), ph, abort_flag);
       if (!ok) {
         if (lane == 0 && !*abort_flag) { *abort_flag = 1; atomicCAS(a.status, 0, DEV_WAIT_TIMEOUT); a.status[1] = 4; a.status[2] = kc; }
         break;
@@ -528,6 +549,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
         umma_commit(empty(s));  // frees the stage when these MMAs have read it
       }
       __syncwarp();
+      if (lane == 0) TC_MARK(2, 22, mk);
       if (++s == S) { s = 0; ph ^= 1u; }
     }
     if (ok && elect_one()) umma_commit(accum_bar);
@@ -910,3 +932,10 @@ int launch_relu_matmul_tc(caten_b200_ctx *ctx, const float *a, const float *b, f
 }
 
 }  // namespace cb
+
+#ifdef DS_TIMING
+extern "C" int cb_debug_tc_marks(long long *out, int *n) {
+  cudaMemcpyFromSymbol(n, cb::g_tc_marks_n, sizeof(int) * 3);
+  return (int)cudaMemcpyFromSymbol(out, cb::g_tc_marks, sizeof(long long) * 3 * 256 * 2);
+}
+#endif
