@@ -118,6 +118,20 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__re
                                                                uint2 *__restrict__ yhi, uint2 *__restrict__ ylo,
                                                                const PartIn pin, float *__restrict__ xout) {
   __shared__ float red[LN_THREADS / 32];
+  // Few-row launches (PARTS: a decode step) are one chain of latencies.  gamma and beta are parameters (written at
+  // load), so they are staged in shared memory before the dependency wait and the loads the kernel ends with are not
+  // one more L2 round trip behind its two reductions.  The many-row launches are bandwidth-bound and read them in place.
+  __shared__ float4 gam[PARTS ? LN_THREADS * LN_MAXV : 1], bet[PARTS ? LN_THREADS * LN_MAXV : 1];
+  if (PARTS) {
+#pragma unroll
+    for (int i = 0; i < LN_MAXV; ++i) {
+      const int c = threadIdx.x + LN_THREADS * i;
+      if (c < d4) {
+        gam[c] = reinterpret_cast<const float4 *>(g)[c];
+        bet[c] = reinterpret_cast<const float4 *>(b)[c];
+      }
+    }
+  }
   pdl_enter();
   const int64_t row = blockIdx.x;
   const int64_t src_row = src_stride > 1 ? (row + 1) * src_stride - 1 : row;
@@ -189,13 +203,13 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__re
   }
   const float var = ln_block_sum(sq, red) * invd;
   const float rs = 1.0f / sqrtf(var + eps);
-  const float4 *g4 = reinterpret_cast<const float4 *>(g), *b4 = reinterpret_cast<const float4 *>(b);
   float4 *yr = reinterpret_cast<float4 *>(y) + row * d4;
 #pragma unroll
   for (int i = 0; i < LN_MAXV; ++i) {
     const int c = threadIdx.x + LN_THREADS * i;
     if (c < d4) {
-      const float4 gg = g4[c], bb = b4[c];
+      const float4 gg = PARTS ? gam[c] : reinterpret_cast<const float4 *>(g)[c];  // (staged by this same thread)
+      const float4 bb = PARTS ? bet[c] : reinterpret_cast<const float4 *>(b)[c];
       float4 o;
       o.x = (v[i].x * rs) * gg.x + bb.x;
       o.y = (v[i].y * rs) * gg.y + bb.y;
