@@ -20,7 +20,7 @@ constexpr float kInvLn2 = 1.0f / 0.6931472f;  // (/ (log 2)) in single float, ap
 #ifndef ATT_U
 #define ATT_U 4  // rows in flight per half-warp
 #endif
-__global__ void __launch_bounds__(256) attn_decode_kernel(const float *__restrict__ qkv, float *__restrict__ kc,
+__global__ void __launch_bounds__(256, 6) attn_decode_kernel(const float *__restrict__ qkv, float *__restrict__ kc,
                                                           float *__restrict__ vc, float *__restrict__ out, int H,
                                                           int T, int n, const int *__restrict__ d_n,
                                                           __nv_bfloat16 *__restrict__ ohi, __nv_bfloat16 *__restrict__ olo,

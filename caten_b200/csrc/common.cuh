@@ -61,9 +61,19 @@ __device__ __forceinline__ float4 partin_load4(const PartIn &p, long long m, int
 __device__ __forceinline__ float partin_load1(const PartIn &p, long long m, int o) {
   const long long tile = (m / p.bnx) * p.tiles_x + (o >> 7);
   const float *src = p.part + (tile * p.bnx + (m % p.bnx)) * 128 + (o & 127);
+  // the bias and up to four partial values are requested together (one round trip to L2 instead of one per split);
+  // the additions keep the split order
+  const float b = p.bias ? p.bias[o] : 0.f;
   float v = 0.f;
-  for (int z = 0; z < p.splits; ++z) v += __ldcs(src + (long long)z * p.zstride);
-  if (p.bias) v = v + p.bias[o];
+  for (int z = 0; z < p.splits; z += 4) {
+    float t[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) t[u] = z + u < p.splits ? __ldcs(src + (long long)(z + u) * p.zstride) : 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (z + u < p.splits) v += t[u];
+  }
+  if (p.bias) v = v + b;
   return v;
 }
 #endif

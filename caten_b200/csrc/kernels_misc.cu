@@ -112,7 +112,7 @@ __device__ __forceinline__ float ln_block_sum(float v, float *red) {
 // PARTS: the row is residual + a pending split-K linear output (the batched partial-tile loads take ~64 more
 // registers, which only the few-row decode launches can afford: without them 8 CTAs share an SM instead of 2).
 template <bool PARTS>
-__global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__restrict__ x, const float *__restrict__ g,
+__global__ void __launch_bounds__(LN_THREADS, PARTS ? 2 : 8) layernorm_kernel(const float *__restrict__ x, const float *__restrict__ g,
                                                                const float *__restrict__ b, float *__restrict__ y,
                                                                int d4, float invd, float eps, int64_t src_stride,
                                                                uint2 *__restrict__ yhi, uint2 *__restrict__ ylo,
@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__re
   // Few-row launches (PARTS: a decode step) are one chain of latencies.  gamma and beta are parameters (written at
   // load), so they are staged in shared memory before the dependency wait and the loads the kernel ends with are not
   // one more L2 round trip behind its two reductions.  The many-row launches are bandwidth-bound and read them in place.
-  __shared__ float4 gam[PARTS ? LN_THREADS * LN_MAXV : 1], bet[PARTS ? LN_THREADS * LN_MAXV : 1];
+  __shared__ float4 gam[PARTS ? LN_THREADS * LN_MAXV : 1], bet[PARTS ? LN_THREADS * LN_MAXV : 1], pbias[PARTS ? LN_THREADS * LN_MAXV : 1];
   if (PARTS) {
 #pragma unroll
     for (int i = 0; i < LN_MAXV; ++i) {
@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__re
       if (c < d4) {
         gam[c] = reinterpret_cast<const float4 *>(g)[c];
         bet[c] = reinterpret_cast<const float4 *>(b)[c];
+        if (pin.bias) pbias[c] = *reinterpret_cast<const float4 *>(pin.bias + 4 * c);  // the pending linear's bias: a parameter too
       }
     }
   }
@@ -173,7 +174,7 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float *__re
       const int c = threadIdx.x + LN_THREADS * i;
       if (on[i]) {
         if (pin.bias) {
-          const float4 bb = *reinterpret_cast<const float4 *>(pin.bias + 4 * c);
+          const float4 bb = pbias[c];
           t[i].x = t[i].x + bb.x; t[i].y = t[i].y + bb.y; t[i].z = t[i].z + bb.z; t[i].w = t[i].w + bb.w;
         }
         v[i].x = v[i].x + t[i].x; v[i].y = v[i].y + t[i].y; v[i].z = v[i].z + t[i].z; v[i].w = v[i].w + t[i].w;
