@@ -219,6 +219,14 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tw_hi, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_launch_dependents();
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_map(&tw_hi);
+    tma_prefetch_map(&tx_hi);
+    if (NSPLIT == 3) {
+      tma_prefetch_map(&tw_lo);
+      tma_prefetch_map(&tx_lo);
+    }
+  }
   // both operands and the residual were written by preceding kernels
   pdl_wait();
 

@@ -483,6 +483,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant_
   } else if (warp == TMA_WARP) {
     // ---------------- activation TMA producer ----------------
     if (lane == 0) {
+      // the tensor maps are fetched while the preceding kernel still runs, not by the first copy after the wait
+      tma_prefetch_map(&tm_hi);
+      if (NSPLIT == 3) tma_prefetch_map(&tm_lo);
       pdl_wait();  // x is written by the preceding kernel
       int issued = 0, s = 0;
       uint32_t ph = 0;
